@@ -1,0 +1,86 @@
+"""Weight initialisation.
+
+Scheme (brain/src/train.rs:2268-2346; original/train.py:148-180): s = 0.68*sqrt(3)/sqrt(D);
+wte ~ N(0,1); lm_head ~ N(0, 0.001); Wq, Wk, Wv, Wfc, value embeddings ~ U(-s, s);
+Wo, Wdn, ve_gate = 0; resid_lambdas = 1.0, x0_lambdas = 0.1; MoE: router = 0,
+expert fc ~ U(-s, s), expert proj = 0.  Random numbers come from one process-wide
+xorshift64 stream seeded 42 with Box-Muller normals (brain/src/train.rs:2424-2483), drawn
+in the reference's order: wte, lm_head, then per layer wq, wk, wv, wfc, ve, experts.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+import torch
+
+from .. import native
+
+
+class InitRng:
+    def __init__(self, seed: int = 42):
+        self.state = C.c_uint64(seed)
+        self.lib = native.lib()
+
+    def uniform(self, shape, bound: float, dtype) -> torch.Tensor:
+        n = int(np.prod(shape))
+        if dtype == torch.bfloat16:
+            buf = np.empty(n, dtype=np.uint16)
+            self.lib.ar_uniform_bf16(C.byref(self.state), n, float(bound), buf.ctypes.data)
+            return torch.from_numpy(buf.view(np.int16)).view(torch.bfloat16).view(*shape)
+        buf = np.empty(n, dtype=np.float32)
+        self.lib.ar_uniform_f32(C.byref(self.state), n, float(bound), buf.ctypes.data)
+        return torch.from_numpy(buf).view(*shape).to(dtype)
+
+    def normal(self, shape, scale: float, dtype) -> torch.Tensor:
+        n = int(np.prod(shape))
+        buf = np.empty(n, dtype=np.float32)
+        self.lib.ar_randn_f32(C.byref(self.state), n, float(scale), buf.ctypes.data)
+        return torch.from_numpy(buf).view(*shape).to(dtype)
+
+
+@torch.no_grad()
+def init_weights(model, seed: int = 42, scheme: str = "reference", std: float = 0.02) -> None:
+    """scheme="reference": the engine's scheme above.  scheme="normal": every matrix
+    N(0, std) (used by the CPU plumbing configuration so that no output is identically
+    zero at step 0)."""
+    cfg = model.cfg
+    D = cfg.d_model
+    rng = InitRng(seed)
+    s = cfg.init_scale * math.sqrt(3.0) / math.sqrt(D)
+
+    def put(p, t):
+        p.data.copy_(t.to(p.device, p.dtype).view(p.shape))
+
+    if scheme == "normal":
+        g = torch.Generator().manual_seed(seed)
+        for _, p, kind in model.named_matrix_groups():
+            if kind == "adamw_lr":
+                p.data.fill_(1.0)
+            elif kind == "adamw_l0":
+                p.data.fill_(0.1)
+            else:
+                put(p, torch.randn(p.shape, generator=g) * std)
+        return
+
+    dt = model.dtype
+    if model.wte is not None:
+        put(model.wte, rng.normal(model.wte.shape, 1.0, dt))
+    if model.lm_head is not None:
+        put(model.lm_head, rng.normal(model.lm_head.shape, 0.001, dt))
+    model.resid_lambdas.data.fill_(1.0)
+    model.x0_lambdas.data.fill_(0.1)
+    for blk in model.blocks:
+        put(blk.wqkv, rng.uniform(blk.wqkv.shape, s, dt))
+        blk.wo.data.zero_()
+        if blk.wfc is not None:
+            put(blk.wfc, rng.uniform(blk.wfc.shape, s, dt))
+            blk.wdn.data.zero_()
+        if blk.ve is not None:
+            put(blk.ve, rng.uniform(blk.ve.shape, s, dt))
+            blk.ve_gate.data.zero_()
+        if blk.router is not None:
+            blk.router.data.zero_()
+            put(blk.expert_fc, rng.uniform(blk.expert_fc.shape, s, dt))
+            blk.expert_proj.data.zero_()

@@ -1,0 +1,172 @@
+"""Ops backends: one interface, three implementations.
+
+* ``oracle``   – the plain PyTorch fp32-math statement in ``ops.reference`` (CPU or GPU),
+                 differentiated by autograd.  The numerical reference for everything else.
+* ``baseline`` – library path on a GPU: bf16 ``torch.matmul`` (cuBLAS), library flash
+                 attention / SDPA, torch elementwise ops.  This is the "cuBLAS + library
+                 attention + NCCL" arm that the sm_100a kernels are measured against.
+* ``sm100``    – the hand-written sm_100a kernels of ``autoresearch_b200.ops.sm100``.
+
+The model (``models.gpt``) only talks to this interface, so swapping the implementation
+never changes the training loop (the reference hard-wires its one implementation in
+brain/src/forward.rs and brain/src/backward.rs).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from . import reference as R
+
+
+class OracleBackend:
+    name = "oracle"
+
+    def __init__(self, eps: float = 1e-5, softcap: float = 15.0, ce_chunk: int = 4096):
+        self.eps = eps
+        self.softcap = softcap
+        self.ce_chunk = ce_chunk
+
+    def configure(self, cfg):
+        self.eps, self.softcap, self.ce_chunk = cfg.eps, cfg.softcap, cfg.ce_chunk
+        return self
+
+    # -- elementwise / norms ------------------------------------------------
+    def embedding(self, ids, w):
+        return F.embedding(ids.long(), w)
+
+    def rmsnorm(self, x):
+        return R.rmsnorm(x, self.eps)
+
+    def resid_scale_norm(self, x, x0, lam_r, lam_0, i):
+        return R.resid_scale_norm(x, x0, lam_r[i], lam_0[i], self.eps)
+
+    def add_norm(self, x, proj):
+        return R.add_norm(x, proj, self.eps)
+
+    def residual_add(self, x, y):
+        return (x.float() + y.float()).to(x.dtype)
+
+    def rope_qknorm(self, x, cos, sin):
+        return R.rope_qknorm(x, cos, sin, self.eps)
+
+    def ve_apply(self, v, ve, gate):
+        return R.ve_apply(v, ve, gate)
+
+    # -- contractions ---------------------------------------------------------
+    def linear_col(self, x, w):
+        return R.linear(x, w)
+
+    def linear_row(self, x, w):
+        return R.linear(x, w)
+
+    def linear_col_relu_sq(self, x, w):
+        return R.relu_sq(R.linear(x, w))
+
+    def gate_linear(self, xn, w, ch):
+        return R.linear(xn[:, :ch], w)
+
+    def attention(self, q, k, v, window):
+        return R.attention(q, k, v, window)
+
+    def lm_head_ce(self, xf, w, targets, grad_scale):
+        N = xf.shape[0]
+        parts = []
+        for a in range(0, N, self.ce_chunk):
+            xs, ts = xf[a:a + self.ce_chunk], targets[a:a + self.ce_chunk]
+            if xs.requires_grad or w.requires_grad:
+                parts.append(checkpoint(self._ce_chunk, xs, w, ts, use_reentrant=False))
+            else:
+                parts.append(self._ce_chunk(xs, w, ts))
+        per_tok = torch.cat(parts)
+        return per_tok.sum() * grad_scale, per_tok.detach()
+
+    def _ce_chunk(self, xs, w, ts):
+        return R.softcap_ce(R.linear(xs, w), ts, self.softcap)
+
+    def moe_mlp(self, xn, router, w_fc, w_proj, moe):
+        return R.moe_mlp(xn, router, w_fc, w_proj, moe.top_k, moe.aux_coeff, moe.capacity_factor)
+
+
+def _blocked_window_attention(q, k, v, window: int):
+    """Exact sliding-window attention (key j visible to query i iff i-window <= j <= i)
+    through SDPA on blocks of `window` queries that see their own and the previous block."""
+    B, T, H, hd = q.shape
+    W = window
+    nb = T // W
+    qb = q.view(B, nb, W, H, hd).permute(0, 1, 3, 2, 4)                     # B nb H W hd
+    kb = k.view(B, nb, W, H, hd).permute(0, 1, 3, 2, 4)
+    vb = v.view(B, nb, W, H, hd).permute(0, 1, 3, 2, 4)
+    kprev = torch.cat([torch.zeros_like(kb[:, :1]), kb[:, :-1]], dim=1)
+    vprev = torch.cat([torch.zeros_like(vb[:, :1]), vb[:, :-1]], dim=1)
+    k2 = torch.cat([kprev, kb], dim=3)                                        # B nb H 2W hd
+    v2 = torch.cat([vprev, vb], dim=3)
+    qi = torch.arange(W, device=q.device).view(W, 1)
+    kk = torch.arange(2 * W, device=q.device).view(1, 2 * W)
+    band = (kk >= qi) & (kk <= qi + W)                                        # W x 2W
+    mask = band.view(1, 1, 1, W, 2 * W).expand(1, nb, 1, W, 2 * W).clone()
+    mask[:, 0, :, :, :W] = False
+    o = F.scaled_dot_product_attention(qb, k2, v2, attn_mask=mask)
+    return o.permute(0, 1, 3, 2, 4).reshape(B, T, H, hd)
+
+
+class BaselineBackend(OracleBackend):
+    """Library arm: cuBLAS matmuls, library attention, torch elementwise kernels."""
+
+    name = "baseline"
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self._flash = None
+
+    def _flash_fn(self):
+        if self._flash is None:
+            try:
+                from flash_attn import flash_attn_func
+                self._flash = flash_attn_func
+            except Exception:
+                self._flash = False
+        return self._flash
+
+    def attention(self, q, k, v, window):
+        B, T, H, hd = q.shape
+        if not q.is_cuda:
+            return R.attention(q, k, v, window)
+        fa = self._flash_fn()
+        if fa and q.dtype in (torch.bfloat16, torch.float16):
+            ws = (window, 0) if window < T else (-1, -1)
+            return fa(q, k, v, causal=True, window_size=ws)
+        if window < T and T % window == 0:
+            return _blocked_window_attention(q, k, v, window)
+        if window < T:
+            return R.attention(q, k, v, window)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2),
+                                           v.transpose(1, 2), is_causal=True)
+        return o.transpose(1, 2)
+
+
+_BACKENDS = {}
+
+
+def get_backend(name: str, cfg=None):
+    """Return a configured backend.  ``auto`` picks ``sm100`` on a CUDA device whose
+    compute capability is 10.x and ``oracle`` otherwise."""
+    if name == "auto":
+        name = "sm100" if (torch.cuda.is_available()
+                           and torch.cuda.get_device_capability()[0] == 10) else "oracle"
+    if name == "oracle":
+        be = OracleBackend()
+    elif name == "baseline":
+        be = BaselineBackend()
+    elif name == "sm100":
+        from .sm100 import Sm100Backend
+        be = Sm100Backend()
+    else:
+        raise KeyError(f"unknown ops backend {name!r}")
+    if cfg is not None:
+        be.configure(cfg)
+    return be

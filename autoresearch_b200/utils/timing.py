@@ -1,0 +1,57 @@
+"""CUDA-event phase timing (device time, read only on log steps) and MFU accounting.
+
+The reference records four events per step and reads them only when it logs
+(brain/src/train.rs:867-870,969-975,1042-1052); MFU = flops_per_token * tokens / dt / peak
+(brain/src/train.rs:152-188,708).
+"""
+from __future__ import annotations
+
+import json
+import time
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+
+class PhaseTimer:
+    def __init__(self, enabled: bool):
+        self.enabled = enabled and torch.cuda.is_available()
+        if self.enabled:
+            self.ev = {k: torch.cuda.Event(enable_timing=True)
+                       for k in ("start", "bwd_end", "opt_end", "end")}
+        self.wall = {}
+
+    def mark(self, name: str):
+        if self.enabled:
+            self.ev[name].record()
+        self.wall[name] = time.perf_counter()
+
+    def read_ms(self):
+        """(fwd_bwd_ms, opt_ms, total_ms): one host<->device sync."""
+        if self.enabled:
+            self.ev["end"].synchronize()
+            return (self.ev["start"].elapsed_time(self.ev["bwd_end"]),
+                    self.ev["bwd_end"].elapsed_time(self.ev["opt_end"]),
+                    self.ev["start"].elapsed_time(self.ev["end"]))
+        w = self.wall
+        return ((w["bwd_end"] - w["start"]) * 1e3, (w["opt_end"] - w["bwd_end"]) * 1e3,
+                (w["end"] - w["start"]) * 1e3)
+
+
+def measured_peak_flops(default: float = 1.59e15) -> float:
+    """bf16 tensor peak used as the MFU denominator: the pool's measured cuBLAS burst
+    throughput when the driver-written file is present, otherwise the fallback figure."""
+    for p in (Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json",):
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]) * 1e12
+        except Exception:
+            pass
+    return default
+
+
+def vram_mb() -> float:
+    if torch.cuda.is_available():
+        free, total = torch.cuda.mem_get_info()
+        return (total - free) / (1024.0 * 1024.0)
+    return 0.0
