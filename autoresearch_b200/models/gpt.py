@@ -91,33 +91,20 @@ class GPT(nn.Module):
     def run_layers(self, x: torch.Tensor, x0: torch.Tensor, ids: torch.Tensor,
                    B: int, T: int) -> torch.Tensor:
         cfg, be = self.cfg, self.backend
-        H, hd = cfg.n_head // self.tp, cfg.head_dim
-        Dl = H * hd
         ids_flat = ids.reshape(-1)
         aux_total = None
         for bi, blk in enumerate(self.blocks):
             l = blk.layer
             x, xn = be.resid_scale_norm(x, x0, self.resid_lambdas, self.x0_lambdas, bi)
-            qkv = be.linear_col(xn, blk.wqkv)
-            q, k, v = qkv[:, :Dl], qkv[:, Dl:2 * Dl], qkv[:, 2 * Dl:]
-            if blk.ve is not None:
-                ve = be.embedding(ids_flat, blk.ve)
-                gate = be.gate_linear(xn, blk.ve_gate, cfg.ve_gate_ch)
-                v = be.ve_apply(v.reshape(B, T, H, hd), ve.view(B, T, H, hd), gate.view(B, T, H))
-            else:
-                v = v.reshape(B, T, H, hd)
-            q = be.rope_qknorm(q.reshape(B, T, H, hd), self.rope_cos, self.rope_sin)
-            k = be.rope_qknorm(k.reshape(B, T, H, hd), self.rope_cos, self.rope_sin)
-            a = be.attention(q, k, v, cfg.window(l))
-            proj = be.linear_row(a.reshape(B * T, Dl), blk.wo)
-            x, xn = be.add_norm(x, proj)
+            a = be.attention_block(xn, blk, ids_flat, B, T, cfg, self.rope_cos, self.rope_sin,
+                                   cfg.window(l))
+            x, xn = be.proj_add_norm(a, blk.wo, x)
             if blk.router is not None:
                 y, aux = be.moe_mlp(xn, blk.router, blk.expert_fc, blk.expert_proj, cfg.moe)
                 aux_total = aux if aux_total is None else aux_total + aux
+                x = be.residual_add(x, y)
             else:
-                h = be.linear_col_relu_sq(xn, blk.wfc)
-                y = be.linear_row(h, blk.wdn)
-            x = be.residual_add(x, y)
+                x = be.mlp_add(xn, blk.wfc, blk.wdn, x)
         self.aux_loss = aux_total
         return x
 

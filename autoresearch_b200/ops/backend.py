@@ -73,6 +73,29 @@ class OracleBackend:
     def attention(self, q, k, v, window):
         return R.attention(q, k, v, window)
 
+    # -- coarse blocks (a backend may fuse across these boundaries) ------------------
+    def attention_block(self, xn, blk, ids_flat, B, T, cfg, cos, sin, window):
+        """xn [N, D] -> attention output [N, H*hd] (before the output projection)."""
+        hd = cfg.head_dim
+        Dl = blk.wqkv.shape[0] // 3
+        H = Dl // hd
+        qkv = self.linear_col(xn, blk.wqkv)
+        q, k, v = qkv[:, :Dl], qkv[:, Dl:2 * Dl], qkv[:, 2 * Dl:]
+        v = v.reshape(B, T, H, hd)
+        if blk.ve is not None:
+            ve = self.embedding(ids_flat, blk.ve)
+            gate = self.gate_linear(xn, blk.ve_gate, cfg.ve_gate_ch)
+            v = self.ve_apply(v, ve.view(B, T, H, hd), gate.view(B, T, H))
+        q = self.rope_qknorm(q.reshape(B, T, H, hd), cos, sin)
+        k = self.rope_qknorm(k.reshape(B, T, H, hd), cos, sin)
+        return self.attention(q, k, v, window).reshape(B * T, Dl)
+
+    def proj_add_norm(self, a, w, x):
+        return self.add_norm(x, self.linear_row(a, w))
+
+    def mlp_add(self, xn, wfc, wdn, x):
+        return self.residual_add(x, self.linear_row(self.linear_col_relu_sq(xn, wfc), wdn))
+
     def lm_head_ce(self, xf, w, targets, grad_scale):
         N = xf.shape[0]
         parts = []

@@ -1,0 +1,128 @@
+// C launchers of every sm_100a kernel (one per op, raw pointers + stream), the layer the
+// reference exposes through brain/src/ffi.rs.  All return 0 on success, a cudaError_t or a
+// negative argument-validation code otherwise.  Kernels that wait on barriers or peers
+// never spin unbounded: on expiry they store one of the ERR_* codes to `err_flag` (device
+// int, may be null) and return normally.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+enum ArbEpilogue {
+  EPI_STORE_BF16 = 0,   // C = acc                      (bf16)
+  EPI_RELU2 = 1,        // C = max(acc, 0)^2            (bf16)
+  EPI_ATOMIC_F32 = 2,   // C += acc   (fp32, red.global; split-K allowed)
+  EPI_NS_COMBINE = 3,   // C = alpha*I + beta*aux + gamma*acc   (bf16)
+  EPI_RELU2_BWD = 4,    // C = acc * 2*sqrt(max(aux, 0)): aux = relu(h)^2 saved by the forward (bf16)
+  EPI_STORE_F32 = 5,    // C = acc                      (fp32)
+  EPI_ADD_AUX = 6,      // C = aux + acc                (bf16)
+};
+
+enum ArbError {
+  ERR_NONE = 0,
+  ERR_GEMM_TIMEOUT = 1,
+  ERR_ATTN_TIMEOUT = 2,
+  ERR_COMM_TIMEOUT = 3,
+  ERR_MOE_TIMEOUT = 4,
+};
+
+extern "C" {
+
+// ---- tensor-core GEMM (gemm_sm100.cu) ----------------------------------------------------
+// C[b] (op)= A[b] * B[b];  A is M x K, B is K x N.  *_mn_major = 0: the operand is stored
+// with K contiguous (A as [M, K], B as [N, K]); 1: with M (resp. N) contiguous (A as [K, M],
+// B as [K, N]).  ld* / stride_* in elements.  splitk <= 0 = automatic (EPI_ATOMIC_F32 only).
+int arb_gemm_bf16(const void* A, const void* B, void* C, const void* aux, int M, int N, int K, int batch,
+                  long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                  long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha, float beta,
+                  float gamma, int* err_flag, cudaStream_t stream);
+
+// ---- flash attention (attn_sm100.cu) ----------------------------------------------------------
+// q, k, v, o: [B, T, H, hd=128] bf16 with token stride `ld*` elements (head h at column
+// h*128); lse: [B, H, T] fp32.  window >= T means plain causal; key j is visible to query i
+// iff i - window <= j <= i.
+int arb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int H,
+                 long long ldq, long long ldk, long long ldv, long long ldo, int window, float scale,
+                 int* err_flag, cudaStream_t stream);
+int arb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                 void* dq, void* dk, void* dv, float* delta, float* dq_accum, int B, int T, int H, long long ldq,
+                 long long ldk, long long ldv, long long ldo, long long lddo, long long lddq, long long lddk,
+                 long long lddv, int window, float scale, int* err_flag, cudaStream_t stream);
+
+// ---- row-wise fused norm / residual kernels (elementwise.cu) --------------------------------
+int arb_rmsnorm_fwd(const void* x, void* y, long long rows, int D, float eps, cudaStream_t s);
+// gx (=|+=) rmsnorm_bwd(x, g);  add_to != null: gx = add_to + rmsnorm_bwd
+int arb_rmsnorm_bwd(const void* x, const void* g, const void* add_to, void* gx, long long rows, int D, float eps,
+                    cudaStream_t s);
+int arb_resid_scale_norm_fwd(const void* x, const void* x0, const void* lam_r, const void* lam_0, int idx,
+                             void* x_out, void* xn_out, long long rows, int D, float eps, cudaStream_t s);
+// t = g_xs + rmsnorm_bwd(x', g_xn);  d_x = lam_r*t;  d_x0 = lam_0*t;  dlam_r[idx] += sum(x*t);
+// dlam_0[idx] += sum(x0*t)   (fp32 atomics, one per CTA)
+int arb_resid_scale_norm_bwd(const void* x, const void* x0, const void* lam_r, const void* lam_0, int idx,
+                             const void* g_xs, const void* g_xn, void* d_x, void* d_x0, float* dlam_r,
+                             float* dlam_0, long long rows, int D, float eps, cudaStream_t s);
+int arb_add_norm_fwd(const void* x, const void* proj, void* x_out, void* xn_out, long long rows, int D, float eps,
+                     cudaStream_t s);
+int arb_residual_add(const void* a, const void* b, void* out, long long n, cudaStream_t s);
+int arb_relu_sq_fwd(const void* x, void* y, long long n, cudaStream_t s);
+int arb_relu_sq_bwd(const void* x, const void* g, void* gx, long long n, cudaStream_t s);
+// In-place on the packed qkv buffer [N, 3*H*128]: RoPE + per-head RMSNorm on the q and k
+// column blocks (rstd saved to rstd_qk [N, 2H] fp32); on value-embedding layers also
+// v += 2*sigmoid(xn[:, :32] . Wg[h]) * VE[ids]   (gate logits saved to gate_out [N, H] fp32).
+int arb_qkv_post_fwd(void* qkv, const void* cos_t, const void* sin_t, float* rstd_qk, const void* xn,
+                     const int* ids, const void* ve_w, const void* gate_w, float* gate_out, long long N, int T,
+                     int H, int D_model, int gate_ch, float eps, cudaStream_t s);
+// In-place on d_qkv: norm/RoPE backward on the q, k blocks (needs the forward outputs in
+// qkv); value-embedding backward: d_ve (dense [N, H*128] bf16), d_gate_w += (fp32 [H, ch]),
+// d_xn_gate [N, ch] bf16; dgl is caller-provided scratch of N*H floats (gate-logit gradient).
+int arb_qkv_post_bwd(void* d_qkv, const void* qkv, const void* cos_t, const void* sin_t, const float* rstd_qk,
+                     const void* xn, const int* ids, const void* ve_w, const void* gate_w, const float* gate,
+                     void* d_ve, float* d_gate_w, void* d_xn_gate, float* dgl, long long N, int T, int H,
+                     int D_model, int gate_ch, cudaStream_t s);
+int arb_embedding_fwd(const int* ids, const void* w, void* out, long long N, int D, int vocab, cudaStream_t s);
+// dW[ids[i], :] += g[i, :]  (fp32 accumulate with red.global)
+int arb_embedding_bwd(const int* ids, const void* g, float* dw, long long N, int D, int vocab, cudaStream_t s);
+int arb_add_cols(void* dst, long long ld_dst, const void* src, long long rows, int cols, cudaStream_t s);
+int arb_cast_f32_to_bf16(const float* src, void* dst, long long n, float scale, cudaStream_t s);
+int arb_accum_bf16_into_f32(const void* src, float* dst, long long n, cudaStream_t s);
+
+// ---- soft-capped cross entropy (cross_entropy.cu) ------------------------------------------
+// logits [rows, V] bf16 (row stride ld).  Writes per-token loss; if dlogits_scale != 0 the
+// logits are overwritten in place by d_logits = (p - 1[tgt]) * scale * (1 - (s/cap)^2).
+int arb_softcap_ce(void* logits, long long ld, const int* targets, float* loss, long long rows, int V,
+                   float softcap, float dlogits_scale, cudaStream_t s);
+
+// ---- optimizer (optim.cu) -----------------------------------------------------------------------
+int arb_adamw(float* master, const float* grad, float* m, float* v, void* shadow_bf16, long long n, float lr,
+              float beta1, float beta2, float eps, float wd, float bc1, float bc2, cudaStream_t s);
+// buf = mu*buf + (1-mu)*g ; u = (1-mu)*g + mu*buf -> bf16 ; sumsq[mat] += sum(u_bf16^2)
+int arb_muon_nesterov(float* buf, const float* grad, void* u_bf16, float* sumsq, long long per_mat, int n_mat,
+                      float mu, cudaStream_t s);
+// x = u / (sqrt(sumsq[mat])*1.02 + 1e-6)
+int arb_muon_frob_scale(void* u_bf16, const float* sumsq, long long per_mat, int n_mat, cudaStream_t s);
+// NorMuon statistics + cautious update, per matrix [m, n]; reduce over columns if m >= n.
+int arb_normuon_stats(const void* x_bf16, float* v_mean, int n_mat, int m, int n, cudaStream_t s);
+int arb_normuon_scales(const float* v_mean, float* second, float* scale, int n_mat, int n_stat, int red_size,
+                       float beta2, cudaStream_t s);
+int arb_muon_update(float* master, void* shadow_bf16, const void* x_bf16, const float* scale, int n_mat, int m,
+                    int n, float lr, float wd, cudaStream_t s);
+
+// ---- peer-memory collectives (comm.cu) ----------------------------------------------------------
+// out[i] = scale * sum_p peer_p[offset + i] for i in [0, n): every peer pointer addresses that
+// rank's whole gradient bucket (bf16 or fp32) mapped into this process.
+// peer_bufs is a HOST array of world+1 entries: the world peer pointers, then this rank's
+// index cast to a pointer.
+int arb_reduce_scatter_peers(const void* const* peer_bufs, int world, long long offset, long long n, int src_is_bf16,
+                             float* out, float scale, cudaStream_t s);
+int arb_reduce_scatter_multimem(const void* mc_ptr, long long offset, long long n, int src_is_bf16, float* out,
+                                float scale, cudaStream_t s);
+// push this rank's shard [offset, offset+n) of `src` to the same offset of every peer buffer
+int arb_all_gather_push(void* const* peer_bufs, int world, int rank, const void* src, long long offset,
+                        long long n_bytes, cudaStream_t s);
+// local[p-th shard] = peer_p[p-th shard] for every p != rank (peer_bufs: host array)
+int arb_all_gather_pull(const void* const* peer_bufs, int world, int rank, void* local, long long shard_bytes,
+                        cudaStream_t s);
+// Bounded flag barrier among ranks: each rank writes `epoch` to flags[rank] of every peer,
+// then waits (<= 2 s) until all of its own flags reach `epoch`.
+int arb_peer_barrier(int* const* peer_flags, int world, int rank, int epoch, int* err_flag, cudaStream_t s);
+
+}  // extern "C"

@@ -1,0 +1,594 @@
+// Row-wise fused kernels: parameter-free RMSNorm, the residual-scale / residual-add norm
+// fusions, RoPE + QK-norm + value-embedding application on the packed qkv buffer, ReLU^2,
+// embedding gather / scatter-add, small casts.
+//
+// Math: brain/kernels/rms_norm.cu:20-90, fused_norm_residual.cu:22-350, rope.cu:10-107,
+// ve_apply.cu:10-99, embedding.cu:8-80, relu_sq.cu:8-75.  Layout choices are new: one warp
+// per row with the row cached in registers as 16-byte vectors (one global read per
+// element), q/k/v processed in place inside the packed [N, 3D] GEMM output, and the
+// QK-norm backward works from the saved inverse RMS instead of recomputing q and k.
+#include "api.h"
+#include "ptx.cuh"
+
+namespace arb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]); u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+constexpr int ROWS_PER_CTA = 8;  // 8 warps, one row each
+
+// ---------------------------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_k(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                                     long long rows, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nch = D >> 3;
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nch) {
+      ld8(x + row * D + c * 8, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / D + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nch) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] *= r;
+      st8(y + row * D + c * 8, v[i]);
+    }
+  }
+}
+
+// gx = (add_to ? add_to : 0) + r*(g - x*(g.x)/D*r^2)
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_k(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
+                                                     const __nv_bfloat16* __restrict__ add_to, __nv_bfloat16* __restrict__ gx,
+                                                     long long rows, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nch = D >> 3;
+  float xv[NV][8], gv[NV][8];
+  float ss = 0.f, dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nch) {
+      ld8(x + row * D + c * 8, xv[i]);
+      ld8(g + row * D + c * 8, gv[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { ss += xv[i][j] * xv[i][j]; dot += xv[i][j] * gv[i][j]; }
+    }
+  }
+  ss = warp_sum(ss);
+  dot = warp_sum(dot);
+  const float r = rsqrtf(ss / D + eps);
+  const float coef = dot / D * r * r;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nch) {
+      float o[8];
+      if (add_to) ld8(add_to + row * D + c * 8, o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float t = r * (gv[i][j] - xv[i][j] * coef);
+        o[j] = add_to ? o[j] + t : t;
+      }
+      st8(gx + row * D + c * 8, o);
+    }
+  }
+}
+
+// x' = lr*x + l0*x0 (stored bf16) ; xn = rmsnorm(x')
+template <int NV, bool SCALE>
+__global__ void __launch_bounds__(256) resid_norm_fwd_k(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x0,
+                                                        const __nv_bfloat16* __restrict__ lam_r, const __nv_bfloat16* __restrict__ lam_0,
+                                                        int idx, __nv_bfloat16* __restrict__ xo, __nv_bfloat16* __restrict__ xn,
+                                                        long long rows, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nch = D >> 3;
+  const float lr = SCALE ? __bfloat162float(lam_r[idx]) : 1.f;
+  const float l0 = SCALE ? __bfloat162float(lam_0[idx]) : 1.f;
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nch) {
+      float b[8];
+      ld8(x + row * D + c * 8, v[i]);
+      ld8(x0 + row * D + c * 8, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[i][j] = bf16_round(lr * v[i][j] + l0 * b[j]);
+        ss += v[i][j] * v[i][j];
+      }
+      st8(xo + row * D + c * 8, v[i]);
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / D + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nch) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] *= r;
+      st8(xn + row * D + c * 8, v[i]);
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) resid_norm_bwd_k(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x0,
+                                                        const __nv_bfloat16* __restrict__ lam_r, const __nv_bfloat16* __restrict__ lam_0,
+                                                        int idx, const __nv_bfloat16* __restrict__ g_xs, const __nv_bfloat16* __restrict__ g_xn,
+                                                        __nv_bfloat16* __restrict__ d_x, __nv_bfloat16* __restrict__ d_x0,
+                                                        float* __restrict__ dlam_r, float* __restrict__ dlam_0,
+                                                        long long rows, int D, float eps) {
+  __shared__ float red[2][ROWS_PER_CTA];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long row = (long long)blockIdx.x * ROWS_PER_CTA + warp;
+  const int nch = D >> 3;
+  const float lr = __bfloat162float(lam_r[idx]);
+  const float l0 = __bfloat162float(lam_0[idx]);
+  float sr = 0.f, s0 = 0.f;
+  if (row < rows) {
+    float xv[NV][8], bv[NV][8], gv[NV][8];
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nch) {
+        ld8(x + row * D + c * 8, xv[i]);
+        ld8(x0 + row * D + c * 8, bv[i]);
+        ld8(g_xn + row * D + c * 8, gv[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xs = bf16_round(lr * xv[i][j] + l0 * bv[i][j]);
+          ss += xs * xs;
+          dot += xs * gv[i][j];
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float r = rsqrtf(ss / D + eps);
+    const float coef = dot / D * r * r;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nch) {
+        float gs[8], o1[8], o2[8];
+        ld8(g_xs + row * D + c * 8, gs);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xs = bf16_round(lr * xv[i][j] + l0 * bv[i][j]);
+          const float t = gs[j] + r * (gv[i][j] - xs * coef);
+          o1[j] = lr * t;
+          o2[j] = l0 * t;
+          sr += xv[i][j] * t;
+          s0 += bv[i][j] * t;
+        }
+        st8(d_x + row * D + c * 8, o1);
+        st8(d_x0 + row * D + c * 8, o2);
+      }
+    }
+  }
+  sr = warp_sum(sr);
+  s0 = warp_sum(s0);
+  if (lane == 0) { red[0][warp] = sr; red[1][warp] = s0; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, b = 0.f;
+    for (int w = 0; w < ROWS_PER_CTA; ++w) { a += red[0][w]; b += red[1][w]; }
+    atomicAdd(dlam_r + idx, a);
+    atomicAdd(dlam_0 + idx, b);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+__global__ void residual_add_k(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ o, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float x[8], y[8];
+    ld8(reinterpret_cast<const __nv_bfloat16*>(a + i), x);
+    ld8(reinterpret_cast<const __nv_bfloat16*>(b + i), y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] += y[j];
+    st8(reinterpret_cast<__nv_bfloat16*>(o + i), x);
+  }
+}
+__global__ void relu_sq_fwd_k(const uint4* __restrict__ a, uint4* __restrict__ o, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float x[8];
+    ld8(reinterpret_cast<const __nv_bfloat16*>(a + i), x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float r = fmaxf(x[j], 0.f); x[j] = r * r; }
+    st8(reinterpret_cast<__nv_bfloat16*>(o + i), x);
+  }
+}
+__global__ void relu_sq_bwd_k(const uint4* __restrict__ a, const uint4* __restrict__ g, uint4* __restrict__ o, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float x[8], y[8];
+    ld8(reinterpret_cast<const __nv_bfloat16*>(a + i), x);
+    ld8(reinterpret_cast<const __nv_bfloat16*>(g + i), y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = 2.f * fmaxf(x[j], 0.f) * y[j];
+    st8(reinterpret_cast<__nv_bfloat16*>(o + i), x);
+  }
+}
+__global__ void cast_f32_bf16_k(const float4* __restrict__ s, uint2* __restrict__ d, long long n4, float scale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 v = s[i];
+    d[i] = make_uint2(pack_bf16(v.x * scale, v.y * scale), pack_bf16(v.z * scale, v.w * scale));
+  }
+}
+__global__ void accum_bf16_f32_k(const uint2* __restrict__ s, float4* __restrict__ d, long long n4) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    uint2 u = s[i];
+    float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+    float4 v = d[i];
+    v.x += a.x; v.y += a.y; v.z += b.x; v.w += b.y;
+    d[i] = v;
+  }
+}
+// dst[r, 0:cols] += src[r, 0:cols]  (dst row stride ld_dst, src dense)
+__global__ void add_cols_k(__nv_bfloat16* dst, long long ld_dst, const __nv_bfloat16* src, long long rows, int cols) {
+  const long long n = rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols;
+    const int c = int(i - r * cols);
+    __nv_bfloat16* p = dst + r * ld_dst + c;
+    *p = __float2bfloat16(__bfloat162float(*p) + __bfloat162float(src[i]));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// embedding
+__global__ void embedding_fwd_k(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                long long N, int D, int vocab) {
+  const int nch = D >> 3;
+  const long long total = N * nch;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / nch;
+    const int c = int(i - t * nch);
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    reinterpret_cast<uint4*>(out)[i] = *reinterpret_cast<const uint4*>(w + (long long)id * D + c * 8);
+  }
+}
+__global__ void embedding_bwd_k(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ g, float* __restrict__ dw,
+                                long long N, int D, int vocab) {
+  const int nch = D >> 3;
+  const long long total = N * nch;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / nch;
+    const int c = int(i - t * nch);
+    int id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    float f[8];
+    ld8(g + i * 8, f);
+    float* dst = dw + (long long)id * D + c * 8;
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(f[0]), "f"(f[1]), "f"(f[2]), "f"(f[3]) : "memory");
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4), "f"(f[4]), "f"(f[5]), "f"(f[6]), "f"(f[7]) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// qkv post-processing, head_dim = 128.  One warp handles one (token, head) slot of q, k or v:
+// lane l owns elements [4l, 4l+4) of the head row; the rotate-half partner (element i+64) lives
+// in lane l^16.
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&f)[4]) {
+  uint2 u = *reinterpret_cast<const uint2*>(p);
+  float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&f)[4]) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]));
+}
+
+__global__ void __launch_bounds__(256) qkv_post_fwd_k(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ cos_t,
+                                                      const __nv_bfloat16* __restrict__ sin_t, float* __restrict__ rstd_qk,
+                                                      const __nv_bfloat16* __restrict__ xn, const int* __restrict__ ids,
+                                                      const __nv_bfloat16* __restrict__ ve_w, const __nv_bfloat16* __restrict__ gate_w,
+                                                      float* __restrict__ gate_out, long long N, int T, int H, int D_model,
+                                                      int gate_ch, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int slots = ve_w ? 3 * H : 2 * H;
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (wid >= N * slots) return;
+  const long long tok = wid / slots;
+  const int slot = int(wid - tok * slots);
+  const int Dl = H * 128;
+  __nv_bfloat16* row = qkv + tok * 3 * Dl + slot * 128;  // slot < 2H: q/k head; else v head
+  if (slot < 2 * H) {
+    const int t = int(tok % T);
+    float v[4], c[4], s[4];
+    ld4(row + lane * 4, v);
+    const int hi = lane >> 4;                 // 0: low half, 1: high half
+    const int pos = (lane & 15) * 4;          // index inside the half
+    ld4(cos_t + (long long)t * 64 + pos, c);
+    ld4(sin_t + (long long)t * 64 + pos, s);
+    float o[4], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+      // lo' = lo*c + hi*s ; hi' = -lo*s + hi*c
+      o[j] = hi ? (v[j] * c[j] - other * s[j]) : (v[j] * c[j] + other * s[j]);
+      ss += o[j] * o[j];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / 128.f + eps);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] *= r;
+    st4(row + lane * 4, o);
+    if (lane == 0) rstd_qk[tok * 2 * H + slot] = r;
+  } else {
+    const int h = slot - 2 * H;
+    // gate logit = xn[tok, :gate_ch] . Wg[h, :]
+    float part = 0.f;
+    for (int j = lane; j < gate_ch; j += 32)
+      part += __bfloat162float(xn[tok * D_model + j]) * __bfloat162float(gate_w[h * gate_ch + j]);
+    const float gl = warp_sum(part);
+    if (lane == 0) gate_out[tok * H + h] = gl;
+    const float gs = 2.f / (1.f + __expf(-gl));
+    int id = ids[tok];
+    float v[4], e[4];
+    ld4(row + lane * 4, v);
+    ld4(ve_w + (long long)id * Dl + h * 128 + lane * 4, e);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] += gs * e[j];
+    st4(row + lane * 4, v);
+  }
+}
+
+__global__ void __launch_bounds__(256) qkv_post_bwd_k(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __restrict__ qkv,
+                                                      const __nv_bfloat16* __restrict__ cos_t, const __nv_bfloat16* __restrict__ sin_t,
+                                                      const float* __restrict__ rstd_qk, const __nv_bfloat16* __restrict__ xn,
+                                                      const int* __restrict__ ids, const __nv_bfloat16* __restrict__ ve_w,
+                                                      const __nv_bfloat16* __restrict__ gate_w, const float* __restrict__ gate,
+                                                      __nv_bfloat16* __restrict__ d_ve, float* __restrict__ d_gate_logit,
+                                                      long long N, int T, int H) {
+  const int lane = threadIdx.x & 31;
+  const int slots = ve_w ? 3 * H : 2 * H;
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (wid >= N * slots) return;
+  const long long tok = wid / slots;
+  const int slot = int(wid - tok * slots);
+  const int Dl = H * 128;
+  const long long off = tok * 3 * Dl + slot * 128 + lane * 4;
+  if (slot < 2 * H) {
+    const int t = int(tok % T);
+    float y[4], g[4], c[4], s[4];
+    ld4(qkv + off, y);
+    ld4(dqkv + off, g);
+    const float r = rstd_qk[tok * 2 * H + slot];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dot += y[j] * g[j];
+    dot = warp_sum(dot) / 128.f;
+    const int hi = lane >> 4;
+    const int pos = (lane & 15) * 4;
+    ld4(cos_t + (long long)t * 64 + pos, c);
+    ld4(sin_t + (long long)t * 64 + pos, s);
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gr = r * (g[j] - y[j] * dot);  // grad wrt the rotated (pre-norm) value
+      const float other = __shfl_xor_sync(0xffffffffu, gr, 16);
+      // transpose of the rotation: d_lo = g_lo*c - g_hi*s ; d_hi = g_lo*s + g_hi*c
+      o[j] = hi ? (other * s[j] + gr * c[j]) : (gr * c[j] - other * s[j]);
+    }
+    st4(dqkv + off, o);
+  } else {
+    const int h = slot - 2 * H;
+    const float gl = gate[tok * H + h];
+    const float sg = 1.f / (1.f + __expf(-gl));
+    float g[4], e[4], o[4];
+    ld4(dqkv + off, g);
+    const int id = ids[tok];
+    ld4(ve_w + (long long)id * Dl + h * 128 + lane * 4, e);
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { o[j] = 2.f * sg * g[j]; dot += e[j] * g[j]; }
+    st4(d_ve + tok * Dl + h * 128 + lane * 4, o);
+    dot = warp_sum(dot);
+    if (lane == 0) d_gate_logit[tok * H + h] = 2.f * sg * (1.f - sg) * dot;
+  }
+}
+
+// d_gate_w[h, j] += sum_t dgl[t, h] * xn[t, j] ; d_xn_gate[t, j] = sum_h dgl[t, h] * Wg[h, j]
+// One CTA handles a slab of tokens; thread (h, j) accumulates its column.
+__global__ void __launch_bounds__(256) ve_gate_bwd_k(const float* __restrict__ dgl, const __nv_bfloat16* __restrict__ xn,
+                                                     const __nv_bfloat16* __restrict__ gate_w, float* __restrict__ d_gate_w,
+                                                     __nv_bfloat16* __restrict__ d_xn_gate, long long N, int H, int D_model,
+                                                     int ch, int tok_per_cta) {
+  const long long t0 = (long long)blockIdx.x * tok_per_cta;
+  const long long t1 = min(N, t0 + tok_per_cta);
+  const int tid = threadIdx.x;
+  if (tid < H * ch) {
+    const int h = tid / ch, j = tid - h * ch;
+    float acc = 0.f;
+    for (long long t = t0; t < t1; ++t) acc += dgl[t * H + h] * __bfloat162float(xn[t * D_model + j]);
+    atomicAdd(d_gate_w + h * ch + j, acc);
+  }
+  for (long long i = t0 * ch + tid; i < t1 * ch; i += blockDim.x) {
+    const long long t = i / ch;
+    const int j = int(i - t * ch);
+    float acc = 0.f;
+    for (int h = 0; h < H; ++h) acc += dgl[t * H + h] * __bfloat162float(gate_w[h * ch + j]);
+    d_xn_gate[i] = __float2bfloat16(acc);
+  }
+}
+
+static inline int grid_for(long long n, int threads, int cap = 148 * 16) {
+  long long b = (n + threads - 1) / threads;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return int(b);
+}
+
+#define ROW_DISPATCH(KERNEL, ...)                                                        \
+  do {                                                                                     \
+    const int blocks = int((rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA);                      \
+    if (D <= 256) KERNEL<1><<<blocks, 256, 0, s>>>(__VA_ARGS__);                           \
+    else if (D <= 512) KERNEL<2><<<blocks, 256, 0, s>>>(__VA_ARGS__);                      \
+    else if (D <= 1024) KERNEL<4><<<blocks, 256, 0, s>>>(__VA_ARGS__);                     \
+    else if (D <= 2048) KERNEL<8><<<blocks, 256, 0, s>>>(__VA_ARGS__);                     \
+    else KERNEL<16><<<blocks, 256, 0, s>>>(__VA_ARGS__);                                   \
+  } while (0)
+
+static inline int check_row_args(long long rows, int D) {
+  if (rows <= 0 || D <= 0 || (D & 7) || D > 4096) return -3;
+  return 0;
+}
+static inline bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
+
+}  // namespace arb
+
+using namespace arb;
+typedef __nv_bfloat16 bf16;
+
+extern "C" {
+
+int arb_rmsnorm_fwd(const void* x, void* y, long long rows, int D, float eps, cudaStream_t s) {
+  if (check_row_args(rows, D) || misaligned(x) || misaligned(y)) return -3;
+  ROW_DISPATCH(rmsnorm_fwd_k, (const bf16*)x, (bf16*)y, rows, D, eps);
+  return int(cudaGetLastError());
+}
+int arb_rmsnorm_bwd(const void* x, const void* g, const void* add_to, void* gx, long long rows, int D, float eps, cudaStream_t s) {
+  if (check_row_args(rows, D) || misaligned(x) || misaligned(g) || misaligned(gx) || misaligned(add_to)) return -3;
+  ROW_DISPATCH(rmsnorm_bwd_k, (const bf16*)x, (const bf16*)g, (const bf16*)add_to, (bf16*)gx, rows, D, eps);
+  return int(cudaGetLastError());
+}
+int arb_resid_scale_norm_fwd(const void* x, const void* x0, const void* lam_r, const void* lam_0, int idx, void* x_out,
+                             void* xn_out, long long rows, int D, float eps, cudaStream_t s) {
+  if (check_row_args(rows, D) || misaligned(x) || misaligned(x0) || misaligned(x_out) || misaligned(xn_out)) return -3;
+#define RSN(NV) resid_norm_fwd_k<NV, true>
+  const int blocks = int((rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA);
+  if (D <= 256) RSN(1)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)x0, (const bf16*)lam_r, (const bf16*)lam_0, idx, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+  else if (D <= 512) RSN(2)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)x0, (const bf16*)lam_r, (const bf16*)lam_0, idx, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+  else if (D <= 1024) RSN(4)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)x0, (const bf16*)lam_r, (const bf16*)lam_0, idx, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+  else if (D <= 2048) RSN(8)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)x0, (const bf16*)lam_r, (const bf16*)lam_0, idx, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+  else RSN(16)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)x0, (const bf16*)lam_r, (const bf16*)lam_0, idx, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+#undef RSN
+  return int(cudaGetLastError());
+}
+int arb_add_norm_fwd(const void* x, const void* proj, void* x_out, void* xn_out, long long rows, int D, float eps, cudaStream_t s) {
+  if (check_row_args(rows, D) || misaligned(x) || misaligned(proj) || misaligned(x_out) || misaligned(xn_out)) return -3;
+#define RSN(NV) resid_norm_fwd_k<NV, false>
+  const int blocks = int((rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA);
+  if (D <= 256) RSN(1)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)proj, nullptr, nullptr, 0, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+  else if (D <= 512) RSN(2)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)proj, nullptr, nullptr, 0, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+  else if (D <= 1024) RSN(4)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)proj, nullptr, nullptr, 0, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+  else if (D <= 2048) RSN(8)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)proj, nullptr, nullptr, 0, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+  else RSN(16)<<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)proj, nullptr, nullptr, 0, (bf16*)x_out, (bf16*)xn_out, rows, D, eps);
+#undef RSN
+  return int(cudaGetLastError());
+}
+int arb_resid_scale_norm_bwd(const void* x, const void* x0, const void* lam_r, const void* lam_0, int idx, const void* g_xs,
+                             const void* g_xn, void* d_x, void* d_x0, float* dlam_r, float* dlam_0, long long rows, int D,
+                             float eps, cudaStream_t s) {
+  if (check_row_args(rows, D) || misaligned(x) || misaligned(x0) || misaligned(g_xs) || misaligned(g_xn) || misaligned(d_x) || misaligned(d_x0)) return -3;
+  ROW_DISPATCH(resid_norm_bwd_k, (const bf16*)x, (const bf16*)x0, (const bf16*)lam_r, (const bf16*)lam_0, idx, (const bf16*)g_xs,
+               (const bf16*)g_xn, (bf16*)d_x, (bf16*)d_x0, dlam_r, dlam_0, rows, D, eps);
+  return int(cudaGetLastError());
+}
+int arb_residual_add(const void* a, const void* b, void* out, long long n, cudaStream_t s) {
+  if (n <= 0 || (n & 7) || misaligned(a) || misaligned(b) || misaligned(out)) return -3;
+  residual_add_k<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)a, (const uint4*)b, (uint4*)out, n / 8);
+  return int(cudaGetLastError());
+}
+int arb_relu_sq_fwd(const void* x, void* y, long long n, cudaStream_t s) {
+  if (n <= 0 || (n & 7) || misaligned(x) || misaligned(y)) return -3;
+  relu_sq_fwd_k<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)x, (uint4*)y, n / 8);
+  return int(cudaGetLastError());
+}
+int arb_relu_sq_bwd(const void* x, const void* g, void* gx, long long n, cudaStream_t s) {
+  if (n <= 0 || (n & 7) || misaligned(x) || misaligned(g) || misaligned(gx)) return -3;
+  relu_sq_bwd_k<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)x, (const uint4*)g, (uint4*)gx, n / 8);
+  return int(cudaGetLastError());
+}
+int arb_qkv_post_fwd(void* qkv, const void* cos_t, const void* sin_t, float* rstd_qk, const void* xn, const int* ids,
+                     const void* ve_w, const void* gate_w, float* gate_out, long long N, int T, int H, int D_model,
+                     int gate_ch, float eps, cudaStream_t s) {
+  if (N <= 0 || T <= 0 || H <= 0 || misaligned(qkv) || (reinterpret_cast<uintptr_t>(cos_t) & 7) || (reinterpret_cast<uintptr_t>(sin_t) & 7)) return -3;
+  if (ve_w && (!gate_w || !gate_out || !xn || !ids || misaligned(ve_w))) return -3;
+  const long long warps = N * (ve_w ? 3 * H : 2 * H);
+  qkv_post_fwd_k<<<int((warps + 7) / 8), 256, 0, s>>>((bf16*)qkv, (const bf16*)cos_t, (const bf16*)sin_t, rstd_qk, (const bf16*)xn, ids,
+                                                      (const bf16*)ve_w, (const bf16*)gate_w, gate_out, N, T, H, D_model, gate_ch, eps);
+  return int(cudaGetLastError());
+}
+int arb_qkv_post_bwd(void* d_qkv, const void* qkv, const void* cos_t, const void* sin_t, const float* rstd_qk, const void* xn,
+                     const int* ids, const void* ve_w, const void* gate_w, const float* gate, void* d_ve, float* d_gate_w,
+                     void* d_xn_gate, float* dgl, long long N, int T, int H, int D_model, int gate_ch, cudaStream_t s) {
+  if (N <= 0 || T <= 0 || H <= 0 || misaligned(d_qkv) || misaligned(qkv)) return -3;
+  if (ve_w && (!gate_w || !gate || !xn || !ids || !d_ve || !d_gate_w || !d_xn_gate || !dgl || H * gate_ch > 256)) return -3;
+  const long long warps = N * (ve_w ? 3 * H : 2 * H);
+  qkv_post_bwd_k<<<int((warps + 7) / 8), 256, 0, s>>>((bf16*)d_qkv, (const bf16*)qkv, (const bf16*)cos_t, (const bf16*)sin_t, rstd_qk,
+                                                      (const bf16*)xn, ids, (const bf16*)ve_w, (const bf16*)gate_w, gate, (bf16*)d_ve,
+                                                      dgl, N, T, H);
+  int rc = int(cudaGetLastError());
+  if (ve_w) {
+    const int tpc = 512;
+    ve_gate_bwd_k<<<int((N + tpc - 1) / tpc), 256, 0, s>>>(dgl, (const bf16*)xn, (const bf16*)gate_w, d_gate_w, (bf16*)d_xn_gate, N, H,
+                                                            D_model, gate_ch, tpc);
+    if (!rc) rc = int(cudaGetLastError());
+  }
+  return rc;
+}
+int arb_embedding_fwd(const int* ids, const void* w, void* out, long long N, int D, int vocab, cudaStream_t s) {
+  if (N <= 0 || (D & 7) || misaligned(w) || misaligned(out)) return -3;
+  embedding_fwd_k<<<grid_for(N * (D / 8), 256), 256, 0, s>>>(ids, (const bf16*)w, (bf16*)out, N, D, vocab);
+  return int(cudaGetLastError());
+}
+int arb_embedding_bwd(const int* ids, const void* g, float* dw, long long N, int D, int vocab, cudaStream_t s) {
+  if (N <= 0 || (D & 7) || misaligned(g) || misaligned(dw)) return -3;
+  embedding_bwd_k<<<grid_for(N * (D / 8), 256), 256, 0, s>>>(ids, (const bf16*)g, dw, N, D, vocab);
+  return int(cudaGetLastError());
+}
+int arb_add_cols(void* dst, long long ld_dst, const void* src, long long rows, int cols, cudaStream_t s) {
+  if (rows <= 0 || cols <= 0) return -3;
+  add_cols_k<<<grid_for(rows * cols, 256), 256, 0, s>>>((bf16*)dst, ld_dst, (const bf16*)src, rows, cols);
+  return int(cudaGetLastError());
+}
+int arb_cast_f32_to_bf16(const float* src, void* dst, long long n, float scale, cudaStream_t s) {
+  if (n <= 0 || (n & 3) || misaligned(src) || (reinterpret_cast<uintptr_t>(dst) & 7)) return -3;
+  cast_f32_bf16_k<<<grid_for(n / 4, 256), 256, 0, s>>>((const float4*)src, (uint2*)dst, n / 4, scale);
+  return int(cudaGetLastError());
+}
+int arb_accum_bf16_into_f32(const void* src, float* dst, long long n, cudaStream_t s) {
+  if (n <= 0 || (n & 3) || misaligned(dst) || (reinterpret_cast<uintptr_t>(src) & 7)) return -3;
+  accum_bf16_f32_k<<<grid_for(n / 4, 256), 256, 0, s>>>((const uint2*)src, (float4*)dst, n / 4);
+  return int(cudaGetLastError());
+}
+
+}  // extern "C"

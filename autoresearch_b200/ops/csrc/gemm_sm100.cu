@@ -1,0 +1,355 @@
+// bf16 GEMM on the 5th-generation tensor cores: persistent, warp-specialised, TMA-fed,
+// fp32 accumulators in TMEM (double buffered so the epilogue of one tile overlaps the main
+// loop of the next).
+//
+//   C[b] (op)= A[b] * B[b]        A: M x K, B: K x N (each K-major or MN-major in memory)
+//
+// Replaces the reference's cuBLAS calls (brain/src/gemm.rs:87-441: matmul = NT,
+// matmul_bwd_x = NN, matmul_acc = TN with beta=1, strided-batched forms for Newton-Schulz)
+// and fuses what the reference runs as separate kernels into the epilogue: ReLU^2
+// (brain/kernels/relu_sq.cu), residual add, the Newton-Schulz combine aI + bA + cA^2
+// (brain/kernels/muon.cu:385-415), and fp32 gradient accumulation (split-K partial sums are
+// added with red.global so wide-K dW GEMMs fill all SMs).
+//
+// CTA = 192 threads: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5 epilogue
+// (warp w reads TMEM lanes 32*(w%4)..+31).  Tile 128 x BN x 64 (BN = 256 or 128), 128-byte
+// swizzled smem stages.
+#include "api.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace arb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmArgs {
+  int M, N, K, batch;
+  int m_tiles, n_tiles, kb_total, kb_per_split, splitk;
+  void* C;
+  const void* aux;
+  long long ldc, stride_c;      // elements
+  float alpha, beta, gamma;
+  int* err;
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // + barriers + alignment slack
+};
+
+template <bool A_MN, bool B_MN, int EPI, int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs p) {
+  using L = SmemLayout<BN>;
+  constexpr int STAGES = L::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int items = p.batch * p.m_tiles * p.n_tiles * p.splitk;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+        int t = w;
+        const int nt = t % p.n_tiles; t /= p.n_tiles;
+        const int mt = t % p.m_tiles; t /= p.m_tiles;
+        const int ks = t % p.splitk;
+        const int b = t / p.splitk;
+        const int kb0 = ks * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + s * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_3d(sa + c * 8192, &tmA, &full_bar[s], mt * BM + c * 64, kb * BK, b);
+          } else {
+            tma_load_3d(sa, &tmA, &full_bar[s], kb * BK, mt * BM, b);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_3d(sb + c * 8192, &tmB, &full_bar[s], nt * BN + c * 64, kb * BK, b);
+          } else {
+            tma_load_3d(sb, &tmB, &full_bar[s], kb * BK, nt * BN, b);
+          }
+        }
+      }
+      if (!ok) {
+        // give loads already in flight a bounded chance to land before the CTA exits
+        for (int s = 0; s < STAGES; ++s)
+          for (uint32_t i = 0; i < 4096 && !mbar_try_wait(&full_bar[s], 0) && !mbar_try_wait(&full_bar[s], 1); ++i) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++tile_it) {
+        int t = w / (p.n_tiles * p.m_tiles);
+        const int ks = t % p.splitk;
+        const int kb0 = ks * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        const int acc = tile_it & 1;
+        const uint32_t aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 0, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 0, 1024);
+            tc_mma_ss(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);
+        }
+        if (ok) tc_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ---------------- epilogue (4 warps) ----------------
+    const int q = warp & 3;
+    uint32_t tile_it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++tile_it) {
+      int t = w;
+      const int nt = t % p.n_tiles; t /= p.n_tiles;
+      const int mt = t % p.m_tiles; t /= p.m_tiles;
+      const int b = t / p.splitk;
+      const int acc = tile_it & 1;
+      const uint32_t aph = (tile_it >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], aph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mt * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const long long row_off = (long long)b * p.stride_c + (long long)row * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN + c * 32), v);
+        tmem_wait_ld();
+        const int col0 = nt * BN + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        const bool full = (col0 + 32 <= p.N);
+        if (EPI == EPI_ATOMIC_F32) {
+          float* dst = reinterpret_cast<float*>(p.C) + row_off + col0;
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(__uint_as_float(v[j])),
+                           "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])), "f"(__uint_as_float(v[j + 3])) : "memory");
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(dst + j, __uint_as_float(v[j]));
+          }
+        } else if (EPI == EPI_STORE_F32) {
+          float* dst = reinterpret_cast<float*>(p.C) + row_off + col0;
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __uint_as_float(v[j]);
+          }
+        } else {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (EPI == EPI_RELU2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { float r = fmaxf(f[j], 0.f); f[j] = r * r; }
+          }
+          if (EPI == EPI_NS_COMBINE || EPI == EPI_RELU2_BWD || EPI == EPI_ADD_AUX) {
+            const __nv_bfloat16* ax = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row_off + col0;
+            float a[32];
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 u = *reinterpret_cast<const uint4*>(ax + j);
+                float2 t0 = unpack_bf16(u.x), t1 = unpack_bf16(u.y), t2 = unpack_bf16(u.z), t3 = unpack_bf16(u.w);
+                a[j] = t0.x; a[j + 1] = t0.y; a[j + 2] = t1.x; a[j + 3] = t1.y;
+                a[j + 4] = t2.x; a[j + 5] = t2.y; a[j + 6] = t3.x; a[j + 7] = t3.y;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) a[j] = (col0 + j < p.N) ? __bfloat162float(ax[j]) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (EPI == EPI_NS_COMBINE) f[j] = p.beta * a[j] + p.gamma * f[j] + ((row == col0 + j) ? p.alpha : 0.f);
+              else if (EPI == EPI_RELU2_BWD) f[j] = f[j] * 2.f * sqrtf(fmaxf(a[j], 0.f));
+              else f[j] = f[j] + a[j];
+            }
+          }
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row_off + col0;
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 u;
+              u.x = pack_bf16(f[j], f[j + 1]); u.y = pack_bf16(f[j + 2], f[j + 3]);
+              u.z = pack_bf16(f[j + 4], f[j + 5]); u.w = pack_bf16(f[j + 6], f[j + 7]);
+              *reinterpret_cast<uint4*>(dst + j) = u;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16(f[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, ERR_GEMM_TIMEOUT);
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+}
+
+// ------------------------------------------------------------------------------------------
+static int g_num_sms = 0;
+
+template <bool A_MN, bool B_MN, int EPI, int BN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, cudaStream_t st) {
+  using L = SmemLayout<BN>;
+  auto kern = gemm_kernel<A_MN, B_MN, EPI, BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  const int items = a.batch * a.m_tiles * a.n_tiles * a.splitk;
+  const int grid = items < g_num_sms ? items : g_num_sms;
+  kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, a);
+  return int(cudaGetLastError());
+}
+
+template <bool A_MN, bool B_MN, int BN>
+static int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, cudaStream_t st) {
+  switch (epi) {
+    case EPI_STORE_BF16: return launch<A_MN, B_MN, EPI_STORE_BF16, BN>(ta, tb, a, st);
+    case EPI_RELU2: return launch<A_MN, B_MN, EPI_RELU2, BN>(ta, tb, a, st);
+    case EPI_ATOMIC_F32: return launch<A_MN, B_MN, EPI_ATOMIC_F32, BN>(ta, tb, a, st);
+    case EPI_NS_COMBINE: return launch<A_MN, B_MN, EPI_NS_COMBINE, BN>(ta, tb, a, st);
+    case EPI_RELU2_BWD: return launch<A_MN, B_MN, EPI_RELU2_BWD, BN>(ta, tb, a, st);
+    case EPI_STORE_F32: return launch<A_MN, B_MN, EPI_STORE_F32, BN>(ta, tb, a, st);
+    case EPI_ADD_AUX: return launch<A_MN, B_MN, EPI_ADD_AUX, BN>(ta, tb, a, st);
+  }
+  return -2;
+}
+
+}  // namespace arb
+
+using namespace arb;
+
+extern "C" int arb_gemm_bf16(const void* A, const void* B, void* C, const void* aux, int M, int N, int K, int batch,
+                             long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                             long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha,
+                             float beta, float gamma, int* err_flag, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -3;
+  // TMA needs 16-byte aligned bases and row strides; vector epilogue needs ldc % 8 == 0.
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -4;
+  if ((lda % 8) || (ldb % 8) || (stride_a % 8) || (stride_b % 8)) return -4;
+  const bool c_f32 = (epi == EPI_ATOMIC_F32 || epi == EPI_STORE_F32);
+  if (ldc % (c_f32 ? 4 : 8)) return -4;
+  if (aux && (reinterpret_cast<uintptr_t>(aux) & 15)) return -4;
+  if ((epi == EPI_NS_COMBINE || epi == EPI_RELU2_BWD || epi == EPI_ADD_AUX) && !aux) return -5;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int BN = (N > 128) ? 256 : 128;
+  GemmArgs a;
+  a.M = M; a.N = N; a.K = K; a.batch = batch;
+  a.m_tiles = (M + BM - 1) / BM;
+  a.n_tiles = (N + BN - 1) / BN;
+  a.kb_total = (K + BK - 1) / BK;
+  if (epi != EPI_ATOMIC_F32) splitk = 1;
+  if (splitk <= 0) {  // automatic: fill the SMs when there are few output tiles
+    const int tiles = batch * a.m_tiles * a.n_tiles;
+    splitk = 1;
+    if (tiles < g_num_sms) splitk = (g_num_sms + tiles - 1) / tiles;
+    const int max_split = a.kb_total / 4 > 0 ? a.kb_total / 4 : 1;  // at least 4 K blocks per split
+    if (splitk > max_split) splitk = max_split;
+  }
+  if (splitk > a.kb_total) splitk = a.kb_total;
+  a.kb_per_split = (a.kb_total + splitk - 1) / splitk;
+  a.splitk = (a.kb_total + a.kb_per_split - 1) / a.kb_per_split;
+  a.C = C; a.aux = aux; a.ldc = ldc; a.stride_c = stride_c;
+  a.alpha = alpha; a.beta = beta; a.gamma = gamma; a.err = err_flag;
+
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[3], str[2];
+    uint32_t box[3];
+    if (a_mn_major) { dims[0] = uint64_t(M); dims[1] = uint64_t(K); box[0] = 64; box[1] = BK; }
+    else { dims[0] = uint64_t(K); dims[1] = uint64_t(M); box[0] = BK; box[1] = BM; }
+    dims[2] = uint64_t(batch); box[2] = 1;
+    str[0] = uint64_t(lda) * 2;
+    str[1] = batch > 1 ? uint64_t(stride_a) * 2 : dims[1] * str[0];
+    int r = make_tmap_bf16(&ta, A, 3, dims, str, box);
+    if (r) return 1000 + r;
+    if (b_mn_major) { dims[0] = uint64_t(N); dims[1] = uint64_t(K); box[0] = 64; box[1] = BK; }
+    else { dims[0] = uint64_t(K); dims[1] = uint64_t(N); box[0] = BK; box[1] = uint32_t(BN); }
+    str[0] = uint64_t(ldb) * 2;
+    str[1] = batch > 1 ? uint64_t(stride_b) * 2 : dims[1] * str[0];
+    r = make_tmap_bf16(&tb, B, 3, dims, str, box);
+    if (r) return 2000 + r;
+  }
+#define ARB_DISPATCH(AM, BMJ)                                                                              \
+  (BN == 256 ? dispatch_epi<AM, BMJ, 256>(epi, ta, tb, a, stream) : dispatch_epi<AM, BMJ, 128>(epi, ta, tb, a, stream))
+  if (!a_mn_major && !b_mn_major) return ARB_DISPATCH(false, false);
+  if (!a_mn_major && b_mn_major) return ARB_DISPATCH(false, true);
+  if (a_mn_major && b_mn_major) return ARB_DISPATCH(true, true);
+  return ARB_DISPATCH(true, false);
+#undef ARB_DISPATCH
+}

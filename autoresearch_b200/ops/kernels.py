@@ -1,0 +1,269 @@
+"""ctypes binding of ``_arb_kernels.so`` plus thin tensor-level wrappers.
+
+Every wrapper validates dtype / device / contiguity and raises on a non-zero return code,
+so a missing or failing native kernel is never silently replaced by a PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_lib = None
+_err_flag = {}
+
+EPI_STORE_BF16, EPI_RELU2, EPI_ATOMIC_F32, EPI_NS_COMBINE, EPI_RELU2_BWD, EPI_STORE_F32, EPI_ADD_AUX = range(7)
+ERR_NAMES = {1: "GEMM barrier wait timed out", 2: "attention barrier wait timed out",
+             3: "peer barrier wait timed out", 4: "MoE dispatch wait timed out"}
+
+launch_count = 0  # number of kernel-launching calls made through this module
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _build.is_current():
+        _build.build()
+    L = C.CDLL(str(_build.SO))
+    vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+    sigs = {
+        "arb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32,
+                          f32, f32, f32, vp, vp],
+        "arb_attn_fwd": [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, f32, vp, vp],
+        "arb_attn_bwd": [vp] * 11 + [i32, i32, i32] + [i64] * 8 + [i32, f32, vp, vp],
+        "arb_rmsnorm_fwd": [vp, vp, i64, i32, f32, vp],
+        "arb_rmsnorm_bwd": [vp, vp, vp, vp, i64, i32, f32, vp],
+        "arb_resid_scale_norm_fwd": [vp, vp, vp, vp, i32, vp, vp, i64, i32, f32, vp],
+        "arb_resid_scale_norm_bwd": [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
+        "arb_add_norm_fwd": [vp, vp, vp, vp, i64, i32, f32, vp],
+        "arb_residual_add": [vp, vp, vp, i64, vp],
+        "arb_relu_sq_fwd": [vp, vp, i64, vp],
+        "arb_relu_sq_bwd": [vp, vp, vp, i64, vp],
+        "arb_qkv_post_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, vp],
+        "arb_qkv_post_bwd": [vp] * 14 + [i64, i32, i32, i32, i32, vp],
+        "arb_embedding_fwd": [vp, vp, vp, i64, i32, i32, vp],
+        "arb_embedding_bwd": [vp, vp, vp, i64, i32, i32, vp],
+        "arb_add_cols": [vp, i64, vp, i64, i32, vp],
+        "arb_cast_f32_to_bf16": [vp, vp, i64, f32, vp],
+        "arb_accum_bf16_into_f32": [vp, vp, i64, vp],
+        "arb_softcap_ce": [vp, i64, vp, vp, i64, i32, f32, f32, vp],
+        "arb_adamw": [vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, f32, vp],
+        "arb_muon_nesterov": [vp, vp, vp, vp, i64, i32, f32, vp],
+        "arb_muon_frob_scale": [vp, vp, i64, i32, vp],
+        "arb_normuon_stats": [vp, vp, i32, i32, i32, vp],
+        "arb_normuon_scales": [vp, vp, vp, i32, i32, i32, f32, vp],
+        "arb_muon_update": [vp, vp, vp, vp, i32, i32, i32, f32, f32, vp],
+        "arb_reduce_scatter_peers": [vp, i32, i64, i64, i32, vp, f32, vp],
+        "arb_reduce_scatter_multimem": [vp, i64, i64, i32, vp, f32, vp],
+        "arb_all_gather_push": [vp, i32, i32, vp, i64, i64, vp],
+        "arb_all_gather_pull": [vp, i32, i32, vp, i64, vp],
+        "arb_peer_barrier": [vp, i32, i32, i32, vp, vp],
+    }
+    for name, args in sigs.items():
+        if hasattr(L, name):
+            f = getattr(L, name)
+            f.restype = C.c_int
+            f.argtypes = args
+    _lib = L
+    return L
+
+
+def available() -> bool:
+    try:
+        lib()
+        return True
+    except Exception:
+        return False
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str):
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+def err_flag(device=None) -> torch.Tensor:
+    """Per-device int32 status word written by kernels whose bounded waits expire."""
+    dev = torch.device(device if device is not None else torch.cuda.current_device())
+    if dev.type != "cuda":
+        dev = torch.device("cuda", torch.cuda.current_device())
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _err_flag:
+        _err_flag[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _err_flag[key]
+
+
+def check_err_flag(device=None) -> None:
+    """Host-side check (one device->host read); raises if any kernel reported a timeout."""
+    f = err_flag(device)
+    v = int(f.item())
+    if v != 0:
+        f.zero_()
+        raise KernelError(ERR_NAMES.get(v, f"kernel error {v}"))
+
+
+def _bf16(t: torch.Tensor, name: str):
+    if not (t.is_cuda and t.dtype == torch.bfloat16):
+        raise TypeError(f"{name} must be a CUDA bf16 tensor")
+
+
+def _row_major_2d(t: torch.Tensor, name: str):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with unit inner stride")
+
+
+# --------------------------------------------------------------------------------------------
+def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = True,
+         out: Optional[torch.Tensor] = None, epi: int = EPI_STORE_BF16, aux: Optional[torch.Tensor] = None,
+         splitk: int = 0, alpha: float = 0.0, beta: float = 0.0, gamma: float = 1.0) -> torch.Tensor:
+    """C = op(A) @ op(B) on the tcgen05 kernel.
+
+    2-D or batched 3-D bf16 operands with unit inner stride.  ``trans_a=False``: ``a`` is
+    [M, K]; True: ``a`` is [K, M] (A = a^T).  ``trans_b=True`` (default, "NT"): ``b`` is
+    [N, K] (B = b^T); False: ``b`` is [K, N].
+    """
+    _bf16(a, "a"); _bf16(b, "b")
+    batched = a.dim() == 3
+    if batched:
+        G = a.shape[0]
+        a2, b2 = a[0], b[0]
+        sa, sb = a.stride(0), b.stride(0)
+    else:
+        G, a2, b2, sa, sb = 1, a, b, 0, 0
+    _row_major_2d(a2, "a"); _row_major_2d(b2, "b")
+    if trans_a:
+        K, M = a2.shape
+    else:
+        M, K = a2.shape
+    if trans_b:
+        N, Kb = b2.shape
+    else:
+        Kb, N = b2.shape
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: {K} vs {Kb}")
+    f32_out = epi in (EPI_ATOMIC_F32, EPI_STORE_F32)
+    if out is None:
+        shape = (G, M, N) if batched else (M, N)
+        if epi == EPI_ATOMIC_F32:
+            raise ValueError("EPI_ATOMIC_F32 accumulates into an existing tensor: pass out=")
+        out = torch.empty(shape, dtype=torch.float32 if f32_out else torch.bfloat16, device=a.device)
+    o2 = out[0] if batched else out
+    _row_major_2d(o2, "out")
+    if tuple(o2.shape) != (M, N) or out.dtype != (torch.float32 if f32_out else torch.bfloat16):
+        raise ValueError("out has the wrong shape or dtype")
+    so = out.stride(0) if batched else 0
+    auxp = 0
+    if aux is not None:
+        _bf16(aux, "aux")
+        ax2 = aux[0] if batched else aux
+        if ax2.stride(0) != o2.stride(0) or tuple(ax2.shape) != (M, N) or (batched and aux.stride(0) != so):
+            raise ValueError("aux must have the layout of out")
+        auxp = aux.data_ptr()
+    rc = lib().arb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), auxp, M, N, K, G,
+                             a2.stride(0), b2.stride(0), o2.stride(0), sa, sb, so,
+                             int(trans_a), int(not trans_b), epi, splitk, alpha, beta, gamma,
+                             err_flag(a.device).data_ptr(), _stream())
+    _check(rc, "arb_gemm_bf16")
+    return out
+
+
+def rmsnorm_fwd(x, eps):
+    _bf16(x, "x")
+    y = torch.empty_like(x)
+    _check(lib().arb_rmsnorm_fwd(x.data_ptr(), y.data_ptr(), x.numel() // x.shape[-1], x.shape[-1], eps, _stream()), "rmsnorm_fwd")
+    return y
+
+
+def rmsnorm_bwd(x, g, eps, add_to=None):
+    gx = torch.empty_like(x)
+    _check(lib().arb_rmsnorm_bwd(x.data_ptr(), g.data_ptr(), add_to.data_ptr() if add_to is not None else 0,
+                                 gx.data_ptr(), x.numel() // x.shape[-1], x.shape[-1], eps, _stream()), "rmsnorm_bwd")
+    return gx
+
+
+def resid_scale_norm_fwd(x, x0, lam_r, lam_0, idx, eps):
+    xo, xn = torch.empty_like(x), torch.empty_like(x)
+    _check(lib().arb_resid_scale_norm_fwd(x.data_ptr(), x0.data_ptr(), lam_r.data_ptr(), lam_0.data_ptr(), idx,
+                                          xo.data_ptr(), xn.data_ptr(), x.shape[0], x.shape[1], eps, _stream()),
+           "resid_scale_norm_fwd")
+    return xo, xn
+
+
+def resid_scale_norm_bwd(x, x0, lam_r, lam_0, idx, g_xs, g_xn, dlam_r, dlam_0, eps):
+    dx, dx0 = torch.empty_like(x), torch.empty_like(x)
+    _check(lib().arb_resid_scale_norm_bwd(x.data_ptr(), x0.data_ptr(), lam_r.data_ptr(), lam_0.data_ptr(), idx,
+                                          g_xs.data_ptr(), g_xn.data_ptr(), dx.data_ptr(), dx0.data_ptr(),
+                                          dlam_r.data_ptr(), dlam_0.data_ptr(), x.shape[0], x.shape[1], eps, _stream()),
+           "resid_scale_norm_bwd")
+    return dx, dx0
+
+
+def add_norm_fwd(x, proj, eps):
+    xo, xn = torch.empty_like(x), torch.empty_like(x)
+    _check(lib().arb_add_norm_fwd(x.data_ptr(), proj.data_ptr(), xo.data_ptr(), xn.data_ptr(), x.shape[0], x.shape[1],
+                                  eps, _stream()), "add_norm_fwd")
+    return xo, xn
+
+
+def residual_add(a, b):
+    o = torch.empty_like(a)
+    _check(lib().arb_residual_add(a.data_ptr(), b.data_ptr(), o.data_ptr(), a.numel(), _stream()), "residual_add")
+    return o
+
+
+def relu_sq_fwd(x):
+    y = torch.empty_like(x)
+    _check(lib().arb_relu_sq_fwd(x.data_ptr(), y.data_ptr(), x.numel(), _stream()), "relu_sq_fwd")
+    return y
+
+
+def relu_sq_bwd(x, g):
+    o = torch.empty_like(x)
+    _check(lib().arb_relu_sq_bwd(x.data_ptr(), g.data_ptr(), o.data_ptr(), x.numel(), _stream()), "relu_sq_bwd")
+    return o
+
+
+def embedding_fwd(ids, w):
+    out = torch.empty(ids.numel(), w.shape[1], dtype=w.dtype, device=w.device)
+    _check(lib().arb_embedding_fwd(ids.data_ptr(), w.data_ptr(), out.data_ptr(), ids.numel(), w.shape[1], w.shape[0],
+                                   _stream()), "embedding_fwd")
+    return out
+
+
+def embedding_bwd(ids, g, dw_f32):
+    _check(lib().arb_embedding_bwd(ids.data_ptr(), g.data_ptr(), dw_f32.data_ptr(), ids.numel(), g.shape[-1],
+                                   dw_f32.shape[0], _stream()), "embedding_bwd")
+
+
+def softcap_ce_(logits, targets, softcap, dlogits_scale):
+    """Returns per-row losses; overwrites logits with their gradient when dlogits_scale != 0."""
+    loss = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+    _check(lib().arb_softcap_ce(logits.data_ptr(), logits.stride(0), targets.data_ptr(), loss.data_ptr(),
+                                logits.shape[0], logits.shape[1], softcap, dlogits_scale, _stream()), "softcap_ce")
+    return loss
+
+
+def cast_f32_to_bf16(src, dst, scale=1.0):
+    _check(lib().arb_cast_f32_to_bf16(src.data_ptr(), dst.data_ptr(), src.numel(), scale, _stream()), "cast_f32_to_bf16")
+
+
+def accum_bf16_into_f32(src, dst):
+    _check(lib().arb_accum_bf16_into_f32(src.data_ptr(), dst.data_ptr(), src.numel(), _stream()), "accum_bf16_into_f32")
+
+
+def add_cols_(dst, src):
+    """dst[:, :src.shape[1]] += src (dst may be wider)."""
+    _check(lib().arb_add_cols(dst.data_ptr(), dst.stride(0), src.data_ptr(), src.shape[0], src.shape[1], _stream()), "add_cols")

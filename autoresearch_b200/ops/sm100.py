@@ -1,0 +1,442 @@
+"""sm_100a backend: autograd Functions over the hand-written kernels.
+
+Granularity follows what fuses well on a B200 rather than the reference's op list
+(brain/src/forward.rs:359-739, brain/src/backward.rs:203-877):
+
+* ``AttnPreFn``   – QKV GEMM (packed [3D, D] weight) + in-place RoPE / QK-norm / value
+                    embedding on the packed output; backward runs the norm/RoPE backward in
+                    place on the packed gradient, one K=3D dX GEMM and one dW GEMM (no
+                    pack / split copies, no recomputed q/k GEMMs).
+* ``AttentionFn`` – flash attention reading q, k, v as column blocks of the packed buffer.
+* ``LinearAddFn`` – O-proj / FC2 GEMM with the residual add in the epilogue.
+* ``MLPFn``       – FC1 GEMM with ReLU^2 epilogue (only relu(h)^2 is kept: the backward
+                    recovers 2*relu(h) as 2*sqrt of it inside the dX GEMM epilogue).
+* ``LMHeadCEFn``  – chunked LM head + soft-capped CE; logits are turned into their
+                    gradient in place during the forward so nothing is recomputed.
+* weight gradients accumulate in fp32 (``param.main_grad``) inside the dW GEMM epilogue.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import kernels as K
+from . import reference as R
+from .backend import OracleBackend
+
+
+def _main_grad(p: torch.Tensor) -> Optional[torch.Tensor]:
+    return getattr(p, "main_grad", None)
+
+
+def _acc_weight_grad(w, dy, x):
+    """main_grad(w) += dy^T @ x.  Returns None when accumulated in place, else the grad."""
+    mg = _main_grad(w)
+    if mg is not None:
+        K.gemm(dy, x, trans_a=True, trans_b=False, out=mg, epi=K.EPI_ATOMIC_F32)
+        return None
+    tmp = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+    K.gemm(dy, x, trans_a=True, trans_b=False, out=tmp, epi=K.EPI_ATOMIC_F32)
+    return tmp.to(w.dtype)
+
+
+class LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return K.gemm(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = K.gemm(dy, w, trans_b=False) if ctx.needs_input_grad[0] else None
+        dw = _acc_weight_grad(w, dy, x)
+        return dx, dw
+
+
+class LinearAddFn(torch.autograd.Function):
+    """out = resid + a @ w^T (residual add in the GEMM epilogue)."""
+
+    @staticmethod
+    def forward(ctx, a, w, resid):
+        ctx.save_for_backward(a, w)
+        return K.gemm(a, w, epi=K.EPI_ADD_AUX, aux=resid)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, w = ctx.saved_tensors
+        g = g.contiguous()
+        da = K.gemm(g, w, trans_b=False)
+        dw = _acc_weight_grad(w, g, a)
+        return da, dw, g
+
+
+class MLPFn(torch.autograd.Function):
+    """out = resid + relu(xn @ wfc^T)^2 @ wdn^T."""
+
+    @staticmethod
+    def forward(ctx, xn, wfc, wdn, resid):
+        act = K.gemm(xn, wfc, epi=K.EPI_RELU2)
+        out = K.gemm(act, wdn, epi=K.EPI_ADD_AUX, aux=resid)
+        ctx.save_for_backward(xn, wfc, wdn, act)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        xn, wfc, wdn, act = ctx.saved_tensors
+        g = g.contiguous()
+        dh = K.gemm(g, wdn, trans_b=False, epi=K.EPI_RELU2_BWD, aux=act)
+        dwdn = _acc_weight_grad(wdn, g, act)
+        dwfc = _acc_weight_grad(wfc, dh, xn)
+        dxn = K.gemm(dh, wfc, trans_b=False)
+        return dxn, dwfc, dwdn, g
+
+
+class RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, eps):
+        ctx.save_for_backward(x)
+        ctx.eps = eps
+        return K.rmsnorm_fwd(x, eps)
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        return K.rmsnorm_bwd(x, g.contiguous(), ctx.eps), None
+
+
+class LinearAddNormFn(torch.autograd.Function):
+    """xs = resid + a @ w^T (add in the GEMM epilogue); xn = rmsnorm(xs).  The backward fuses
+    the sum of the two incoming gradients into the norm backward."""
+
+    @staticmethod
+    def forward(ctx, a, w, resid, eps):
+        xs = K.gemm(a, w, epi=K.EPI_ADD_AUX, aux=resid)
+        xn = K.rmsnorm_fwd(xs, eps)
+        ctx.save_for_backward(a, w, xs)
+        ctx.eps = eps
+        return xs, xn
+
+    @staticmethod
+    def backward(ctx, g_xs, g_xn):
+        a, w, xs = ctx.saved_tensors
+        if g_xn is None:
+            g = g_xs.contiguous()
+        else:
+            add = g_xs.contiguous() if g_xs is not None else None
+            g = K.rmsnorm_bwd(xs, g_xn.contiguous(), ctx.eps, add_to=add)
+        da = K.gemm(g, w, trans_b=False)
+        dw = _acc_weight_grad(w, g, a)
+        return da, dw, g, None
+
+
+class ResidScaleNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, x0, lam_r, lam_0, idx, eps):
+        ctx.save_for_backward(x, x0, lam_r, lam_0)
+        ctx.idx, ctx.eps = idx, eps
+        xs, xn = K.resid_scale_norm_fwd(x, x0, lam_r, lam_0, idx, eps)
+        return xs, xn
+
+    @staticmethod
+    def backward(ctx, g_xs, g_xn):
+        x, x0, lam_r, lam_0 = ctx.saved_tensors
+        if g_xs is None:
+            g_xs = torch.zeros_like(x)
+        if g_xn is None:
+            g_xn = torch.zeros_like(x)
+        mr, m0 = _main_grad(lam_r), _main_grad(lam_0)
+        dr = mr if mr is not None else torch.zeros(lam_r.shape, dtype=torch.float32, device=x.device)
+        d0 = m0 if m0 is not None else torch.zeros(lam_0.shape, dtype=torch.float32, device=x.device)
+        dx, dx0 = K.resid_scale_norm_bwd(x, x0, lam_r, lam_0, ctx.idx, g_xs.contiguous(), g_xn.contiguous(),
+                                         dr, d0, ctx.eps)
+        return (dx, dx0, None if mr is not None else dr.to(lam_r.dtype),
+                None if m0 is not None else d0.to(lam_0.dtype), None, None)
+
+
+class EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, w):
+        ctx.save_for_backward(ids, w)
+        return K.embedding_fwd(ids, w)
+
+    @staticmethod
+    def backward(ctx, g):
+        ids, w = ctx.saved_tensors
+        mg = _main_grad(w)
+        if mg is not None:
+            K.embedding_bwd(ids, g.contiguous(), mg)
+            return None, None
+        tmp = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        K.embedding_bwd(ids, g.contiguous(), tmp)
+        return None, tmp.to(w.dtype)
+
+
+class AttnPreFn(torch.autograd.Function):
+    """packed qkv = post(xn @ wqkv^T): RoPE + QK-norm on q, k; value embedding on v."""
+
+    @staticmethod
+    def forward(ctx, xn, wqkv, ids, ve_w, gate_w, cos, sin, T, H, gate_ch, eps):
+        N, D = xn.shape
+        qkv = K.gemm(xn, wqkv)
+        rstd = torch.empty(N, 2 * H, dtype=torch.float32, device=xn.device)
+        gate = torch.empty(N, H, dtype=torch.float32, device=xn.device) if ve_w is not None else None
+        rc = K.lib().arb_qkv_post_fwd(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), rstd.data_ptr(),
+                                      xn.data_ptr(), ids.data_ptr(),
+                                      ve_w.data_ptr() if ve_w is not None else 0,
+                                      gate_w.data_ptr() if ve_w is not None else 0,
+                                      gate.data_ptr() if ve_w is not None else 0,
+                                      N, T, H, D, gate_ch, eps, K._stream())
+        K._check(rc, "qkv_post_fwd")
+        ctx.save_for_backward(xn, wqkv, ids, ve_w, gate_w, cos, sin, qkv, rstd, gate)
+        ctx.dims = (T, H, gate_ch)
+        ctx.mark_non_differentiable(rstd)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, d_qkv):
+        xn, wqkv, ids, ve_w, gate_w, cos, sin, qkv, rstd, gate = ctx.saved_tensors
+        T, H, gate_ch = ctx.dims
+        N, D = xn.shape
+        d_qkv = d_qkv.contiguous()
+        has_ve = ve_w is not None
+        d_ve = d_xn_gate = dgl = None
+        dgw = None
+        if has_ve:
+            d_ve = torch.empty(N, H * 128, dtype=torch.bfloat16, device=xn.device)
+            d_xn_gate = torch.empty(N, gate_ch, dtype=torch.bfloat16, device=xn.device)
+            dgl = torch.empty(N, H, dtype=torch.float32, device=xn.device)
+            mg = _main_grad(gate_w)
+            dgw = mg if mg is not None else torch.zeros(gate_w.shape, dtype=torch.float32, device=xn.device)
+        rc = K.lib().arb_qkv_post_bwd(d_qkv.data_ptr(), qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), rstd.data_ptr(),
+                                      xn.data_ptr(), ids.data_ptr(),
+                                      ve_w.data_ptr() if has_ve else 0, gate_w.data_ptr() if has_ve else 0,
+                                      gate.data_ptr() if has_ve else 0, d_ve.data_ptr() if has_ve else 0,
+                                      dgw.data_ptr() if has_ve else 0, d_xn_gate.data_ptr() if has_ve else 0,
+                                      dgl.data_ptr() if has_ve else 0, N, T, H, D, gate_ch, K._stream())
+        K._check(rc, "qkv_post_bwd")
+        dw = _acc_weight_grad(wqkv, d_qkv, xn)
+        dxn = K.gemm(d_qkv, wqkv, trans_b=False)
+        g_ve = g_gate = None
+        if has_ve:
+            K.add_cols_(dxn, d_xn_gate)
+            mgv = _main_grad(ve_w)
+            if mgv is not None:
+                K.embedding_bwd(ids, d_ve, mgv)
+            else:
+                tmp = torch.zeros(ve_w.shape, dtype=torch.float32, device=xn.device)
+                K.embedding_bwd(ids, d_ve, tmp)
+                g_ve = tmp.to(ve_w.dtype)
+            if _main_grad(gate_w) is None:
+                g_gate = dgw.to(gate_w.dtype)
+        return dxn, dw, None, g_ve, g_gate, None, None, None, None, None, None
+
+
+class AttentionFn(torch.autograd.Function):
+    """Flash attention over the packed qkv buffer [N, 3*H*128] -> [N, H*128]."""
+
+    @staticmethod
+    def forward(ctx, qkv, B, T, H, window):
+        N = B * T
+        Dl = H * 128
+        out = torch.empty(N, Dl, dtype=torch.bfloat16, device=qkv.device)
+        lse = torch.empty(B, H, T, dtype=torch.float32, device=qkv.device)
+        ld = qkv.stride(0)
+        base = qkv.data_ptr()
+        scale = 1.0 / math.sqrt(128.0)
+        rc = K.lib().arb_attn_fwd(base, base + 2 * Dl, base + 4 * Dl, out.data_ptr(), lse.data_ptr(), B, T, H,
+                                  ld, ld, ld, Dl, window, scale, K.err_flag(qkv.device).data_ptr(), K._stream())
+        K._check(rc, "attn_fwd")
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.dims = (B, T, H, window)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        qkv, out, lse = ctx.saved_tensors
+        B, T, H, window = ctx.dims
+        N, Dl = B * T, H * 128
+        d_out = d_out.contiguous()
+        d_qkv = torch.empty_like(qkv)
+        delta = torch.empty(B, H, T, dtype=torch.float32, device=qkv.device)
+        dq_acc = torch.zeros(N, Dl, dtype=torch.float32, device=qkv.device)
+        ld = qkv.stride(0)
+        b, db = qkv.data_ptr(), d_qkv.data_ptr()
+        rc = K.lib().arb_attn_bwd(b, b + 2 * Dl, b + 4 * Dl, out.data_ptr(), d_out.data_ptr(), lse.data_ptr(),
+                                  db, db + 2 * Dl, db + 4 * Dl, delta.data_ptr(), dq_acc.data_ptr(), B, T, H,
+                                  ld, ld, ld, Dl, Dl, ld, ld, ld, window, 1.0 / math.sqrt(128.0),
+                                  K.err_flag(qkv.device).data_ptr(), K._stream())
+        K._check(rc, "attn_bwd")
+        return d_qkv, None, None, None, None
+
+
+class LibraryAttentionFn(torch.autograd.Function):
+    """Library attention (flash-attn) on the packed buffer: the comparison arm."""
+
+    @staticmethod
+    def forward(ctx, qkv, B, T, H, window):
+        from flash_attn import flash_attn_func
+        Dl = H * 128
+        with torch.enable_grad():
+            src = qkv.detach().requires_grad_(True)
+            q = src[:, :Dl].view(B, T, H, 128)
+            k = src[:, Dl:2 * Dl].view(B, T, H, 128)
+            v = src[:, 2 * Dl:].view(B, T, H, 128)
+            ws = (window, 0) if window < T else (-1, -1)
+            o = flash_attn_func(q, k, v, causal=True, window_size=ws)
+        ctx.src, ctx.o = src, o
+        return o.detach().reshape(B * T, Dl)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        (g,) = torch.autograd.grad(ctx.o, ctx.src, d_out.view_as(ctx.o))
+        ctx.src = ctx.o = None
+        return g, None, None, None, None
+
+
+class LMHeadCEFn(torch.autograd.Function):
+    """sum_t loss_t * grad_scale, with d_xf and dW produced during the forward."""
+
+    @staticmethod
+    def forward(ctx, xf, w, targets, softcap, grad_scale, chunk, need_grad):
+        N, D = xf.shape
+        per_tok = torch.empty(N, dtype=torch.float32, device=xf.device)
+        d_xf = torch.empty_like(xf) if need_grad else None
+        mg = _main_grad(w)
+        dw_tmp = None
+        if need_grad and mg is None:
+            dw_tmp = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        acc = mg if mg is not None else dw_tmp
+        for a in range(0, N, chunk):
+            b = min(N, a + chunk)
+            logits = K.gemm(xf[a:b], w)
+            per_tok[a:b] = K.softcap_ce_(logits, targets[a:b], softcap, grad_scale if need_grad else 0.0)
+            if need_grad:
+                K.gemm(logits, w, trans_b=False, out=d_xf[a:b])
+                K.gemm(logits, xf[a:b], trans_a=True, trans_b=False, out=acc, epi=K.EPI_ATOMIC_F32)
+        ctx.d_xf = d_xf
+        ctx.dw = dw_tmp.to(w.dtype) if dw_tmp is not None else None
+        ctx.mark_non_differentiable(per_tok)
+        return per_tok.sum() * grad_scale, per_tok
+
+    @staticmethod
+    def backward(ctx, g_loss, _g_per_tok):
+        # Contract: the caller back-propagates the returned scalar with gradient 1 (the scale
+        # is already folded into d_xf and dW).
+        d_xf, dw = ctx.d_xf, ctx.dw
+        ctx.d_xf = ctx.dw = None
+        return d_xf, dw, None, None, None, None, None
+
+
+# ----------------------------------------------------------------------------------------------
+class OptimKernels:
+    """Fused optimizer steps for MuonAdamW (same math as optim.muon_adamw's reference)."""
+
+    MIN_GEMM_DIM = 64
+
+    def adamw_group(self, st, grad, pv, step, lr, b1, b2, eps, wd):
+        n = grad.numel()
+        bc1, bc2 = 1.0 - b1 ** step, 1.0 - b2 ** step
+        g = grad if grad.dtype == torch.float32 else grad.float()
+        shadow = pv if pv.dtype == torch.bfloat16 else None
+        K._check(K.lib().arb_adamw(st["master"].data_ptr(), g.data_ptr(), st["m"].data_ptr(), st["v"].data_ptr(),
+                                   shadow.data_ptr() if shadow is not None else 0, n, lr, b1, b2, eps, wd, bc1, bc2,
+                                   K._stream()), "adamw")
+        if shadow is None:
+            pv.copy_(st["master"])
+
+    def muon_group(self, st, grad, pv, mu, lr, wd, beta2, ns_steps):
+        from ..optim import muon_adamw as MA
+        G, m, n = grad.shape
+        if min(m, n) < self.MIN_GEMM_DIM or pv.dtype != torch.bfloat16 or (m % 8) or (n % 8):
+            u = MA.muon_nesterov(st["momentum"], grad.float(), mu, torch.bfloat16)
+            x = MA.newton_schulz(MA.frob_normalise(u), ns_steps)
+            gfin = MA.normuon(x, st["second"], beta2)
+            MA.cautious_update(st["master"], gfin, lr, wd)
+            pv.copy_(st["master"])
+            return
+        dev = grad.device
+        L = K.lib()
+        s = K._stream()
+        x = torch.empty(G, m, n, dtype=torch.bfloat16, device=dev)
+        sumsq = torch.empty(G, dtype=torch.float32, device=dev)
+        K._check(L.arb_muon_nesterov(st["momentum"].data_ptr(), grad.data_ptr(), x.data_ptr(), sumsq.data_ptr(),
+                                     m * n, G, mu, s), "muon_nesterov")
+        K._check(L.arb_muon_frob_scale(x.data_ptr(), sumsq.data_ptr(), m * n, G, s), "muon_frob_scale")
+        tall = m > n
+        d = n if tall else m
+        A = torch.empty(G, d, d, dtype=torch.bfloat16, device=dev)
+        Cm = torch.empty(G, d, d, dtype=torch.bfloat16, device=dev)
+        x2 = torch.empty_like(x)
+        for a, b, c in MA.POLAR_EXPRESS[:ns_steps]:
+            if tall:
+                K.gemm(x, x, trans_a=True, trans_b=False, out=A)          # X^T X
+            else:
+                K.gemm(x, x, out=A)                                        # X X^T
+            K.gemm(A, A, out=Cm, epi=K.EPI_NS_COMBINE, aux=A, alpha=a, beta=b, gamma=c)
+            if tall:
+                K.gemm(x, Cm, out=x2)                                      # X C  (C symmetric)
+            else:
+                K.gemm(Cm, x, trans_b=False, out=x2)                       # C X
+            x, x2 = x2, x
+        n_stat = m if m >= n else n
+        red = n if m >= n else m
+        vmean = torch.empty(G, n_stat, dtype=torch.float32, device=dev)
+        scale = torch.empty(G, n_stat, dtype=torch.float32, device=dev)
+        K._check(L.arb_normuon_stats(x.data_ptr(), vmean.data_ptr(), G, m, n, s), "normuon_stats")
+        K._check(L.arb_normuon_scales(vmean.data_ptr(), st["second"].data_ptr(), scale.data_ptr(), G, n_stat, red,
+                                      beta2, s), "normuon_scales")
+        K._check(L.arb_muon_update(st["master"].data_ptr(), pv.data_ptr(), x.data_ptr(), scale.data_ptr(), G, m, n,
+                                   lr, wd, s), "muon_update")
+
+
+# ----------------------------------------------------------------------------------------------
+class Sm100Backend(OracleBackend):
+    name = "sm100"
+
+    def __init__(self, attn: str = "own", **kw):
+        super().__init__(**kw)
+        if not torch.cuda.is_available():
+            raise RuntimeError("the sm100 backend needs a CUDA device")
+        K.lib()  # fail loudly when the native library is missing
+        self.attn = attn
+        self.big_ce_chunk = 16384
+
+    def optim_kernels(self):
+        return OptimKernels()
+
+    def embedding(self, ids, w):
+        return EmbeddingFn.apply(ids.contiguous(), w)
+
+    def rmsnorm(self, x):
+        return RMSNormFn.apply(x.contiguous(), self.eps)
+
+    def resid_scale_norm(self, x, x0, lam_r, lam_0, i):
+        return ResidScaleNormFn.apply(x.contiguous(), x0.contiguous(), lam_r, lam_0, i, self.eps)
+
+    def linear_col(self, x, w):
+        return LinearFn.apply(x, w)
+
+    linear_row = linear_col
+
+    def attention_block(self, xn, blk, ids_flat, B, T, cfg, cos, sin, window):
+        H = blk.wqkv.shape[0] // (3 * cfg.head_dim)
+        if cfg.head_dim != 128:
+            raise ValueError("the sm100 kernels support head_dim = 128 only")
+        qkv = AttnPreFn.apply(xn, blk.wqkv, ids_flat, blk.ve, blk.ve_gate, cos, sin, T, H, cfg.ve_gate_ch, self.eps)
+        fn = AttentionFn if self.attn == "own" else LibraryAttentionFn
+        return fn.apply(qkv, B, T, H, window)
+
+    def proj_add_norm(self, a, w, x):
+        return LinearAddNormFn.apply(a, w, x, self.eps)
+
+    def mlp_add(self, xn, wfc, wdn, x):
+        return MLPFn.apply(xn, wfc, wdn, x)
+
+    def lm_head_ce(self, xf, w, targets, grad_scale):
+        need = torch.is_grad_enabled() and (xf.requires_grad or w.requires_grad)
+        chunk = max(self.ce_chunk, self.big_ce_chunk)
+        return LMHeadCEFn.apply(xf, w, targets.contiguous(), self.softcap, grad_scale, chunk, need)

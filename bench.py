@@ -1,0 +1,145 @@
+"""Headline benchmark: training tokens/s of the 428 M GPT (D=1024, L=30, T=32768, 524 288
+tokens per optimizer step) on N B200s of one node, device-timed, max over ranks.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torchrun)
+    python bench.py --impl reference ...                     (the reference arm)
+
+Prints ONE JSON line on rank 0.  ``value`` is timed with CUDA events around exactly K
+optimizer steps (each step stages its inputs from pinned host memory); ``e2e`` repeats the
+K steps through the public ``Trainer.train_step`` API with a wall clock and a device->host
+read of the loss every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+BASELINE_TOK_S = 52643.0  # reference, 1x H100 SXM, results/480m_30pct_cooldown/train.log
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="sm100", choices=["sm100", "baseline", "reference"])
+    ap.add_argument("--model", default="phase2")
+    ap.add_argument("--attn", default=None, choices=[None, "own", "library"])
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--micro-batch", type=int, default=4)
+    ap.add_argument("--total-batch", type=int, default=524288)
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: marks the result invalid")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust crate (no setup.py/pyproject at its root, pip refuses it; "
+                          "no cargo/rustc in the image) linking a Hopper-only (sm_90a) FlashAttention-3 "
+                          "build that needs a network clone"}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    from autoresearch_b200.config import ParallelConfig, ScheduleConfig, TrainConfig, model_preset
+    from autoresearch_b200.ops import kernels as K
+    from autoresearch_b200.trainer import Trainer
+    from autoresearch_b200.utils.clocks import ClockSampler
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(f"bench.py --gpus {args.gpus} must be launched by torch.distributed.run", file=sys.stderr)
+            return 2
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    over = {}
+    if args.seq_len:
+        over["seq_len"] = args.seq_len
+    if args.layers:
+        over["n_layer"] = args.layers
+    mcfg = model_preset(args.model, **over)
+    sched = ScheduleConfig(peak_lr=0.02, weight_decay=0.3, final_lr_frac=0.02,
+                           embedding_lr=0.45, unembedding_lr=0.0025, scalar_lr=0.25)
+    tcfg = TrainConfig(device_batch_size=args.micro_batch, total_batch_size=args.total_batch,
+                       max_steps=1000, cooldown_steps=300, synthetic_data=True, synthetic_kind="zipf",
+                       impl=args.impl, schedule_cfg=sched, cooldown_trigger_file="",
+                       parallel=ParallelConfig(dp=world, comm=args.comm))
+    tr = Trainer(mcfg, tcfg, device=f"cuda:{local}", quiet=True)
+    if args.attn and hasattr(tr.backend, "attn"):
+        tr.backend.attn = args.attn
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        tr.train_step()
+    sync()
+    # ---- device-timed region ---------------------------------------------------------------
+    sampler = ClockSampler(local).start()
+    n0 = K.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = tr.train_step()
+    e1.record()
+    sync()
+    launches = K.launch_count - n0
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    # ---- end-to-end region (public API, loss read back every step) ------------------------------
+    sync()
+    t0 = time.perf_counter()
+    last = None
+    for _ in range(args.steps):
+        last = float(tr.train_step().item())
+    sync()
+    e2e_s = time.perf_counter() - t0
+    K.check_err_flag()
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0].item()), float(t[1].item())
+    tokens_step = tr.micro_batch * mcfg.seq_len * tr.accum * world
+    value = tokens_step * args.steps / (ms / 1e3)
+    e2e = tokens_step * args.steps / e2e_s
+    valid = args.layers is None and args.seq_len is None and args.model == "phase2" and args.total_batch == 524288
+    out = {
+        "metric": "train tokens/sec, 428M D1024 L30 T32K (device-timed, max/rank)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 2), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": (round(value / BASELINE_TOK_S, 3) if world == 1 and valid else None),
+        "dtype": "bf16", "data": "synthetic Zipf(1.1) token ids from a seed; random-init weights",
+        "impl": args.impl,
+        "config": {"model": f"{mcfg.name} {mcfg.num_params()['total'] / 1e6:.1f}M D{mcfg.d_model} L{mcfg.n_layer} T{mcfg.seq_len}",
+                   "global_batch": tokens_step, "seq_len": mcfg.seq_len,
+                   "micro_batch_per_gpu": tr.micro_batch, "grad_accum": tr.accum,
+                   "parallelism": f"dp{world}", "comm": tr.comm.name,
+                   "attention": getattr(tr.backend, "attn", "library"),
+                   "l2": "inputs larger than L2 (per-step working set of tens of GB)",
+                   "valid_headline_config": valid},
+        "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": tr.h2d_bytes_per_step,
+                "d2h_bytes_per_step": 4, "last_loss": last},
+        "gpu_launches": launches,
+        "mfu_vs_measured_peak": round(mcfg.flops_per_token() * value / (tr.peak_flops * world), 4),
+    }
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

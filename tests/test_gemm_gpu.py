@@ -1,0 +1,109 @@
+"""tcgen05 GEMM against a plain fp32 PyTorch matmul of the same bf16 operands."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _close(out, ref, tol=2e-2):
+    err = (out.float() - ref).abs().max().item()
+    den = ref.abs().max().item() + 1e-6
+    assert err / den < tol, f"rel err {err / den:.4g}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 128, 192), (200, 328, 136),
+                                   (1024, 1024, 1024), (129, 72, 520)])
+def test_nt(M, N, K):
+    from autoresearch_b200.ops import kernels as K_
+    torch.manual_seed(0)
+    a, b = _rand(M, K), _rand(N, K)
+    out = K_.gemm(a, b)
+    _close(out, a.float() @ b.float().t())
+    K_.check_err_flag()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (200, 328, 136), (512, 1024, 768)])
+def test_nn(M, N, K):
+    from autoresearch_b200.ops import kernels as K_
+    torch.manual_seed(1)
+    a, b = _rand(M, K), _rand(K, N)
+    out = K_.gemm(a, b, trans_b=False)
+    _close(out, a.float() @ b.float())
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (264, 136, 1000), (1024, 512, 4096)])
+def test_tn_atomic_accumulate(M, N, K):
+    from autoresearch_b200.ops import kernels as K_
+    torch.manual_seed(2)
+    a, b = _rand(K, M), _rand(K, N)
+    acc = torch.randn(M, N, device="cuda")
+    ref = acc.clone() + a.float().t() @ b.float()
+    K_.gemm(a, b, trans_a=True, trans_b=False, out=acc, epi=K_.EPI_ATOMIC_F32)
+    _close(acc, ref, 1e-2)
+    # explicit split-K
+    acc2 = torch.zeros(M, N, device="cuda")
+    K_.gemm(a, b, trans_a=True, trans_b=False, out=acc2, epi=K_.EPI_ATOMIC_F32, splitk=3)
+    _close(acc2, a.float().t() @ b.float(), 1e-2)
+
+
+def test_tn_nt_mixed_and_f32_store():
+    from autoresearch_b200.ops import kernels as K_
+    torch.manual_seed(3)
+    a, b = _rand(320, 192), _rand(256, 320)      # A = a^T [192, 320], B = b^T
+    out = K_.gemm(a, b, trans_a=True, trans_b=True, epi=K_.EPI_STORE_F32)
+    _close(out, a.float().t() @ b.float().t(), 1e-2)
+
+
+def test_epilogues():
+    from autoresearch_b200.ops import kernels as K_
+    torch.manual_seed(4)
+    M, N, Kd = 256, 384, 128
+    a, b = _rand(M, Kd, scale=0.3), _rand(N, Kd, scale=0.3)
+    ref = a.float() @ b.float().t()
+    _close(K_.gemm(a, b, epi=K_.EPI_RELU2), torch.relu(ref) ** 2)
+    aux = _rand(M, N)
+    _close(K_.gemm(a, b, epi=K_.EPI_ADD_AUX, aux=aux), ref + aux.float())
+    act = (torch.relu(aux.float()) ** 2).to(torch.bfloat16)
+    _close(K_.gemm(a, b, epi=K_.EPI_RELU2_BWD, aux=act), ref * 2 * torch.sqrt(act.float()))
+    sq = _rand(256, 256, scale=0.1)
+    got = K_.gemm(sq, sq, epi=K_.EPI_NS_COMBINE, aux=sq, alpha=1.5, beta=-2.0, gamma=0.5)
+    want = 1.5 * torch.eye(256, device="cuda") - 2.0 * sq.float() + 0.5 * (sq.float() @ sq.float().t())
+    _close(got, want)
+
+
+def test_batched():
+    from autoresearch_b200.ops import kernels as K_
+    torch.manual_seed(5)
+    G, m, n = 5, 256, 512
+    x = _rand(G, m, n, scale=0.2)
+    A = K_.gemm(x, x)                                        # X X^T
+    _close(A, x.float() @ x.float().transpose(1, 2))
+    At = K_.gemm(x, x, trans_a=True, trans_b=False)          # X^T X
+    _close(At, x.float().transpose(1, 2) @ x.float())
+    y = K_.gemm(A, x, trans_b=False)                         # A X
+    _close(y, A.float() @ x.float())
+
+
+def test_strided_views():
+    """Operands that are column blocks of a wider buffer (packed qkv) and row slices."""
+    from autoresearch_b200.ops import kernels as K_
+    torch.manual_seed(6)
+    big = _rand(512, 768)
+    w = _rand(256, 256)
+    a = big[:, 256:512]
+    _close(K_.gemm(a, w), a.float() @ w.float().t())
+    out = torch.zeros(512, 512, dtype=torch.bfloat16, device="cuda")
+    K_.gemm(a, w, out=out[:, 256:])
+    _close(out[:, 256:], a.float() @ w.float().t())
+    assert out[:, :256].abs().max().item() == 0
+
+
+def test_rejects_bad_arguments():
+    from autoresearch_b200.ops import kernels as K_
+    a, b = _rand(128, 60), _rand(128, 60)      # K not a multiple of 8
+    with pytest.raises(K_.KernelError):
+        K_.gemm(a, b)

@@ -1,0 +1,159 @@
+"""Fused elementwise / norm / CE / optimizer kernels against the PyTorch fp32 reference."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+EPS = 1e-5
+
+
+def _bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _close(a, b, tol=2e-2, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    den = b.abs().max().item() + 1e-6
+    assert err / den < tol, f"{what} rel err {err / den:.4g}"
+
+
+@pytest.mark.parametrize("rows,D", [(37, 256), (64, 512), (100, 1024), (9, 2048), (16, 136)])
+def test_rmsnorm_fwd_bwd(rows, D):
+    from autoresearch_b200.ops import kernels as K, reference as R
+    torch.manual_seed(0)
+    x, g = _bf(rows, D), _bf(rows, D)
+    _close(K.rmsnorm_fwd(x, EPS), R.rmsnorm(x.float(), EPS), what="fwd")
+    xf = x.float().requires_grad_(True)
+    R.rmsnorm(xf, EPS).backward(g.float())
+    _close(K.rmsnorm_bwd(x, g, EPS), xf.grad, what="bwd")
+    add = _bf(rows, D)
+    _close(K.rmsnorm_bwd(x, g, EPS, add_to=add), xf.grad + add.float(), what="bwd+add")
+
+
+def test_resid_scale_norm_fwd_bwd():
+    from autoresearch_b200.ops import kernels as K, reference as R
+    torch.manual_seed(1)
+    rows, D, L, idx = 50, 512, 4, 2
+    x, x0 = _bf(rows, D), _bf(rows, D)
+    lr = torch.tensor([1.0, 0.9, 1.1, 0.8], device="cuda").to(torch.bfloat16)
+    l0 = torch.tensor([0.1, 0.2, 0.3, 0.05], device="cuda").to(torch.bfloat16)
+    xs, xn = K.resid_scale_norm_fwd(x, x0, lr, l0, idx, EPS)
+    xf, x0f = x.float().requires_grad_(True), x0.float().requires_grad_(True)
+    lrf, l0f = lr.float().requires_grad_(True), l0.float().requires_grad_(True)
+    rs, rn = R.resid_scale_norm(xf, x0f, lrf[idx], l0f[idx], EPS)
+    _close(xs, rs, what="xs"); _close(xn, rn, what="xn")
+    g1, g2 = _bf(rows, D), _bf(rows, D)
+    (rs * g1.float()).sum().backward(retain_graph=True)
+    (rn * g2.float()).sum().backward()
+    dr = torch.zeros(L, device="cuda"); d0 = torch.zeros(L, device="cuda")
+    dx, dx0 = K.resid_scale_norm_bwd(x, x0, lr, l0, idx, g1, g2, dr, d0, EPS)
+    _close(dx, xf.grad, what="dx"); _close(dx0, x0f.grad, what="dx0")
+    _close(dr, lrf.grad, 3e-2, "dlam_r"); _close(d0, l0f.grad, 3e-2, "dlam_0")
+
+
+def test_add_norm_relu_residual_embedding():
+    from autoresearch_b200.ops import kernels as K, reference as R
+    torch.manual_seed(2)
+    x, p = _bf(33, 512), _bf(33, 512)
+    xs, xn = K.add_norm_fwd(x, p, EPS)
+    rs, rn = R.add_norm(x.float(), p.float(), EPS)
+    _close(xs, rs); _close(xn, rn)
+    _close(K.residual_add(x, p), x.float() + p.float())
+    _close(K.relu_sq_fwd(x), torch.relu(x.float()) ** 2)
+    _close(K.relu_sq_bwd(x, p), 2 * torch.relu(x.float()) * p.float())
+    w = _bf(100, 256)
+    ids = torch.randint(0, 100, (77,), device="cuda", dtype=torch.int32)
+    assert torch.equal(K.embedding_fwd(ids, w), w[ids.long()])
+    g = _bf(77, 256)
+    dw = torch.zeros(100, 256, device="cuda")
+    K.embedding_bwd(ids, g, dw)
+    ref = torch.zeros(100, 256, device="cuda").index_add_(0, ids.long(), g.float())
+    _close(dw, ref, 1e-3)
+
+
+@pytest.mark.parametrize("V", [1024, 8192, 264])
+def test_softcap_ce(V):
+    from autoresearch_b200.ops import kernels as K, reference as R
+    torch.manual_seed(3)
+    rows = 65
+    logits = _bf(rows, V, scale=6.0)
+    tgt = torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)
+    lf = logits.float().requires_grad_(True)
+    ref = R.softcap_ce(lf, tgt, 15.0)
+    (ref.sum() * 0.125).backward()
+    work = logits.clone()
+    loss = K.softcap_ce_(work, tgt, 15.0, 0.125)
+    _close(loss, ref, 1e-3, "loss")
+    _close(work, lf.grad, 2e-2, "dlogits")
+    keep = logits.clone()
+    loss2 = K.softcap_ce_(keep, tgt, 15.0, 0.0)
+    assert torch.equal(keep, logits)
+    _close(loss2, ref, 1e-3)
+
+
+def test_qkv_post_matches_reference():
+    from autoresearch_b200.ops import kernels as K, reference as R, sm100
+    torch.manual_seed(4)
+    B, T, H, D, V, ch = 2, 64, 2, 256, 50, 32
+    N = B * T
+    xn = _bf(N, D).requires_grad_(True)
+    w = _bf(3 * D, D, scale=0.05).requires_grad_(True)
+    ve = _bf(V, D, scale=0.5).requires_grad_(True)
+    gw = _bf(H, ch, scale=0.3).requires_grad_(True)
+    ids = torch.randint(0, V, (N,), device="cuda", dtype=torch.int32)
+    cos, sin = R.rope_tables(T, 128, 200000.0, device="cuda")
+    cos, sin = cos.to(torch.bfloat16), sin.to(torch.bfloat16)
+    qkv = sm100.AttnPreFn.apply(xn, w, ids, ve, gw, cos, sin, T, H, ch, EPS)
+    g = _bf(N, 3 * D)
+    qkv.backward(g.clone())
+    # reference
+    xr, wr, ver, gwr = (t.detach().float().requires_grad_(True) for t in (xn, w, ve, gw))
+    raw = xr @ wr.t()
+    q = R.rope_qknorm(raw[:, :D].reshape(B, T, H, 128), cos, sin, EPS)
+    k = R.rope_qknorm(raw[:, D:2 * D].reshape(B, T, H, 128), cos, sin, EPS)
+    gate = xr[:, :ch] @ gwr.t()
+    v = R.ve_apply(raw[:, 2 * D:].reshape(B, T, H, 128), ver[ids.long()].view(B, T, H, 128), gate.view(B, T, H))
+    ref = torch.cat([q.reshape(N, D), k.reshape(N, D), v.reshape(N, D)], 1)
+    _close(qkv, ref, 3e-2, "qkv")
+    ref.backward(g.float())
+    _close(xn.grad, xr.grad, 4e-2, "d_xn")
+    _close(w.grad, wr.grad, 4e-2, "d_w")
+    _close(ve.grad, ver.grad, 4e-2, "d_ve")
+    _close(gw.grad, gwr.grad, 5e-2, "d_gate_w")
+
+
+def test_adamw_and_muon_kernels_match_reference():
+    from autoresearch_b200.ops.sm100 import OptimKernels
+    from autoresearch_b200.optim import muon_adamw as MA
+    torch.manual_seed(5)
+    ok = OptimKernels()
+    n = 4096 + 24
+    p0 = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda") * 0.1
+    st = dict(master=p0.clone(), m=torch.zeros(n, device="cuda"), v=torch.zeros(n, device="cuda"))
+    pv = p0.to(torch.bfloat16)
+    rp, rm, rv = p0.clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    for step in (1, 2, 3):
+        ok.adamw_group(st, g, pv, step, 0.01, 0.8, 0.95, 1e-10, 0.01)
+        MA.adamw_update(rp, g, rm, rv, step, 0.01, 0.8, 0.95, 1e-10, 0.01)
+    _close(st["master"], rp, 1e-4, "adamw")
+    _close(pv, rp, 1e-2, "adamw shadow")
+    for (G, m, nn) in [(3, 256, 256), (2, 512, 128), (2, 128, 512)]:
+        master = torch.randn(G, m, nn, device="cuda") * 0.05
+        grad = torch.randn(G, m, nn, device="cuda") * 0.01
+        sshape = (G, m, 1) if m >= nn else (G, 1, nn)
+        st = dict(master=master.clone(), momentum=torch.zeros_like(master), second=torch.zeros(sshape, device="cuda"))
+        pv = master.to(torch.bfloat16)
+        rmaster, rmom, rsec = master.clone(), torch.zeros_like(master), torch.zeros(sshape, device="cuda")
+        for _ in range(2):
+            ok.muon_group(st, grad, pv, 0.9, 0.02, 0.1, 0.95, 5)
+            u = MA.muon_nesterov(rmom, grad, 0.9, torch.bfloat16)
+            x = MA.newton_schulz(MA.frob_normalise(u), 5)
+            MA.cautious_update(rmaster, MA.normuon(x, rsec, 0.95), 0.02, 0.1)
+        upd, rupd = st["master"] - master, rmaster - master
+        rel = (upd - rupd).norm() / rupd.norm()
+        assert rel < 0.05, f"muon update mismatch {rel:.4f} for {(G, m, nn)}"
+        _close(st["second"], rsec, 5e-2, "second moment")
