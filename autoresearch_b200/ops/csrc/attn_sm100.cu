@@ -1,0 +1,815 @@
+// Causal / sliding-window flash attention for head_dim = 128 on tcgen05 tensor cores with
+// TMEM accumulators.  Three kernels share one structure (TMA producer warp, single-thread MMA
+// issuer, four softmax/epilogue warps that own one TMEM lane = one row each):
+//
+//   attn_fwd_k   : per 128-query tile, loop over visible 128-key tiles:
+//                  S = Q K^T (TMEM, double buffered) -> online softmax in registers (exp2,
+//                  lazy rescale of O only when the row maximum grows by more than 2^8) ->
+//                  P (bf16, swizzled smem) -> O += P V (TMEM).
+//   attn_bwd_dq_k: per 128-query tile: S = Q K^T, dP = dO V^T -> dS = P o (dP - delta) * scale
+//                  -> dQ += dS K.
+//   attn_bwd_dkv_k: per 128-key tile, loop over visible 64-query tiles, transposed scores:
+//                  S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T -> dV += P^T dO, dK += dS^T Q.
+//
+// Fully masked key tiles are never visited (causal upper triangle, keys older than the
+// window).  Mask semantics: key j is visible to query i iff i - window <= j <= i
+// (brain/src/forward.rs:1134-1138, brain/fa3/flash3_api.cu:124-133).  The reference calls a
+// Hopper-only FlashAttention-3 build here (brain/src/forward.rs:1124-1177,
+// brain/src/backward.rs:613-659); the two-kernel backward is deterministic (no atomics into
+// dQ, unlike the FA3 semaphore/atomic accumulation).
+#include "api.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace arb {
+
+constexpr int HD = 128;
+constexpr int ATT_THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnArgs {
+  int B, T, H, window;
+  float scale;
+  // forward / dq
+  void* o; long long ldo;            // forward: O [B,T,H,128] bf16 ; dq kernel: dQ
+  float* lse;                        // [B,H,T]
+  const float* delta;                // [B,H,T] (backward)
+  // dkv
+  void* dk; void* dv; long long lddk, lddv;
+  int* err;
+};
+
+// 16-byte store into a K-major 128-byte-swizzled tile of `rows` rows; columns beyond 64 go
+// to the next (rows*128)-byte half.
+__device__ __forceinline__ void st_sw128(uint32_t base, int rows, int r, int c0, uint4 v) {
+  const uint32_t addr = base + uint32_t(c0 >> 6) * uint32_t(rows) * 128u + uint32_t(r) * 128u +
+                        (uint32_t(((c0 & 63) >> 3) ^ (r & 7)) << 4);
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// ===============================================================================================
+// Forward
+// ===============================================================================================
+struct FwdSmem {
+  static constexpr int Q = 0;
+  static constexpr int K0 = 32768;            // 2 stages of 32 KB
+  static constexpr int V0 = K0 + 2 * 32768;   // 2 stages of 32 KB
+  static constexpr int P0 = V0 + 2 * 32768;   // 2 buffers of 32 KB
+  static constexpr int BAR = P0 + 2 * 32768;
+  static constexpr int TOTAL = BAR + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+           const __grid_constant__ CUtensorMap tmV, const AttnArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FwdSmem::BAR);
+  uint64_t* q_full = bars;             // 1
+  uint64_t* k_full = bars + 1;         // 2
+  uint64_t* k_empty = bars + 3;        // 2
+  uint64_t* v_full = bars + 5;         // 2
+  uint64_t* v_empty = bars + 7;        // 2
+  uint64_t* s_full = bars + 9;         // 2
+  uint64_t* s_empty = bars + 11;       // 2
+  uint64_t* p_full = bars + 13;        // 2
+  uint64_t* p_empty = bars + 15;       // 2
+  uint64_t* o_done = bars + 17;        // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Heavier (later) query tiles are scheduled first.
+  const int n_mt = (p.T + 127) / 128;
+  const int mt = n_mt - 1 - int(blockIdx.x);
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int m0 = mt * 128;
+  const int j_lo = (p.window >= p.T) ? 0 : max(0, (m0 - p.window) / 128);
+  const int j_hi = min((p.T - 1) / 128, (m0 + 127) / 128);
+  const int n_tiles = j_hi - j_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+      mbar_init(&p_full[i], 4); mbar_init(&p_empty[i], 1);
+    }
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t TM_S = tmem, TM_O = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, 32768);
+      tma_load_4d(smem + FwdSmem::Q, &tmQ, q_full, 0, h, m0, b);
+      tma_load_4d(smem + FwdSmem::Q + 16384, &tmQ, q_full, 64, h, m0, b);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        const int n0 = (j_lo + t) * 128;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&k_full[s], 32768);
+        tma_load_4d(smem + FwdSmem::K0 + s * 32768, &tmK, &k_full[s], 0, h, n0, b);
+        tma_load_4d(smem + FwdSmem::K0 + s * 32768 + 16384, &tmK, &k_full[s], 64, h, n0, b);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&v_full[s], 32768);
+        tma_load_4d(smem + FwdSmem::V0 + s * 32768, &tmV, &v_full[s], 0, h, n0, b);
+        tma_load_4d(smem + FwdSmem::V0 + s * 32768 + 16384, &tmV, &v_full[s], 64, h, n0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, false, true);
+      const uint32_t sq = smem_u32(smem + FwdSmem::Q);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_s = [&](int t) -> bool {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(&k_full[s], ph, abort_flag)) return false;
+        if (!mbar_wait(&s_empty[s], ph ^ 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + FwdSmem::K0 + s * 32768);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
+          tc_mma_ss(TM_S + s * 128, make_smem_desc(sq + off, 0, 1024), make_smem_desc(sk + off, 0, 1024), idesc_s, k > 0);
+        }
+        tc_commit(&k_empty[s]);
+        tc_commit(&s_full[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        if (t + 1 < n_tiles) { ok = issue_s(t + 1); if (!ok) break; }
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(&p_full[s], ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sp = smem_u32(smem + FwdSmem::P0 + s * 32768);
+        const uint32_t sv = smem_u32(smem + FwdSmem::V0 + s * 32768);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
+          tc_mma_ss(TM_O, make_smem_desc(sp + aoff, 0, 1024), make_smem_desc(sv + k * 2048, 16384, 1024), idesc_o,
+                    (t > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&v_empty[s]);
+        tc_commit(&p_empty[s]);
+      }
+      if (ok) tc_commit(o_done);
+    }
+  } else {
+    // ---------------- softmax / correction / epilogue: thread <-> query row ----------------
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int row = m0 + r;
+    const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    const float c = p.scale * LOG2E;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int s = t & 1;
+      const uint32_t ph = (t >> 1) & 1;
+      const int n0 = (j_lo + t) * 128;
+      if (!mbar_wait(&s_full[s], ph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      float sc[128];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t v[32];
+        tmem_ld32(TM_S + lane_addr + uint32_t(s * 128 + cc * 32), v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sc[cc * 32 + j] = __uint_as_float(v[j]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[s]);
+      // masks are needed only on tiles that touch the diagonal, the window edge or the tail
+      const bool need_mask = (n0 + 127 > m0) || (p.window < p.T && n0 < m0 + 127 - p.window) || (n0 + 127 >= p.T);
+      if (need_mask) {
+#pragma unroll
+        for (int j = 0; j < 128; ++j) {
+          const int key = n0 + j;
+          const bool vis = (key <= row) && (key >= row - p.window) && (key < p.T);
+          sc[j] = vis ? sc[j] : -INFINITY;
+        }
+      }
+      float mx = sc[0];
+#pragma unroll
+      for (int j = 1; j < 128; ++j) mx = fmaxf(mx, sc[j]);
+      const float m_new = fmaxf(m_used, mx);
+      bool resc = false;
+      if (m_used == -INFINITY) m_used = m_new;            // nothing accumulated for this row yet
+      else resc = (m_new - m_used) * c > 8.f;
+      if (t > 0 && __any_sync(0xffffffffu, resc)) {
+        // O must not be in flight: PV of the previous tile has to be complete.
+        const int sp = (t - 1) & 1;
+        if (!mbar_wait(&p_empty[sp], ((t - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const float alpha = resc ? fast_exp2((m_used - m_new) * c) : 1.f;
+        if (resc) { l *= alpha; m_used = m_new; }
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t v[32];
+          tmem_ld32(TM_O + lane_addr + uint32_t(cc * 32), v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+          tmem_st32(TM_O + lane_addr + uint32_t(cc * 32), v);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+      }
+      const float mc = (m_used == -INFINITY) ? 0.f : m_used * c;
+      // P buffer s was last read by the PV MMA of tile t-2
+      if (t >= 2 && !mbar_wait(&p_empty[s], ((t - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+      const uint32_t pbase = smem_u32(smem + FwdSmem::P0 + s * 32768);
+      float rs = 0.f;
+#pragma unroll
+      for (int j = 0; j < 128; j += 8) {
+        float e[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { e[u] = fast_exp2(sc[j + u] * c - mc); rs += e[u]; }
+        uint4 pk;
+        pk.x = pack_bf16(e[0], e[1]); pk.y = pack_bf16(e[2], e[3]); pk.z = pack_bf16(e[4], e[5]); pk.w = pack_bf16(e[6], e[7]);
+        st_sw128(pbase, 128, r, j, pk);
+      }
+      l += rs;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[s]);
+    }
+    if (ok && mbar_wait(o_done, 0, abort_flag)) {
+      tc_fence_after();
+      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + ((long long)b * p.T + row) * p.ldo + h * HD;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t v[32];
+        tmem_ld32(TM_O + lane_addr + uint32_t(cc * 32), v);
+        tmem_wait_ld();
+        if (row < p.T) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(v[j]) * inv_l, __uint_as_float(v[j + 1]) * inv_l);
+            u.y = pack_bf16(__uint_as_float(v[j + 2]) * inv_l, __uint_as_float(v[j + 3]) * inv_l);
+            u.z = pack_bf16(__uint_as_float(v[j + 4]) * inv_l, __uint_as_float(v[j + 5]) * inv_l);
+            u.w = pack_bf16(__uint_as_float(v[j + 6]) * inv_l, __uint_as_float(v[j + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + cc * 32 + j) = u;
+          }
+        }
+      }
+      if (row < p.T) p.lse[((long long)b * p.H + h) * p.T + row] = (l > 0.f) ? (m_used * p.scale + __logf(l)) : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, ERR_ATTN_TIMEOUT);
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// ===============================================================================================
+// Backward, dQ: query-stationary.
+// ===============================================================================================
+struct DqSmem {
+  static constexpr int Q = 0, DO = 32768;
+  static constexpr int K0 = 65536;              // 2 stages
+  static constexpr int V0 = K0 + 2 * 32768;     // 2 stages
+  static constexpr int DS = V0 + 2 * 32768;     // 1 buffer of 32 KB
+  static constexpr int BAR = DS + 32768;
+  static constexpr int TOTAL = BAR + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const AttnArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DqSmem::BAR);
+  uint64_t* q_full = bars;             // Q + dO
+  uint64_t* k_full = bars + 1;         // 2
+  uint64_t* k_empty = bars + 3;        // 2  (freed by the dQ MMA)
+  uint64_t* v_full = bars + 5;         // 2
+  uint64_t* v_empty = bars + 7;        // 2  (freed by the dP MMA)
+  uint64_t* sd_full = bars + 9;        // 1  S and dP ready
+  uint64_t* sd_empty = bars + 10;      // 1  threads have read S and dP
+  uint64_t* ds_full = bars + 11;       // 1
+  uint64_t* ds_empty = bars + 12;      // 1  dQ MMA consumed dS
+  uint64_t* done = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_mt = (p.T + 127) / 128;
+  const int mt = n_mt - 1 - int(blockIdx.x);
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int m0 = mt * 128;
+  const int j_lo = (p.window >= p.T) ? 0 : max(0, (m0 - p.window) / 128);
+  const int j_hi = min((p.T - 1) / 128, (m0 + 127) / 128);
+  const int n_tiles = j_hi - j_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
+    mbar_init(sd_full, 1); mbar_init(sd_empty, 4); mbar_init(ds_full, 4); mbar_init(ds_empty, 1); mbar_init(done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t TM_S = tmem, TM_DP = tmem + 128, TM_DQ = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(q_full, 65536);
+      tma_load_4d(smem + DqSmem::Q, &tmQ, q_full, 0, h, m0, b);
+      tma_load_4d(smem + DqSmem::Q + 16384, &tmQ, q_full, 64, h, m0, b);
+      tma_load_4d(smem + DqSmem::DO, &tmDO, q_full, 0, h, m0, b);
+      tma_load_4d(smem + DqSmem::DO + 16384, &tmDO, q_full, 64, h, m0, b);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        const int n0 = (j_lo + t) * 128;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&k_full[s], 32768);
+        tma_load_4d(smem + DqSmem::K0 + s * 32768, &tmK, &k_full[s], 0, h, n0, b);
+        tma_load_4d(smem + DqSmem::K0 + s * 32768 + 16384, &tmK, &k_full[s], 64, h, n0, b);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&v_full[s], 32768);
+        tma_load_4d(smem + DqSmem::V0 + s * 32768, &tmV, &v_full[s], 0, h, n0, b);
+        tma_load_4d(smem + DqSmem::V0 + s * 32768 + 16384, &tmV, &v_full[s], 64, h, n0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_kmn = make_idesc_bf16(128, 128, false, true);
+      const uint32_t sq = smem_u32(smem + DqSmem::Q), sdo = smem_u32(smem + DqSmem::DO);
+      const uint32_t sds = smem_u32(smem + DqSmem::DS);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_sd = [&](int t) -> bool {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(&k_full[s], ph, abort_flag)) return false;
+        if (!mbar_wait(&v_full[s], ph, abort_flag)) return false;
+        if (!mbar_wait(sd_empty, (t & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + DqSmem::K0 + s * 32768);
+        const uint32_t sv = smem_u32(smem + DqSmem::V0 + s * 32768);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
+          tc_mma_ss(TM_S, make_smem_desc(sq + off, 0, 1024), make_smem_desc(sk + off, 0, 1024), idesc_kk, k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
+          tc_mma_ss(TM_DP, make_smem_desc(sdo + off, 0, 1024), make_smem_desc(sv + off, 0, 1024), idesc_kk, k > 0);
+        }
+        tc_commit(&v_empty[s]);
+        tc_commit(sd_full);
+        return true;
+      };
+      if (ok) ok = issue_sd(0);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int s = t & 1;
+        if (!mbar_wait(ds_full, t & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + DqSmem::K0 + s * 32768);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
+          tc_mma_ss(TM_DQ, make_smem_desc(sds + aoff, 0, 1024), make_smem_desc(sk + k * 2048, 16384, 1024), idesc_kmn,
+                    (t > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&k_empty[s]);
+        tc_commit(ds_empty);
+        if (t + 1 < n_tiles) ok = issue_sd(t + 1);
+      }
+      if (ok) tc_commit(done);
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int row = m0 + r;
+    const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    const float c = p.scale * LOG2E;
+    const long long stat = ((long long)b * p.H + h) * p.T + row;
+    const float lse2 = (row < p.T) ? p.lse[stat] * LOG2E : INFINITY;
+    const float dlt = (row < p.T) ? p.delta[stat] : 0.f;
+    const uint32_t dsbase = smem_u32(smem + DqSmem::DS);
+    bool ok = true;
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int n0 = (j_lo + t) * 128;
+      if (!mbar_wait(sd_full, t & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      // dS buffer is free once the dQ MMA of the previous tile has consumed it
+      if (t >= 1 && !mbar_wait(ds_empty, (t - 1) & 1, abort_flag)) { ok = false; break; }
+      const bool need_mask = (n0 + 127 > m0) || (p.window < p.T && n0 < m0 + 127 - p.window) || (n0 + 127 >= p.T);
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(TM_S + lane_addr + uint32_t(cc * 32), sv);
+        tmem_ld32(TM_DP + lane_addr + uint32_t(cc * 32), dv);
+        tmem_wait_ld();
+        float ds[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int key = n0 + cc * 32 + j;
+          const bool vis = !need_mask || ((key <= row) && (key >= row - p.window) && (key < p.T));
+          const float pr = vis ? fast_exp2(__uint_as_float(sv[j]) * c - lse2) : 0.f;
+          ds[j] = pr * (__uint_as_float(dv[j]) - dlt) * p.scale;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 pk;
+          pk.x = pack_bf16(ds[j], ds[j + 1]); pk.y = pack_bf16(ds[j + 2], ds[j + 3]);
+          pk.z = pack_bf16(ds[j + 4], ds[j + 5]); pk.w = pack_bf16(ds[j + 6], ds[j + 7]);
+          st_sw128(dsbase, 128, r, cc * 32 + j, pk);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(sd_empty); mbar_arrive(ds_full); }
+    }
+    if (ok && mbar_wait(done, 0, abort_flag)) {
+      tc_fence_after();
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + ((long long)b * p.T + row) * p.ldo + h * HD;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t v[32];
+        tmem_ld32(TM_DQ + lane_addr + uint32_t(cc * 32), v);
+        tmem_wait_ld();
+        if (row < p.T) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+            u.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+            u.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+            u.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+            *reinterpret_cast<uint4*>(orow + cc * 32 + j) = u;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, ERR_ATTN_TIMEOUT);
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// ===============================================================================================
+// Backward, dK / dV: key-stationary, 64-query streaming tiles, transposed scores.
+// ===============================================================================================
+struct DkvSmem {
+  static constexpr int K = 0, V = 32768;
+  static constexpr int Q0 = 65536;              // 2 stages of 16 KB
+  static constexpr int DO0 = Q0 + 2 * 16384;    // 2 stages of 16 KB
+  static constexpr int PT = DO0 + 2 * 16384;    // 16 KB  P^T  [128 kv x 64 q]
+  static constexpr int DST = PT + 16384;        // 16 KB  dS^T
+  static constexpr int STAT = DST + 16384;      // lse2[2][64], delta[2][64] floats = 1 KB
+  static constexpr int BAR = STAT + 1024;
+  static constexpr int TOTAL = BAR + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const AttnArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DkvSmem::BAR);
+  uint64_t* kv_full = bars;            // K + V
+  uint64_t* q_full = bars + 1;         // 2 (Q_i and dO_i together)
+  uint64_t* q_empty = bars + 3;        // 2 (freed by the dV/dK MMAs)
+  uint64_t* sd_full = bars + 5;        // 1
+  uint64_t* sd_empty = bars + 6;       // 1
+  uint64_t* pd_full = bars + 7;        // 1  P^T and dS^T written
+  uint64_t* pd_empty = bars + 8;       // 1
+  uint64_t* done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stat_lse = reinterpret_cast<float*>(smem + DkvSmem::STAT);   // [2][64]
+  float* stat_dl = stat_lse + 128;                                     // [2][64]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nt = int(blockIdx.x);
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int n0 = nt * 128;
+  // visible queries: n0 <= i <= n0 + 127 + window
+  const int i_lo = n0 / 64;
+  const long long last_q = (p.window >= p.T) ? (long long)(p.T - 1) : min((long long)(p.T - 1), (long long)n0 + 127 + p.window);
+  const int i_hi = int(last_q / 64);
+  const int n_tiles = i_hi - i_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    mbar_init(sd_full, 1); mbar_init(sd_empty, 4); mbar_init(pd_full, 4); mbar_init(pd_empty, 1); mbar_init(done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t TM_S = tmem, TM_DP = tmem + 64, TM_DV = tmem + 128, TM_DK = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(kv_full, 65536);
+      tma_load_4d(smem + DkvSmem::K, &tmK, kv_full, 0, h, n0, b);
+      tma_load_4d(smem + DkvSmem::K + 16384, &tmK, kv_full, 64, h, n0, b);
+      tma_load_4d(smem + DkvSmem::V, &tmV, kv_full, 0, h, n0, b);
+      tma_load_4d(smem + DkvSmem::V + 16384, &tmV, kv_full, 64, h, n0, b);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        const int q0 = (i_lo + t) * 64;
+        if (!mbar_wait(&q_empty[s], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&q_full[s], 32768);
+        tma_load_4d(smem + DkvSmem::Q0 + s * 16384, &tmQ, &q_full[s], 0, h, q0, b);
+        tma_load_4d(smem + DkvSmem::Q0 + s * 16384 + 8192, &tmQ, &q_full[s], 64, h, q0, b);
+        tma_load_4d(smem + DkvSmem::DO0 + s * 16384, &tmDO, &q_full[s], 0, h, q0, b);
+        tma_load_4d(smem + DkvSmem::DO0 + s * 16384 + 8192, &tmDO, &q_full[s], 64, h, q0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);     // [128 kv x 64 q]
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, false, true);     // [128 kv x 128 d], B MN-major
+      const uint32_t sk = smem_u32(smem + DkvSmem::K), sv = smem_u32(smem + DkvSmem::V);
+      const uint32_t spt = smem_u32(smem + DkvSmem::PT), sdst = smem_u32(smem + DkvSmem::DST);
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      auto issue_sd = [&](int t) -> bool {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(&q_full[s], ph, abort_flag)) return false;
+        if (!mbar_wait(sd_empty, (t & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t sq = smem_u32(smem + DkvSmem::Q0 + s * 16384);
+        const uint32_t sdo = smem_u32(smem + DkvSmem::DO0 + s * 16384);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {   // K dim = d: A halves are 16 KB apart (128 rows), B halves 8 KB apart (64 rows)
+          const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
+          const uint32_t boff = uint32_t(k >> 2) * 8192u + uint32_t(k & 3) * 32u;
+          tc_mma_ss(TM_S, make_smem_desc(sk + aoff, 0, 1024), make_smem_desc(sq + boff, 0, 1024), idesc_s, k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
+          const uint32_t boff = uint32_t(k >> 2) * 8192u + uint32_t(k & 3) * 32u;
+          tc_mma_ss(TM_DP, make_smem_desc(sv + aoff, 0, 1024), make_smem_desc(sdo + boff, 0, 1024), idesc_s, k > 0);
+        }
+        tc_commit(sd_full);
+        return true;
+      };
+      if (ok) ok = issue_sd(0);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int s = t & 1;
+        if (!mbar_wait(pd_full, t & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sq = smem_u32(smem + DkvSmem::Q0 + s * 16384);
+        const uint32_t sdo = smem_u32(smem + DkvSmem::DO0 + s * 16384);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {   // K dim = 64 queries
+          tc_mma_ss(TM_DV, make_smem_desc(spt + k * 32, 0, 1024), make_smem_desc(sdo + k * 2048, 8192, 1024), idesc_o,
+                    (t > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          tc_mma_ss(TM_DK, make_smem_desc(sdst + k * 32, 0, 1024), make_smem_desc(sq + k * 2048, 8192, 1024), idesc_o,
+                    (t > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&q_empty[s]);
+        tc_commit(pd_empty);
+        if (t + 1 < n_tiles) ok = issue_sd(t + 1);
+      }
+      if (ok) tc_commit(done);
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;         // key row inside the tile
+    const int key = n0 + r;
+    const int tid = threadIdx.x - 64;    // 0..127
+    const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    const float c = p.scale * LOG2E;
+    const uint32_t ptbase = smem_u32(smem + DkvSmem::PT), dstbase = smem_u32(smem + DkvSmem::DST);
+    const long long stat0 = ((long long)b * p.H + h) * p.T;
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int q0 = (i_lo + t) * 64;
+      const int sb = t & 1;
+      // stage the 64 per-query statistics of this tile (double buffered by tile parity)
+      {
+        const int qi = q0 + (tid & 63);
+        if (tid < 64) stat_lse[sb * 64 + tid] = (qi < p.T) ? p.lse[stat0 + qi] * LOG2E : INFINITY;
+        else stat_dl[sb * 64 + (tid & 63)] = (qi < p.T) ? p.delta[stat0 + qi] : 0.f;
+      }
+      named_bar_sync(1, 128);
+      if (ok && !mbar_wait(sd_full, t & 1, abort_flag)) ok = false;
+      if (ok && t >= 1 && !mbar_wait(pd_empty, (t - 1) & 1, abort_flag)) ok = false;
+      if (!ok) continue;   // keep taking part in the named barrier so nobody is left waiting
+      tc_fence_after();
+      const bool need_mask = (q0 < n0 + 127) || (p.window < p.T && q0 + 63 > n0 + p.window) || (q0 + 63 >= p.T) || (n0 + 127 >= p.T);
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(TM_S + lane_addr + uint32_t(cc * 32), sv);
+        tmem_ld32(TM_DP + lane_addr + uint32_t(cc * 32), dv);
+        tmem_wait_ld();
+        float pt[32], ds[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int qi = q0 + cc * 32 + j;
+          const bool vis = !need_mask || ((key <= qi) && (key >= qi - p.window) && (qi < p.T) && (key < p.T));
+          const float pr = vis ? fast_exp2(__uint_as_float(sv[j]) * c - stat_lse[sb * 64 + cc * 32 + j]) : 0.f;
+          pt[j] = pr;
+          ds[j] = pr * (__uint_as_float(dv[j]) - stat_dl[sb * 64 + cc * 32 + j]) * p.scale;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 a, d;
+          a.x = pack_bf16(pt[j], pt[j + 1]); a.y = pack_bf16(pt[j + 2], pt[j + 3]);
+          a.z = pack_bf16(pt[j + 4], pt[j + 5]); a.w = pack_bf16(pt[j + 6], pt[j + 7]);
+          d.x = pack_bf16(ds[j], ds[j + 1]); d.y = pack_bf16(ds[j + 2], ds[j + 3]);
+          d.z = pack_bf16(ds[j + 4], ds[j + 5]); d.w = pack_bf16(ds[j + 6], ds[j + 7]);
+          st_sw128(ptbase, 128, r, cc * 32 + j, a);
+          st_sw128(dstbase, 128, r, cc * 32 + j, d);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(sd_empty); mbar_arrive(pd_full); }
+    }
+    if (ok && mbar_wait(done, 0, abort_flag)) {
+      tc_fence_after();
+      __nv_bfloat16* dkrow = reinterpret_cast<__nv_bfloat16*>(p.dk) + ((long long)b * p.T + key) * p.lddk + h * HD;
+      __nv_bfloat16* dvrow = reinterpret_cast<__nv_bfloat16*>(p.dv) + ((long long)b * p.T + key) * p.lddv + h * HD;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t v[32];
+          tmem_ld32((which ? TM_DK : TM_DV) + lane_addr + uint32_t(cc * 32), v);
+          tmem_wait_ld();
+          if (key < p.T) {
+            __nv_bfloat16* dst = (which ? dkrow : dvrow) + cc * 32;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 u;
+              u.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+              u.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              u.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+              u.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+              *reinterpret_cast<uint4*>(dst + j) = u;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, ERR_ATTN_TIMEOUT);
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per (token, head)
+__global__ void __launch_bounds__(256) attn_delta_k(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                                    float* __restrict__ delta, int B, int T, int H, long long ldo, long long lddo) {
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)B * T * H) return;
+  const int h = int(wid % H);
+  const long long bt = wid / H;
+  const uint2 a = *reinterpret_cast<const uint2*>(o + bt * ldo + h * HD + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(d_o + bt * lddo + h * HD + lane * 4);
+  float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), g0 = unpack_bf16(g.x), g1 = unpack_bf16(g.y);
+  float acc = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) {
+    const int t = int(bt % T);
+    const int b = int(bt / T);
+    delta[((long long)b * H + h) * T + t] = acc;
+  }
+}
+
+// [B, T, H, 128] bf16 view with token stride ld: dims {128, H, T, B}; box {64, 1, rows, 1}
+static int make_qkv_tmap(CUtensorMap* m, const void* base, int B, int T, int H, long long ld, int box_rows) {
+  uint64_t dims[4] = {128, uint64_t(H), uint64_t(T), uint64_t(B)};
+  uint64_t str[3] = {256, uint64_t(ld) * 2, uint64_t(ld) * 2 * uint64_t(T)};
+  uint32_t box[4] = {64, 1, uint32_t(box_rows), 1};
+  return make_tmap_bf16(m, base, 4, dims, str, box);
+}
+
+static bool bad_ptr(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
+
+template <typename Kern>
+static int set_smem(Kern k, int bytes) {
+  return int(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+}
+
+}  // namespace arb
+
+using namespace arb;
+
+extern "C" int arb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int H,
+                            long long ldq, long long ldk, long long ldv, long long ldo, int window, float scale,
+                            int* err_flag, cudaStream_t stream) {
+  if (B <= 0 || T <= 0 || H <= 0 || window < 0) return -3;
+  if (bad_ptr(q) || bad_ptr(k) || bad_ptr(v) || bad_ptr(o) || (ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -4;
+  if (H > 65535 || B > 65535) return -3;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_qkv_tmap(&tq, q, B, T, H, ldq, 128))) return 1000 + r;
+  if ((r = make_qkv_tmap(&tk, k, B, T, H, ldk, 128))) return 1000 + r;
+  if ((r = make_qkv_tmap(&tv, v, B, T, H, ldv, 128))) return 1000 + r;
+  static bool cfg = false;
+  if (!cfg) { if ((r = set_smem(attn_fwd_k, FwdSmem::TOTAL))) return r; cfg = true; }
+  AttnArgs a{};
+  a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
+  a.o = o; a.ldo = ldo; a.lse = lse; a.err = err_flag;
+  dim3 grid((T + 127) / 128, H, B);
+  attn_fwd_k<<<grid, ATT_THREADS, FwdSmem::TOTAL, stream>>>(tq, tk, tv, a);
+  return int(cudaGetLastError());
+}
+
+extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                            void* dq, void* dk, void* dv, float* delta, float* dq_accum, int B, int T, int H,
+                            long long ldq, long long ldk, long long ldv, long long ldo, long long lddo, long long lddq,
+                            long long lddk, long long lddv, int window, float scale, int* err_flag, cudaStream_t stream) {
+  (void)dq_accum;  // the two-kernel backward needs no fp32 dQ accumulator
+  if (B <= 0 || T <= 0 || H <= 0 || window < 0 || H > 65535 || B > 65535) return -3;
+  if (bad_ptr(q) || bad_ptr(k) || bad_ptr(v) || bad_ptr(o) || bad_ptr(d_o) || bad_ptr(dq) || bad_ptr(dk) || bad_ptr(dv)) return -4;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8) || (lddo % 8) || (lddq % 8) || (lddk % 8) || (lddv % 8)) return -4;
+  int r;
+  attn_delta_k<<<unsigned(((long long)B * T * H + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, T, H, ldo, lddo);
+  if ((r = int(cudaGetLastError()))) return r;
+  static bool cfg = false;
+  if (!cfg) {
+    if ((r = set_smem(attn_bwd_dq_k, DqSmem::TOTAL))) return r;
+    if ((r = set_smem(attn_bwd_dkv_k, DkvSmem::TOTAL))) return r;
+    cfg = true;
+  }
+  AttnArgs a{};
+  a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
+  a.lse = const_cast<float*>(lse); a.delta = delta; a.err = err_flag;
+  {
+    CUtensorMap tq, tk, tv, tdo;
+    if ((r = make_qkv_tmap(&tq, q, B, T, H, ldq, 128))) return 1000 + r;
+    if ((r = make_qkv_tmap(&tk, k, B, T, H, ldk, 128))) return 1000 + r;
+    if ((r = make_qkv_tmap(&tv, v, B, T, H, ldv, 128))) return 1000 + r;
+    if ((r = make_qkv_tmap(&tdo, d_o, B, T, H, lddo, 128))) return 1000 + r;
+    a.o = dq; a.ldo = lddq;
+    dim3 grid((T + 127) / 128, H, B);
+    attn_bwd_dq_k<<<grid, ATT_THREADS, DqSmem::TOTAL, stream>>>(tq, tk, tv, tdo, a);
+    if ((r = int(cudaGetLastError()))) return r;
+  }
+  {
+    CUtensorMap tq, tk, tv, tdo;
+    if ((r = make_qkv_tmap(&tq, q, B, T, H, ldq, 64))) return 1000 + r;
+    if ((r = make_qkv_tmap(&tk, k, B, T, H, ldk, 128))) return 1000 + r;
+    if ((r = make_qkv_tmap(&tv, v, B, T, H, ldv, 128))) return 1000 + r;
+    if ((r = make_qkv_tmap(&tdo, d_o, B, T, H, lddo, 64))) return 1000 + r;
+    a.dk = dk; a.dv = dv; a.lddk = lddk; a.lddv = lddv;
+    dim3 grid((T + 127) / 128, H, B);
+    attn_bwd_dkv_k<<<grid, ATT_THREADS, DkvSmem::TOTAL, stream>>>(tq, tk, tv, tdo, a);
+    if ((r = int(cudaGetLastError()))) return r;
+  }
+  return 0;
+}

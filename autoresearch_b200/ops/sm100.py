@@ -262,11 +262,10 @@ class AttentionFn(torch.autograd.Function):
         d_out = d_out.contiguous()
         d_qkv = torch.empty_like(qkv)
         delta = torch.empty(B, H, T, dtype=torch.float32, device=qkv.device)
-        dq_acc = torch.zeros(N, Dl, dtype=torch.float32, device=qkv.device)
         ld = qkv.stride(0)
         b, db = qkv.data_ptr(), d_qkv.data_ptr()
         rc = K.lib().arb_attn_bwd(b, b + 2 * Dl, b + 4 * Dl, out.data_ptr(), d_out.data_ptr(), lse.data_ptr(),
-                                  db, db + 2 * Dl, db + 4 * Dl, delta.data_ptr(), dq_acc.data_ptr(), B, T, H,
+                                  db, db + 2 * Dl, db + 4 * Dl, delta.data_ptr(), 0, B, T, H,
                                   ld, ld, ld, Dl, Dl, ld, ld, ld, window, 1.0 / math.sqrt(128.0),
                                   K.err_flag(qkv.device).data_ptr(), K._stream())
         K._check(rc, "attn_bwd")

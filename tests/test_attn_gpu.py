@@ -1,0 +1,58 @@
+"""tcgen05 flash attention (forward, dQ, dK/dV) against explicit-mask fp32 attention."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(B, T, H, window, seed=0):
+    from autoresearch_b200.ops import kernels as K, reference as R, sm100
+    torch.manual_seed(seed)
+    Dl = H * 128
+    qkv = (torch.randn(B * T, 3 * Dl, device="cuda") * 1.0).to(torch.bfloat16).requires_grad_(True)
+    out = sm100.AttentionFn.apply(qkv, B, T, H, window)
+    g = (torch.randn(B * T, Dl, device="cuda")).to(torch.bfloat16)
+    out.backward(g)
+    torch.cuda.synchronize()
+    K.check_err_flag()
+    ref_in = qkv.detach().float().requires_grad_(True)
+    q = ref_in[:, :Dl].reshape(B, T, H, 128)
+    k = ref_in[:, Dl:2 * Dl].reshape(B, T, H, 128)
+    v = ref_in[:, 2 * Dl:].reshape(B, T, H, 128)
+    ref = R.attention(q, k, v, window).reshape(B * T, Dl)
+    ref.backward(g.float())
+
+    def rel(a, b):
+        return ((a.float() - b).norm() / (b.norm() + 1e-12)).item()
+
+    assert rel(out, ref) < 2e-2, f"out {rel(out, ref)}"
+    gq, gk, gv = (qkv.grad[:, i * Dl:(i + 1) * Dl] for i in range(3))
+    rq, rk, rv = (ref_in.grad[:, i * Dl:(i + 1) * Dl] for i in range(3))
+    assert rel(gv, rv) < 3e-2, f"dv {rel(gv, rv)}"
+    assert rel(gk, rk) < 3e-2, f"dk {rel(gk, rk)}"
+    assert rel(gq, rq) < 3e-2, f"dq {rel(gq, rq)}"
+
+
+@pytest.mark.parametrize("B,T,H,window", [(1, 128, 1, 128), (2, 256, 2, 256), (1, 512, 2, 256), (1, 1024, 1, 256),
+                                         (1, 640, 1, 64), (2, 320, 1, 100), (1, 1536, 2, 1536)])
+def test_attention_matches_reference(B, T, H, window):
+    _run(B, T, H, window)
+
+
+def test_lse_matches_reference():
+    from autoresearch_b200.ops import kernels as K, reference as R, sm100
+    torch.manual_seed(1)
+    B, T, H = 1, 384, 1
+    qkv = torch.randn(B * T, 3 * 128, device="cuda").to(torch.bfloat16)
+    out = torch.empty(B * T, 128, dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty(B, H, T, dtype=torch.float32, device="cuda")
+    base = qkv.data_ptr()
+    rc = K.lib().arb_attn_fwd(base, base + 256, base + 512, out.data_ptr(), lse.data_ptr(), B, T, H, 384, 384, 384, 128,
+                              T, 1 / math.sqrt(128), K.err_flag().data_ptr(), K._stream())
+    assert rc == 0
+    q, k = qkv[:, :128].float(), qkv[:, 128:256].float()
+    s = (q @ k.t()) / math.sqrt(128)
+    s = s.masked_fill(~R.window_mask(T, T, "cuda"), float("-inf"))
+    assert (torch.logsumexp(s, -1) - lse.view(-1)).abs().max().item() < 2e-2
