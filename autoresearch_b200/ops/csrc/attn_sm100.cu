@@ -293,14 +293,47 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 }
 
 // ===============================================================================================
-// Backward, dQ: query-stationary.
+// Backward.  Both kernels stream 64-row sub-tiles through a 4-stage TMA ring, keep two TMEM
+// buffers for the score / dP accumulators (the MMAs of sub-tile t+1 run while the softmax warps
+// work on sub-tile t) and stage the bf16 P / dS operands of the output MMAs in swizzled smem.
 // ===============================================================================================
+constexpr int BWD_STAGES = 4;
+
+// p = exp2(s*c - lse2), ds = p * (dp - delta) * scale for 32 columns of one row; results packed
+// to bf16 pairs.  ROWSTAT: lse2/delta are per-row scalars (dQ kernel); otherwise per-column
+// arrays (dK/dV kernel, transposed scores).
+template <bool MASK, bool ROWSTAT, bool WANT_P>
+__device__ __forceinline__ void bwd_chunk(const uint32_t (&sv)[32], const uint32_t (&dv)[32], float c, float scale,
+                                          float row_lse2, float row_dl, const float* col_lse2, const float* col_dl,
+                                          int row_idx, int col0, int window, int T, bool row_is_query,
+                                          uint32_t* p_pk, uint32_t* ds_pk) {
+  float pr[32], ds[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const float l2 = ROWSTAT ? row_lse2 : col_lse2[j];
+    const float dl = ROWSTAT ? row_dl : col_dl[j];
+    float e = fast_exp2(__uint_as_float(sv[j]) * c - l2);
+    if (MASK) {
+      const int qi = row_is_query ? row_idx : col0 + j;
+      const int ki = row_is_query ? col0 + j : row_idx;
+      const bool vis = (ki <= qi) && (ki >= qi - window) && (qi < T) && (ki < T);
+      e = vis ? e : 0.f;
+    }
+    pr[j] = e;
+    ds[j] = e * scale * (__uint_as_float(dv[j]) - dl);
+  }
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    if (WANT_P) p_pk[j >> 1] = pack_bf16(pr[j], pr[j + 1]);
+    ds_pk[j >> 1] = pack_bf16(ds[j], ds[j + 1]);
+  }
+}
+
 struct DqSmem {
   static constexpr int Q = 0, DO = 32768;
-  static constexpr int K0 = 65536;              // 2 stages
-  static constexpr int V0 = K0 + 2 * 32768;     // 2 stages
-  static constexpr int DS = V0 + 2 * 32768;     // 1 buffer of 32 KB
-  static constexpr int BAR = DS + 32768;
+  static constexpr int KV0 = 65536;                          // BWD_STAGES x (K_sub 16 KB + V_sub 16 KB)
+  static constexpr int DS = KV0 + BWD_STAGES * 32768;        // 16 KB  dS [128 q x 64 keys]
+  static constexpr int BAR = DS + 16384;
   static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
@@ -310,17 +343,16 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DqSmem::BAR);
-  uint64_t* q_full = bars;             // Q + dO
-  uint64_t* k_full = bars + 1;         // 2
-  uint64_t* k_empty = bars + 3;        // 2  (freed by the dQ MMA)
-  uint64_t* v_full = bars + 5;         // 2
-  uint64_t* v_empty = bars + 7;        // 2  (freed by the dP MMA)
-  uint64_t* sd_full = bars + 9;        // 1  S and dP ready
-  uint64_t* sd_empty = bars + 10;      // 1  threads have read S and dP
-  uint64_t* ds_full = bars + 11;       // 1
-  uint64_t* ds_empty = bars + 12;      // 1  dQ MMA consumed dS
-  uint64_t* done = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* q_full = bars;                          // Q + dO
+  uint64_t* kv_full = bars + 1;                     // [4]
+  uint64_t* k_empty = kv_full + BWD_STAGES;         // [4] released by the dQ MMA
+  uint64_t* v_empty = k_empty + BWD_STAGES;         // [4] released by the dP MMA
+  uint64_t* sd_full = v_empty + BWD_STAGES;         // [2]
+  uint64_t* sd_empty = sd_full + 2;                 // [2]
+  uint64_t* ds_full = sd_empty + 2;
+  uint64_t* ds_empty = ds_full + 1;
+  uint64_t* done = ds_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -328,14 +360,15 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int mt = n_mt - 1 - int(blockIdx.x);
   const int h = blockIdx.y, b = blockIdx.z;
   const int m0 = mt * 128;
-  const int j_lo = (p.window >= p.T) ? 0 : max(0, (m0 - p.window) / 128);
-  const int j_hi = min((p.T - 1) / 128, (m0 + 127) / 128);
-  const int n_tiles = j_hi - j_lo + 1;
+  const int j_lo = (p.window >= p.T) ? 0 : max(0, (m0 - p.window) / 64);
+  const int j_hi = min((p.T - 1) / 64, (m0 + 127) / 64);
+  const int n_sub = j_hi - j_lo + 1;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
-    mbar_init(sd_full, 1); mbar_init(sd_empty, 4); mbar_init(ds_full, 4); mbar_init(ds_empty, 1); mbar_init(done, 1);
+    for (int i = 0; i < BWD_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sd_full[i], 1); mbar_init(&sd_empty[i], 4); }
+    mbar_init(ds_full, 4); mbar_init(ds_empty, 1); mbar_init(done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -344,7 +377,7 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t TM_S = tmem, TM_DP = tmem + 128, TM_DQ = tmem + 256;
+  const uint32_t TM_S = tmem, TM_DP = tmem + 128, TM_DQ = tmem + 256;   // S[2] x 64, dP[2] x 64, dQ 128
 
   if (warp == 0) {
     if (lane == 0) {
@@ -354,65 +387,62 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tma_load_4d(smem + DqSmem::Q + 16384, &tmQ, q_full, 64, h, m0, b);
       tma_load_4d(smem + DqSmem::DO, &tmDO, q_full, 0, h, m0, b);
       tma_load_4d(smem + DqSmem::DO + 16384, &tmDO, q_full, 64, h, m0, b);
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
-        const int n0 = (j_lo + t) * 128;
+      for (int t = 0; t < n_sub; ++t) {
+        const int s = t % BWD_STAGES;
+        const uint32_t ph = (t / BWD_STAGES) & 1;
+        const int n0 = (j_lo + t) * 64;
         if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag)) break;
-        mbar_expect_tx(&k_full[s], 32768);
-        tma_load_4d(smem + DqSmem::K0 + s * 32768, &tmK, &k_full[s], 0, h, n0, b);
-        tma_load_4d(smem + DqSmem::K0 + s * 32768 + 16384, &tmK, &k_full[s], 64, h, n0, b);
         if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag)) break;
-        mbar_expect_tx(&v_full[s], 32768);
-        tma_load_4d(smem + DqSmem::V0 + s * 32768, &tmV, &v_full[s], 0, h, n0, b);
-        tma_load_4d(smem + DqSmem::V0 + s * 32768 + 16384, &tmV, &v_full[s], 64, h, n0, b);
+        uint8_t* st = smem + DqSmem::KV0 + s * 32768;
+        mbar_expect_tx(&kv_full[s], 32768);
+        tma_load_4d(st, &tmK, &kv_full[s], 0, h, n0, b);
+        tma_load_4d(st + 8192, &tmK, &kv_full[s], 64, h, n0, b);
+        tma_load_4d(st + 16384, &tmV, &kv_full[s], 0, h, n0, b);
+        tma_load_4d(st + 24576, &tmV, &kv_full[s], 64, h, n0, b);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_kmn = make_idesc_bf16(128, 128, false, true);
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, false, true);
       const uint32_t sq = smem_u32(smem + DqSmem::Q), sdo = smem_u32(smem + DqSmem::DO);
       const uint32_t sds = smem_u32(smem + DqSmem::DS);
       bool ok = mbar_wait(q_full, 0, abort_flag);
       auto issue_sd = [&](int t) -> bool {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, abort_flag)) return false;
-        if (!mbar_wait(&v_full[s], ph, abort_flag)) return false;
-        if (!mbar_wait(sd_empty, (t & 1) ^ 1, abort_flag)) return false;
+        const int s = t % BWD_STAGES, buf = t & 1;
+        if (!mbar_wait(&kv_full[s], (t / BWD_STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait(&sd_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + DqSmem::K0 + s * 32768);
-        const uint32_t sv = smem_u32(smem + DqSmem::V0 + s * 32768);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
-          tc_mma_ss(TM_S, make_smem_desc(sq + off, 0, 1024), make_smem_desc(sk + off, 0, 1024), idesc_kk, k > 0);
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
-          tc_mma_ss(TM_DP, make_smem_desc(sdo + off, 0, 1024), make_smem_desc(sv + off, 0, 1024), idesc_kk, k > 0);
-        }
-        tc_commit(&v_empty[s]);
-        tc_commit(sd_full);
-        return true;
-      };
-      if (ok) ok = issue_sd(0);
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        const int s = t & 1;
-        if (!mbar_wait(ds_full, t & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t sk = smem_u32(smem + DqSmem::K0 + s * 32768);
+        const uint32_t sk = smem_u32(smem + DqSmem::KV0 + s * 32768), sv = sk + 16384;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
-          tc_mma_ss(TM_DQ, make_smem_desc(sds + aoff, 0, 1024), make_smem_desc(sk + k * 2048, 16384, 1024), idesc_kmn,
-                    (t > 0 || k > 0) ? 1u : 0u);
+          const uint32_t boff = uint32_t(k >> 2) * 8192u + uint32_t(k & 3) * 32u;
+          tc_mma_ss(TM_S + buf * 64, make_smem_desc(sq + aoff, 0, 1024), make_smem_desc(sk + boff, 0, 1024), idesc_s, k > 0);
         }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
+          const uint32_t boff = uint32_t(k >> 2) * 8192u + uint32_t(k & 3) * 32u;
+          tc_mma_ss(TM_DP + buf * 64, make_smem_desc(sdo + aoff, 0, 1024), make_smem_desc(sv + boff, 0, 1024), idesc_s, k > 0);
+        }
+        tc_commit(&v_empty[s]);
+        tc_commit(&sd_full[buf]);
+        return true;
+      };
+      if (ok) ok = issue_sd(0);
+      for (int t = 0; t < n_sub && ok; ++t) {
+        if (t + 1 < n_sub) { ok = issue_sd(t + 1); if (!ok) break; }
+        const int s = t % BWD_STAGES;
+        if (!mbar_wait(ds_full, t & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + DqSmem::KV0 + s * 32768);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_ss(TM_DQ, make_smem_desc(sds + k * 32, 0, 1024), make_smem_desc(sk + k * 2048, 8192, 1024), idesc_o,
+                    (t > 0 || k > 0) ? 1u : 0u);
         tc_commit(&k_empty[s]);
         tc_commit(ds_empty);
-        if (t + 1 < n_tiles) ok = issue_sd(t + 1);
       }
       if (ok) tc_commit(done);
     }
@@ -427,39 +457,32 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const float dlt = (row < p.T) ? p.delta[stat] : 0.f;
     const uint32_t dsbase = smem_u32(smem + DqSmem::DS);
     bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
-      const int n0 = (j_lo + t) * 128;
-      if (!mbar_wait(sd_full, t & 1, abort_flag)) { ok = false; break; }
+    for (int t = 0; t < n_sub && ok; ++t) {
+      const int n0 = (j_lo + t) * 64;
+      const int buf = t & 1;
+      if (!mbar_wait(&sd_full[buf], (t >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      // dS buffer is free once the dQ MMA of the previous tile has consumed it
-      if (t >= 1 && !mbar_wait(ds_empty, (t - 1) & 1, abort_flag)) { ok = false; break; }
-      const bool need_mask = (n0 + 127 > m0) || (p.window < p.T && n0 < m0 + 127 - p.window) || (n0 + 127 >= p.T);
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
+      const bool need_mask = (n0 + 63 > m0) || (p.window < p.T && n0 < m0 + 127 - p.window) || (n0 + 63 >= p.T) || (m0 + 127 >= p.T);
+      uint32_t ds_pk[32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t sv[32], dv[32];
-        tmem_ld32(TM_S + lane_addr + uint32_t(cc * 32), sv);
-        tmem_ld32(TM_DP + lane_addr + uint32_t(cc * 32), dv);
+        tmem_ld32(TM_S + lane_addr + uint32_t(buf * 64 + cc * 32), sv);
+        tmem_ld32(TM_DP + lane_addr + uint32_t(buf * 64 + cc * 32), dv);
         tmem_wait_ld();
-        float ds[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = n0 + cc * 32 + j;
-          const bool vis = !need_mask || ((key <= row) && (key >= row - p.window) && (key < p.T));
-          const float pr = vis ? fast_exp2(__uint_as_float(sv[j]) * c - lse2) : 0.f;
-          ds[j] = pr * (__uint_as_float(dv[j]) - dlt) * p.scale;
-        }
-#pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          uint4 pk;
-          pk.x = pack_bf16(ds[j], ds[j + 1]); pk.y = pack_bf16(ds[j + 2], ds[j + 3]);
-          pk.z = pack_bf16(ds[j + 4], ds[j + 5]); pk.w = pack_bf16(ds[j + 6], ds[j + 7]);
-          st_sw128(dsbase, 128, r, cc * 32 + j, pk);
-        }
+        if (need_mask) bwd_chunk<true, true, false>(sv, dv, c, p.scale, lse2, dlt, nullptr, nullptr, row, n0 + cc * 32, p.window, p.T, true, nullptr, ds_pk + cc * 16);
+        else bwd_chunk<false, true, false>(sv, dv, c, p.scale, lse2, dlt, nullptr, nullptr, row, n0 + cc * 32, p.window, p.T, true, nullptr, ds_pk + cc * 16);
       }
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sd_empty[buf]);
+      if (t >= 1 && !mbar_wait(ds_empty, (t - 1) & 1, abort_flag)) { ok = false; break; }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        st_sw128(dsbase, 128, r, j * 8, make_uint4(ds_pk[j * 4], ds_pk[j * 4 + 1], ds_pk[j * 4 + 2], ds_pk[j * 4 + 3]));
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(sd_empty); mbar_arrive(ds_full); }
+      if (lane == 0) mbar_arrive(ds_full);
     }
     if (ok && mbar_wait(done, 0, abort_flag)) {
       tc_fence_after();
@@ -489,16 +512,15 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
-// ===============================================================================================
-// Backward, dK / dV: key-stationary, 64-query streaming tiles, transposed scores.
-// ===============================================================================================
+// -----------------------------------------------------------------------------------------------
+// dK / dV: key-stationary, transposed scores (TMEM lane = key, column = query).
+// -----------------------------------------------------------------------------------------------
 struct DkvSmem {
   static constexpr int K = 0, V = 32768;
-  static constexpr int Q0 = 65536;              // 2 stages of 16 KB
-  static constexpr int DO0 = Q0 + 2 * 16384;    // 2 stages of 16 KB
-  static constexpr int PT = DO0 + 2 * 16384;    // 16 KB  P^T  [128 kv x 64 q]
-  static constexpr int DST = PT + 16384;        // 16 KB  dS^T
-  static constexpr int STAT = DST + 16384;      // lse2[2][64], delta[2][64] floats = 1 KB
+  static constexpr int QD0 = 65536;                          // BWD_STAGES x (Q_sub 16 KB + dO_sub 16 KB)
+  static constexpr int PT = QD0 + BWD_STAGES * 32768;        // 16 KB  P^T  [128 keys x 64 q]
+  static constexpr int DST = PT + 16384;                     // 16 KB  dS^T
+  static constexpr int STAT = DST + 16384;                   // lse2[2][64], delta[2][64]
   static constexpr int BAR = STAT + 1024;
   static constexpr int TOTAL = BAR + 256 + 1024;
 };
@@ -509,33 +531,32 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DkvSmem::BAR);
-  uint64_t* kv_full = bars;            // K + V
-  uint64_t* q_full = bars + 1;         // 2 (Q_i and dO_i together)
-  uint64_t* q_empty = bars + 3;        // 2 (freed by the dV/dK MMAs)
-  uint64_t* sd_full = bars + 5;        // 1
-  uint64_t* sd_empty = bars + 6;       // 1
-  uint64_t* pd_full = bars + 7;        // 1  P^T and dS^T written
-  uint64_t* pd_empty = bars + 8;       // 1
-  uint64_t* done = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;                      // [4]
+  uint64_t* q_empty = q_full + BWD_STAGES;          // [4] released by the dV/dK MMAs
+  uint64_t* sd_full = q_empty + BWD_STAGES;         // [2]
+  uint64_t* sd_empty = sd_full + 2;                 // [2]
+  uint64_t* pd_full = sd_empty + 2;
+  uint64_t* pd_empty = pd_full + 1;
+  uint64_t* done = pd_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stat_lse = reinterpret_cast<float*>(smem + DkvSmem::STAT);   // [2][64]
   float* stat_dl = stat_lse + 128;                                     // [2][64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nt = int(blockIdx.x);
   const int h = blockIdx.y, b = blockIdx.z;
-  const int n0 = nt * 128;
-  // visible queries: n0 <= i <= n0 + 127 + window
+  const int n0 = int(blockIdx.x) * 128;
   const int i_lo = n0 / 64;
   const long long last_q = (p.window >= p.T) ? (long long)(p.T - 1) : min((long long)(p.T - 1), (long long)n0 + 127 + p.window);
   const int i_hi = int(last_q / 64);
-  const int n_tiles = i_hi - i_lo + 1;
+  const int n_sub = i_hi - i_lo + 1;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
-    mbar_init(sd_full, 1); mbar_init(sd_empty, 4); mbar_init(pd_full, 4); mbar_init(pd_empty, 1); mbar_init(done, 1);
+    for (int i = 0; i < BWD_STAGES; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sd_full[i], 1); mbar_init(&sd_empty[i], 4); }
+    mbar_init(pd_full, 4); mbar_init(pd_empty, 1); mbar_init(done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -544,7 +565,7 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t TM_S = tmem, TM_DP = tmem + 64, TM_DV = tmem + 128, TM_DK = tmem + 256;
+  const uint32_t TM_S = tmem, TM_DP = tmem + 128, TM_DV = tmem + 256, TM_DK = tmem + 384;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -554,68 +575,64 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tma_load_4d(smem + DkvSmem::K + 16384, &tmK, kv_full, 64, h, n0, b);
       tma_load_4d(smem + DkvSmem::V, &tmV, kv_full, 0, h, n0, b);
       tma_load_4d(smem + DkvSmem::V + 16384, &tmV, kv_full, 64, h, n0, b);
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+      for (int t = 0; t < n_sub; ++t) {
+        const int s = t % BWD_STAGES;
+        const uint32_t ph = (t / BWD_STAGES) & 1;
         const int q0 = (i_lo + t) * 64;
         if (!mbar_wait(&q_empty[s], ph ^ 1, abort_flag)) break;
+        uint8_t* st = smem + DkvSmem::QD0 + s * 32768;
         mbar_expect_tx(&q_full[s], 32768);
-        tma_load_4d(smem + DkvSmem::Q0 + s * 16384, &tmQ, &q_full[s], 0, h, q0, b);
-        tma_load_4d(smem + DkvSmem::Q0 + s * 16384 + 8192, &tmQ, &q_full[s], 64, h, q0, b);
-        tma_load_4d(smem + DkvSmem::DO0 + s * 16384, &tmDO, &q_full[s], 0, h, q0, b);
-        tma_load_4d(smem + DkvSmem::DO0 + s * 16384 + 8192, &tmDO, &q_full[s], 64, h, q0, b);
+        tma_load_4d(st, &tmQ, &q_full[s], 0, h, q0, b);
+        tma_load_4d(st + 8192, &tmQ, &q_full[s], 64, h, q0, b);
+        tma_load_4d(st + 16384, &tmDO, &q_full[s], 0, h, q0, b);
+        tma_load_4d(st + 24576, &tmDO, &q_full[s], 64, h, q0, b);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);     // [128 kv x 64 q]
-      constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, false, true);     // [128 kv x 128 d], B MN-major
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, false, true);
       const uint32_t sk = smem_u32(smem + DkvSmem::K), sv = smem_u32(smem + DkvSmem::V);
       const uint32_t spt = smem_u32(smem + DkvSmem::PT), sdst = smem_u32(smem + DkvSmem::DST);
       bool ok = mbar_wait(kv_full, 0, abort_flag);
       auto issue_sd = [&](int t) -> bool {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(&q_full[s], ph, abort_flag)) return false;
-        if (!mbar_wait(sd_empty, (t & 1) ^ 1, abort_flag)) return false;
+        const int s = t % BWD_STAGES, buf = t & 1;
+        if (!mbar_wait(&q_full[s], (t / BWD_STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait(&sd_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t sq = smem_u32(smem + DkvSmem::Q0 + s * 16384);
-        const uint32_t sdo = smem_u32(smem + DkvSmem::DO0 + s * 16384);
+        const uint32_t sq = smem_u32(smem + DkvSmem::QD0 + s * 32768), sdo = sq + 16384;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {   // K dim = d: A halves are 16 KB apart (128 rows), B halves 8 KB apart (64 rows)
+        for (int k = 0; k < 8; ++k) {
           const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
           const uint32_t boff = uint32_t(k >> 2) * 8192u + uint32_t(k & 3) * 32u;
-          tc_mma_ss(TM_S, make_smem_desc(sk + aoff, 0, 1024), make_smem_desc(sq + boff, 0, 1024), idesc_s, k > 0);
+          tc_mma_ss(TM_S + buf * 64, make_smem_desc(sk + aoff, 0, 1024), make_smem_desc(sq + boff, 0, 1024), idesc_s, k > 0);
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
           const uint32_t boff = uint32_t(k >> 2) * 8192u + uint32_t(k & 3) * 32u;
-          tc_mma_ss(TM_DP, make_smem_desc(sv + aoff, 0, 1024), make_smem_desc(sdo + boff, 0, 1024), idesc_s, k > 0);
+          tc_mma_ss(TM_DP + buf * 64, make_smem_desc(sv + aoff, 0, 1024), make_smem_desc(sdo + boff, 0, 1024), idesc_s, k > 0);
         }
-        tc_commit(sd_full);
+        tc_commit(&sd_full[buf]);
         return true;
       };
       if (ok) ok = issue_sd(0);
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        const int s = t & 1;
+      for (int t = 0; t < n_sub && ok; ++t) {
+        if (t + 1 < n_sub) { ok = issue_sd(t + 1); if (!ok) break; }
+        const int s = t % BWD_STAGES;
         if (!mbar_wait(pd_full, t & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sq = smem_u32(smem + DkvSmem::Q0 + s * 16384);
-        const uint32_t sdo = smem_u32(smem + DkvSmem::DO0 + s * 16384);
+        const uint32_t sq = smem_u32(smem + DkvSmem::QD0 + s * 32768), sdo = sq + 16384;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {   // K dim = 64 queries
+        for (int k = 0; k < 4; ++k)
           tc_mma_ss(TM_DV, make_smem_desc(spt + k * 32, 0, 1024), make_smem_desc(sdo + k * 2048, 8192, 1024), idesc_o,
                     (t > 0 || k > 0) ? 1u : 0u);
-        }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < 4; ++k)
           tc_mma_ss(TM_DK, make_smem_desc(sdst + k * 32, 0, 1024), make_smem_desc(sq + k * 2048, 8192, 1024), idesc_o,
                     (t > 0 || k > 0) ? 1u : 0u);
-        }
         tc_commit(&q_empty[s]);
         tc_commit(pd_empty);
-        if (t + 1 < n_tiles) ok = issue_sd(t + 1);
       }
       if (ok) tc_commit(done);
     }
@@ -628,52 +645,53 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const float c = p.scale * LOG2E;
     const uint32_t ptbase = smem_u32(smem + DkvSmem::PT), dstbase = smem_u32(smem + DkvSmem::DST);
     const long long stat0 = ((long long)b * p.H + h) * p.T;
+    auto load_stat = [&](int t) -> float {   // thread tid < 64: lse2 of query tid; else delta of query tid-64
+      const int qi = (i_lo + t) * 64 + (tid & 63);
+      if (t >= n_sub || qi >= p.T) return (tid < 64) ? INFINITY : 0.f;
+      return (tid < 64) ? p.lse[stat0 + qi] * LOG2E : p.delta[stat0 + qi];
+    };
+    {
+      const float v0 = load_stat(0);
+      (tid < 64 ? stat_lse : stat_dl)[tid & 63] = v0;
+    }
     bool ok = true;
-    for (int t = 0; t < n_tiles; ++t) {
+    for (int t = 0; t < n_sub; ++t) {
       const int q0 = (i_lo + t) * 64;
-      const int sb = t & 1;
-      // stage the 64 per-query statistics of this tile (double buffered by tile parity)
-      {
-        const int qi = q0 + (tid & 63);
-        if (tid < 64) stat_lse[sb * 64 + tid] = (qi < p.T) ? p.lse[stat0 + qi] * LOG2E : INFINITY;
-        else stat_dl[sb * 64 + (tid & 63)] = (qi < p.T) ? p.delta[stat0 + qi] : 0.f;
-      }
-      named_bar_sync(1, 128);
-      if (ok && !mbar_wait(sd_full, t & 1, abort_flag)) ok = false;
-      if (ok && t >= 1 && !mbar_wait(pd_empty, (t - 1) & 1, abort_flag)) ok = false;
-      if (!ok) continue;   // keep taking part in the named barrier so nobody is left waiting
-      tc_fence_after();
-      const bool need_mask = (q0 < n0 + 127) || (p.window < p.T && q0 + 63 > n0 + p.window) || (q0 + 63 >= p.T) || (n0 + 127 >= p.T);
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t sv[32], dv[32];
-        tmem_ld32(TM_S + lane_addr + uint32_t(cc * 32), sv);
-        tmem_ld32(TM_DP + lane_addr + uint32_t(cc * 32), dv);
-        tmem_wait_ld();
-        float pt[32], ds[32];
+      const int buf = t & 1;
+      named_bar_sync(1, 128);                   // statistics of sub-tile t are visible
+      const float next_stat = load_stat(t + 1);  // in flight while this sub-tile is processed
+      if (ok && !mbar_wait(&sd_full[buf], (t >> 1) & 1, abort_flag)) ok = false;
+      if (ok) {
+        tc_fence_after();
+        const bool need_mask = (q0 < n0 + 127) || (p.window < p.T && q0 + 63 > n0 + p.window) || (q0 + 63 >= p.T) || (n0 + 127 >= p.T);
+        uint32_t p_pk[32], ds_pk[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int qi = q0 + cc * 32 + j;
-          const bool vis = !need_mask || ((key <= qi) && (key >= qi - p.window) && (qi < p.T) && (key < p.T));
-          const float pr = vis ? fast_exp2(__uint_as_float(sv[j]) * c - stat_lse[sb * 64 + cc * 32 + j]) : 0.f;
-          pt[j] = pr;
-          ds[j] = pr * (__uint_as_float(dv[j]) - stat_dl[sb * 64 + cc * 32 + j]) * p.scale;
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t sv[32], dv[32];
+          tmem_ld32(TM_S + lane_addr + uint32_t(buf * 64 + cc * 32), sv);
+          tmem_ld32(TM_DP + lane_addr + uint32_t(buf * 64 + cc * 32), dv);
+          tmem_wait_ld();
+          const float* cl = stat_lse + buf * 64 + cc * 32;
+          const float* cd = stat_dl + buf * 64 + cc * 32;
+          if (need_mask) bwd_chunk<true, false, true>(sv, dv, c, p.scale, 0.f, 0.f, cl, cd, key, q0 + cc * 32, p.window, p.T, false, p_pk + cc * 16, ds_pk + cc * 16);
+          else bwd_chunk<false, false, true>(sv, dv, c, p.scale, 0.f, 0.f, cl, cd, key, q0 + cc * 32, p.window, p.T, false, p_pk + cc * 16, ds_pk + cc * 16);
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sd_empty[buf]);
+        if (t >= 1 && !mbar_wait(pd_empty, (t - 1) & 1, abort_flag)) ok = false;
+        if (ok) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          uint4 a, d;
-          a.x = pack_bf16(pt[j], pt[j + 1]); a.y = pack_bf16(pt[j + 2], pt[j + 3]);
-          a.z = pack_bf16(pt[j + 4], pt[j + 5]); a.w = pack_bf16(pt[j + 6], pt[j + 7]);
-          d.x = pack_bf16(ds[j], ds[j + 1]); d.y = pack_bf16(ds[j + 2], ds[j + 3]);
-          d.z = pack_bf16(ds[j + 4], ds[j + 5]); d.w = pack_bf16(ds[j + 6], ds[j + 7]);
-          st_sw128(ptbase, 128, r, cc * 32 + j, a);
-          st_sw128(dstbase, 128, r, cc * 32 + j, d);
+          for (int j = 0; j < 8; ++j) {
+            st_sw128(ptbase, 128, r, j * 8, make_uint4(p_pk[j * 4], p_pk[j * 4 + 1], p_pk[j * 4 + 2], p_pk[j * 4 + 3]));
+            st_sw128(dstbase, 128, r, j * 8, make_uint4(ds_pk[j * 4], ds_pk[j * 4 + 1], ds_pk[j * 4 + 2], ds_pk[j * 4 + 3]));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(pd_full);
         }
       }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) { mbar_arrive(sd_empty); mbar_arrive(pd_full); }
+      (tid < 64 ? stat_lse : stat_dl)[((t + 1) & 1) * 64 + (tid & 63)] = next_stat;
     }
     if (ok && mbar_wait(done, 0, abort_flag)) {
       tc_fence_after();
@@ -792,8 +810,8 @@ extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const v
   {
     CUtensorMap tq, tk, tv, tdo;
     if ((r = make_qkv_tmap(&tq, q, B, T, H, ldq, 128))) return 1000 + r;
-    if ((r = make_qkv_tmap(&tk, k, B, T, H, ldk, 128))) return 1000 + r;
-    if ((r = make_qkv_tmap(&tv, v, B, T, H, ldv, 128))) return 1000 + r;
+    if ((r = make_qkv_tmap(&tk, k, B, T, H, ldk, 64))) return 1000 + r;
+    if ((r = make_qkv_tmap(&tv, v, B, T, H, ldv, 64))) return 1000 + r;
     if ((r = make_qkv_tmap(&tdo, d_o, B, T, H, lddo, 128))) return 1000 + r;
     a.o = dq; a.ldo = lddq;
     dim3 grid((T + 127) / 128, H, B);
