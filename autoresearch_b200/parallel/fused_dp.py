@@ -1,0 +1,105 @@
+"""Data-parallel gradient reduce-scatter and parameter all-gather done by this package's own
+kernels over NVLink peer memory (no library collective on the path).
+
+Per optimizer step, on the compute stream:
+
+1. the fp32 main gradients are cast into this rank's bf16 bucket (symmetric memory);
+2. a bounded flag barrier (kernel; every wait gives up after 2 s of device time and reports
+   through the error word) makes all buckets visible;
+3. ONE kernel reduces this rank's owner shard across all ranks - ``multimem.ld_reduce`` through
+   the NVSwitch when a multicast mapping exists, plain peer loads otherwise - accumulating in
+   fp32, applying the scale and writing the fp32 gradient the optimizer consumes;
+4. the optimizer updates the owned matrices and writes bf16 parameters into the symmetric
+   parameter buffer;
+5. a second barrier, then one kernel pulls every peer's updated shard into the local copy.
+
+The library arm (``LibraryComm``) does the same with ncclReduceScatter / ncclAllGather and is
+what this path is measured against.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import kernels as K
+from .layout import ParamLayout
+from .symm import SymmBuffer
+
+
+class FusedComm:
+    name = "fused"
+
+    def __init__(self, group=None, device=None, bucket_dtype: torch.dtype = torch.bfloat16,
+                 use_multimem: bool = True):
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = torch.device(device if device is not None else torch.cuda.current_device())
+        self.bucket_dtype = bucket_dtype
+        self.use_multimem = use_multimem
+        self._bufs = []
+        self._param: Optional[SymmBuffer] = None
+        self._bucket: Optional[SymmBuffer] = None
+        self._flags: Optional[SymmBuffer] = None
+        self.epoch = 0
+        K.lib()
+
+    # the layout asks for its flat tensors through this hook: parameters go to symmetric memory
+    def allocator(self, numel, dtype, device):
+        if self._param is None and dtype != torch.float32:
+            self._param = SymmBuffer(numel, dtype, device, self.group)
+            return self._param.tensor
+        return torch.zeros(numel, dtype=dtype, device=device)
+
+    def attach(self, layout: ParamLayout) -> None:
+        if self._param is None:  # fp32 parameters (tests): place a bf16-free copy path
+            raise RuntimeError("FusedComm needs bf16 parameters in symmetric memory")
+        self._bucket = SymmBuffer(layout.total, self.bucket_dtype, self.device, self.group)
+        self._flags = SymmBuffer(64, torch.int32, self.device, self.group)
+        for b in (self._param, self._bucket, self._flags):
+            b.rendezvous()
+        dist.barrier(group=self.group)
+        self._param_ptrs = self._ptr_array(self._param.peer_ptrs)
+        self._bucket_ptrs = self._ptr_array(self._bucket.peer_ptrs + [self.rank])
+        self._flag_ptrs = self._ptr_array(self._flags.peer_ptrs)
+        self._mc = self._bucket.multicast_ptr if self.use_multimem else 0
+
+    @staticmethod
+    def _ptr_array(ptrs):
+        arr = (C.c_void_p * len(ptrs))(*ptrs)
+        return arr
+
+    def barrier(self) -> None:
+        self.epoch += 1
+        rc = K.lib().arb_peer_barrier(self._flag_ptrs, self.world, self.rank, self.epoch,
+                                      K.err_flag(self.device).data_ptr(), K._stream())
+        K._check(rc, "peer_barrier")
+
+    def reduce_scatter_grads(self, layout: ParamLayout) -> None:
+        lo, hi = layout.shard_range()
+        src_bf16 = self.bucket_dtype == torch.bfloat16
+        if src_bf16:
+            K.cast_f32_to_bf16(layout.flat_grad, self._bucket.tensor, 1.0)
+        else:
+            self._bucket.tensor.copy_(layout.flat_grad)
+        self.barrier()
+        out = layout.flat_grad[lo:hi]
+        L = K.lib()
+        if self._mc:
+            rc = L.arb_reduce_scatter_multimem(self._mc, lo, hi - lo, int(src_bf16), out.data_ptr(), 1.0, K._stream())
+        else:
+            rc = L.arb_reduce_scatter_peers(self._bucket_ptrs, self.world, lo, hi - lo, int(src_bf16), out.data_ptr(),
+                                            1.0, K._stream())
+        K._check(rc, "reduce_scatter")
+
+    def all_gather_params(self, layout: ParamLayout) -> None:
+        self.barrier()
+        shard_bytes = layout.shard_size * layout.flat_param.element_size()
+        rc = K.lib().arb_all_gather_pull(self._param_ptrs, self.world, self.rank, layout.flat_param.data_ptr(),
+                                         shard_bytes, K._stream())
+        K._check(rc, "all_gather_pull")
+        # peers may start overwriting their shards (next optimizer step) only after everyone has
+        # pulled: the barrier that opens the next reduce-scatter provides that ordering.
