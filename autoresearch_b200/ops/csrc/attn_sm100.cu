@@ -831,3 +831,33 @@ extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const v
   }
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the backward (see attn_noalloc.h): the delta scratch is a
+// file-scope device array.  In host code the array's name is only a handle; its device address
+// comes from cudaGetSymbolAddress, once per device, with that device current.
+// ---------------------------------------------------------------------------------------------
+#include "attn_noalloc.h"
+
+static __device__ __align__(256) float g_attn_noalloc_delta[ARB_ATTN_NOALLOC_MAX_ROWS];
+
+extern "C" int arb_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                    const float* lse, void* dq, void* dk, void* dv, int B, int T, int H,
+                                    long long ldq, long long ldk, long long ldv, long long ldo, long long lddo,
+                                    long long lddq, long long lddk, long long lddv, int window, float scale,
+                                    int* err_flag, cudaStream_t stream) {
+  constexpr int MAX_DEVICES = 64;
+  static float* scratch_of_device[MAX_DEVICES] = {nullptr};
+  if (B <= 0 || T <= 0 || H <= 0) return -3;
+  if ((long long)B * T * H > (long long)ARB_ATTN_NOALLOC_MAX_ROWS) return ARB_ERR_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return ARB_ERR_NOALLOC_SYMBOL;
+  if (scratch_of_device[dev] == nullptr) {
+    float* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_attn_noalloc_delta);
+    if (e != cudaSuccess || ptr == nullptr) return ARB_ERR_NOALLOC_SYMBOL;
+    scratch_of_device[dev] = ptr;
+  }
+  return arb_attn_bwd(q, k, v, o, d_o, lse, dq, dk, dv, scratch_of_device[dev], nullptr, B, T, H, ldq, ldk, ldv, ldo,
+                      lddo, lddq, lddk, lddv, window, scale, err_flag, stream);
+}
