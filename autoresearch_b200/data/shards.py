@@ -26,6 +26,7 @@ _ERR = {-1: "cannot read file", -2: "shard too small for header", -3: "bad magic
 class Shard:
     def __init__(self, path):
         self.lib = native.lib()
+        self.h = None
         h, v, s, n = C.c_void_p(), C.c_uint32(), C.c_uint32(), C.c_uint32()
         rc = self.lib.ar_shard_open(str(path).encode(), C.byref(h), C.byref(v), C.byref(s), C.byref(n))
         if rc != 0:
