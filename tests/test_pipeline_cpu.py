@@ -1,0 +1,75 @@
+"""Pipeline parallelism on CPU ranks (gloo): schedule shape, layer split, and loss parity of a
+2-stage 1F1B run with the single-process run."""
+import json
+import os
+import subprocess
+import sys
+
+from autoresearch_b200.parallel.pipeline import one_f_one_b, split_layers
+
+
+def test_layer_split_gives_remainder_to_early_stages():
+    assert split_layers(30, 4) == [(0, 8), (8, 16), (16, 23), (23, 30)]
+    assert split_layers(30, 8)[0] == (0, 4) and split_layers(30, 8)[-1] == (27, 30)
+    assert split_layers(2, 2) == [(0, 1), (1, 2)]
+
+
+def test_1f1b_schedule_properties():
+    for P in (2, 3, 4):
+        for M in (1, 2, 4, 8):
+            for s in range(P):
+                sch = one_f_one_b(s, P, M)
+                assert [i for k, i in sch if k == "F"] == list(range(M))
+                assert [i for k, i in sch if k == "B"] == list(range(M))
+                for k, i in sch:       # a micro-batch is never back-propagated before its forward
+                    if k == "B":
+                        assert sch.index(("F", i)) < sch.index(("B", i))
+                live = peak = 0
+                for k, _ in sch:
+                    live += 1 if k == "F" else -1
+                    peak = max(peak, live)
+                assert peak <= min(P - s, M)     # activations in flight are bounded by the depth
+
+
+WORKER = r"""
+import os, sys, json, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ARB_ROOT"])
+from autoresearch_b200.config import TrainConfig, model_preset
+from autoresearch_b200.parallel.pipeline import PipelineTrainer
+dist.init_process_group("gloo")
+cfg = model_preset("tiny")
+t = TrainConfig(device_batch_size=2, total_batch_size=8 * 128, max_steps=10, cooldown_steps=3, synthetic_data=True,
+                synthetic_kind="zipf", impl="oracle", cooldown_trigger_file="")
+t.init_scheme = "normal"
+tr = PipelineTrainer(cfg, t, pp=2, device="cpu", quiet=True)
+ls = [tr.loss_on_all_ranks(tr.train_step()) for _ in range(4)]
+if dist.get_rank() == 0:
+    print("RESULT " + json.dumps({"losses": ls, "accum": tr.accum, "bytes": tr.comm_bytes}))
+dist.destroy_process_group()
+"""
+
+
+def test_two_stage_pipeline_matches_single_process(tmp_path):
+    import torch
+    from autoresearch_b200.config import TrainConfig, model_preset
+    from autoresearch_b200.models.init import init_weights
+    from autoresearch_b200.trainer import Trainer
+    cfg = model_preset("tiny")
+    t = TrainConfig(device_batch_size=2, total_batch_size=8 * 128, max_steps=10, cooldown_steps=3, synthetic_data=True,
+                    synthetic_kind="zipf", impl="oracle", cooldown_trigger_file="")
+    one = Trainer(cfg, t, device="cpu", quiet=True)
+    init_weights(one.model, seed=t.seed, scheme="normal")
+    for gi, st in one.opt.state.items():
+        st["master"].copy_(one.layout.group_view(one.layout.flat_param, one.layout.groups[gi]).float())
+    ref = [float(one.train_step()) for _ in range(4)]
+    script = tmp_path / "w.py"
+    script.write_text(WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29656", str(script)],
+                       env=dict(os.environ, ARB_ROOT=root), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert res["accum"] == 4 and res["bytes"] > 0
+    for a, b in zip(ref, res["losses"]):
+        assert abs(a - b) < 2e-3, (ref, res)
