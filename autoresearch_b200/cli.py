@@ -10,7 +10,7 @@ CHECKPOINT_EVERY INIT_WEIGHTS_PATH PIPELINE_RANK PIPELINE_WORLD_SIZE``.
 
 Additions (the reference fixes these at compile time): ``--model PRESET`` (or ``MODEL``),
 ``--impl oracle|baseline|sm100|auto``, ``--synthetic-kind lcg|zipf``, ``--comm fused|nccl``,
-``--metrics-jsonl PATH``, ``--resume``, ``--tp N``.  Under ``torchrun`` the ranks form a
+``--metrics-jsonl PATH``, ``--resume``, ``--tp N``, ``--ep N`` (expert parallel over the DP ranks).  Under ``torchrun`` the ranks form a
 data-parallel group (times ``--pipeline`` stages, times ``--tp``).
 """
 from __future__ import annotations
@@ -56,6 +56,7 @@ def parse_args(argv: List[str], env=None):
         elif a == "--metrics-jsonl": t.metrics_jsonl = val()
         elif a == "--resume": t.resume = True
         elif a == "--tp": tp = int(val())
+        elif a == "--ep": t.parallel.ep = int(val())
         elif a == "train": pass
         i += 1
     if max_steps_cli is not None:

@@ -119,6 +119,10 @@ def _preset(name: str) -> ModelConfig:
     if name == "small":  # GPU smoke size: head_dim 128 so the tensor-core kernels apply
         return ModelConfig(vocab=1024, seq_len=512, d_model=256, n_head=2, head_dim=128,
                            mlp_dim=1024, n_layer=4, ce_chunk=1024, name="small")
+    if name == "small_moe":
+        return ModelConfig(vocab=1024, seq_len=256, d_model=256, n_head=2, head_dim=128,
+                           mlp_dim=1024, n_layer=2, ce_chunk=1024, name="small_moe",
+                           moe=MoEConfig(n_experts=4, top_k=2, mlp_dim_e=512, capacity_factor=2.0))
     if name == "phase1":
         return ModelConfig(vocab=8192, seq_len=2048, d_model=512, n_head=4, head_dim=128,
                            mlp_dim=2048, n_layer=30, name="phase1")
@@ -136,7 +140,7 @@ def _preset(name: str) -> ModelConfig:
     raise KeyError(f"unknown model preset {name!r}")
 
 
-PRESETS = ("tiny", "tiny_moe", "small", "phase1", "phase2", "moe", "wide")
+PRESETS = ("tiny", "tiny_moe", "small", "small_moe", "phase1", "phase2", "moe", "wide")
 
 
 def model_preset(name: str, **overrides) -> ModelConfig:

@@ -24,7 +24,7 @@ from ..ops import reference as R
 
 
 class Block(nn.Module):
-    def __init__(self, cfg: ModelConfig, layer: int, dtype, device, tp: int = 1):
+    def __init__(self, cfg: ModelConfig, layer: int, dtype, device, tp: int = 1, ep: int = 1):
         super().__init__()
         D, M = cfg.d_model, cfg.mlp_dim
         self.layer = layer
@@ -44,8 +44,9 @@ class Block(nn.Module):
         if cfg.is_moe_layer(layer):
             E, ME = cfg.moe.n_experts, cfg.moe.mlp_dim_e
             self.router = nn.Parameter(torch.empty(E, D, **kw))
-            self.expert_fc = nn.Parameter(torch.empty(E, ME, D, **kw))
-            self.expert_proj = nn.Parameter(torch.empty(E, D, ME, **kw))
+            # with expert parallelism a rank holds E / ep experts; the router scores all E
+            self.expert_fc = nn.Parameter(torch.empty(E // ep, ME, D, **kw))
+            self.expert_proj = nn.Parameter(torch.empty(E // ep, D, ME, **kw))
             self.wfc = None
             self.wdn = None
         else:
@@ -57,13 +58,15 @@ class Block(nn.Module):
 class GPT(nn.Module):
     def __init__(self, cfg: ModelConfig, backend=None, dtype=torch.float32, device="cpu",
                  layer_range: Optional[Tuple[int, int]] = None,
-                 has_embedding: bool = True, has_head: bool = True, tp: int = 1):
+                 has_embedding: bool = True, has_head: bool = True, tp: int = 1, ep: int = 1,
+                 ep_rank: int = 0):
         super().__init__()
         from ..ops.backend import get_backend
         self.cfg = cfg
         self.backend = backend if backend is not None else get_backend("oracle")
         self.dtype = dtype
         self.tp = tp
+        self.ep, self.ep_rank = ep, ep_rank
         lo, hi = layer_range if layer_range is not None else (0, cfg.n_layer)
         self.layer_lo, self.layer_hi = lo, hi
         self.has_embedding = has_embedding
@@ -74,7 +77,7 @@ class GPT(nn.Module):
         self.lm_head = nn.Parameter(torch.empty(V, D, **kw)) if has_head else None
         self.resid_lambdas = nn.Parameter(torch.empty(hi - lo, **kw))
         self.x0_lambdas = nn.Parameter(torch.empty(hi - lo, **kw))
-        self.blocks = nn.ModuleList([Block(cfg, l, dtype, device, tp) for l in range(lo, hi)])
+        self.blocks = nn.ModuleList([Block(cfg, l, dtype, device, tp, ep) for l in range(lo, hi)])
         cos, sin = R.rope_tables(cfg.seq_len, cfg.head_dim, cfg.rope_base, device=device)
         # bf16 tables like the reference (brain/src/train.rs:2402-2422) when running in bf16
         tdt = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
@@ -100,9 +103,8 @@ class GPT(nn.Module):
                                    cfg.window(l))
             x, xn = be.proj_add_norm(a, blk.wo, x)
             if blk.router is not None:
-                y, aux = be.moe_mlp(xn, blk.router, blk.expert_fc, blk.expert_proj, cfg.moe)
+                x, aux = be.moe_mlp_add(xn, x, blk, cfg.moe)
                 aux_total = aux if aux_total is None else aux_total + aux
-                x = be.residual_add(x, y)
             else:
                 x = be.mlp_add(xn, blk.wfc, blk.wdn, x)
         self.aux_loss = aux_total

@@ -60,6 +60,10 @@ def init_weights(model, seed: int = 42, scheme: str = "reference", std: float = 
                 p.data.fill_(1.0)
             elif kind == "adamw_l0":
                 p.data.fill_(0.1)
+            elif kind == "muon_expert" and getattr(model, "ep", 1) > 1:
+                full = (cfg.moe.n_experts,) + tuple(p.shape[1:])
+                r0 = model.ep_rank * p.shape[0]
+                put(p, (torch.randn(full, generator=g) * std)[r0:r0 + p.shape[0]])
             else:
                 put(p, torch.randn(p.shape, generator=g) * std)
         return
@@ -82,5 +86,10 @@ def init_weights(model, seed: int = 42, scheme: str = "reference", std: float = 
             blk.ve_gate.data.zero_()
         if blk.router is not None:
             blk.router.data.zero_()
-            put(blk.expert_fc, rng.uniform(blk.expert_fc.shape, s, dt))
+            # draw all E experts so every expert-parallel rank sees the single-process stream
+            el = blk.expert_fc.shape[0]
+            full = (cfg.moe.n_experts,) + tuple(blk.expert_fc.shape[1:])
+            allw = rng.uniform(full, s, dt)
+            r0 = getattr(model, "ep_rank", 0) * el
+            put(blk.expert_fc, allw[r0:r0 + el])
             blk.expert_proj.data.zero_()

@@ -96,6 +96,10 @@ class OracleBackend:
     def mlp_add(self, xn, wfc, wdn, x):
         return self.residual_add(x, self.linear_row(self.linear_col_relu_sq(xn, wfc), wdn))
 
+    def moe_mlp_add(self, xn, x, blk, moe):
+        y, aux = self.moe_mlp(xn, blk.router, blk.expert_fc, blk.expert_proj, moe)
+        return self.residual_add(x, y), aux
+
     def lm_head_ce(self, xf, w, targets, grad_scale):
         N = xf.shape[0]
         parts = []

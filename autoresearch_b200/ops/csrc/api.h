@@ -125,4 +125,26 @@ int arb_all_gather_pull(const void* const* peer_bufs, int world, int rank, void*
 // then waits (<= 2 s) until all of its own flags reach `epoch`.
 int arb_peer_barrier(int* const* peer_flags, int world, int rank, int epoch, int* err_flag, cudaStream_t s);
 
+// ---- mixture of experts (moe.cu) ---------------------------------------------------------------
+// Router: probs [N,E] fp32 = softmax(xn . Wr^T); idx [N,K]; gates [N,K] = p_k / sum_top p.
+int arb_moe_router_fwd(const void* xn, const void* wr, float* probs, int* idx, float* gates, long long N, int D,
+                       int E, int K, cudaStream_t s);
+// d_logits [N,E] bf16 (row stride ld >= E) from d_gates [N,K] and a per-expert constant added to
+// d_probs (aux loss).
+int arb_moe_router_bwd(const float* probs, const int* idx, const float* gates, const float* d_gates,
+                       const float* aux_dp, void* d_logits, long long ld, long long N, int E, int K,
+                       cudaStream_t s);
+// expert_bufs: HOST array of E device pointers (local or NVLink peer mappings) to [rows, D] bf16
+// buffers; row [N,K] = destination row of each slot inside its expert's buffer, -1 = dropped.
+int arb_moe_dispatch(const void* x, void* const* expert_bufs, const int* idx, const int* row, long long N, int K,
+                     int D, int E, cudaStream_t s);
+// out[t] = resid[t] + sum_k gates[t,k] * buf[idx][row]  (resid / gates may be null: 0 / 1)
+int arb_moe_combine_fwd(const void* resid, void* const* expert_bufs, const int* idx, const int* row,
+                        const float* gates, void* out, long long N, int K, int D, int E, cudaStream_t s);
+// dy_buf[idx][row] = gates * d_out[t];  d_gates[t,k] = <y, d_out[t]> where y is y_buf[idx][row]
+// or, when y_rows is given, row t*K+k of that dense [N*K, D] tensor (expert outputs saved by slot).
+int arb_moe_combine_bwd(const void* d_out, void* const* y_bufs, const void* y_rows, void* const* dy_bufs,
+                        const int* idx, const int* row, const float* gates, float* d_gates, long long N, int K, int D,
+                        int E, cudaStream_t s);
+
 }  // extern "C"

@@ -66,6 +66,11 @@ def lib() -> C.CDLL:
         "arb_all_gather_push": [vp, i32, i32, vp, i64, i64, vp],
         "arb_all_gather_pull": [vp, i32, i32, vp, i64, vp],
         "arb_peer_barrier": [vp, i32, i32, i32, vp, vp],
+        "arb_moe_router_fwd": [vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
+        "arb_moe_router_bwd": [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, vp],
+        "arb_moe_dispatch": [vp, vp, vp, vp, i64, i32, i32, i32, vp],
+        "arb_moe_combine_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
+        "arb_moe_combine_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
     }
     for name, args in sigs.items():
         if hasattr(L, name):

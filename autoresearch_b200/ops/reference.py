@@ -148,9 +148,11 @@ def moe_aux_loss(probs, idx, n_experts: int, coeff: float):
 
 
 def moe_capacity(n_tokens: int, n_experts: int, top_k: int, capacity_factor: float) -> int:
+    """Rows per expert buffer: ceil(cf * N * K / E) rounded up to a multiple of 8 (16-byte rows
+    for the tensor-core path); cf <= 0 means unlimited."""
     if capacity_factor <= 0:
         return n_tokens * top_k
-    return int(math.ceil(capacity_factor * n_tokens * top_k / n_experts))
+    return (int(math.ceil(capacity_factor * n_tokens * top_k / n_experts)) + 7) // 8 * 8
 
 
 def moe_keep_mask(idx, n_experts: int, capacity: int):

@@ -435,6 +435,12 @@ class Sm100Backend(OracleBackend):
     def mlp_add(self, xn, wfc, wdn, x):
         return MLPFn.apply(xn, wfc, wdn, x)
 
+    def moe_mlp_add(self, xn, x, blk, moe):
+        """x + MoE(xn) and the auxiliary loss; `self.ep` (an EPContext) switches on expert parallelism."""
+        from ..models.moe import MoEFn
+        return MoEFn.apply(xn, x, blk.router, blk.expert_fc, blk.expert_proj, moe.top_k, moe.aux_coeff,
+                           moe.capacity_factor, getattr(self, "ep", None))
+
     def lm_head_ce(self, xf, w, targets, grad_scale):
         need = torch.is_grad_enabled() and (xf.requires_grad or w.requires_grad)
         chunk = max(self.ce_chunk, self.big_ce_chunk)

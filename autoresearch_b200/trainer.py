@@ -62,7 +62,9 @@ class Trainer:
         self.impl = impl
         self.dtype = torch.bfloat16 if on_gpu and impl != "oracle" else torch.float32
         self.backend = get_backend(impl, mcfg)
-        self.model = GPT(mcfg, self.backend, dtype=self.dtype, device=self.device)
+        self.ep = self.world if (tcfg.parallel.ep > 1 and mcfg.moe is not None and self.world > 1) else 1
+        self.model = GPT(mcfg, self.backend, dtype=self.dtype, device=self.device, ep=self.ep,
+                         ep_rank=self.rank if self.ep > 1 else 0)
         if tcfg.load_checkpoint:
             st = ckpt.load_weights(self.model, tcfg.load_checkpoint, strict=True)
             self._say(f"Loaded checkpoint {tcfg.load_checkpoint}: {st}")
@@ -76,13 +78,25 @@ class Trainer:
         # ---- flat storage, communicator, optimizer ---------------------------------------
         self.comm = self._make_comm()
         alloc = getattr(self.comm, "allocator", None)
-        self.layout = ParamLayout(self.model.named_matrix_groups(), self.world, self.rank,
-                                  allocator=alloc)
+        groups = self.model.named_matrix_groups()
+        expert_groups = [g for g in groups if g[2] == "muon_expert"] if self.ep > 1 else []
+        dense_groups = [g for g in groups if g not in expert_groups]
+        self.layout = ParamLayout(dense_groups, self.world, self.rank, allocator=alloc)
         if hasattr(self.comm, "attach"):
             self.comm.attach(self.layout)
         kernels = getattr(self.backend, "optim_kernels", None)
         self.opt = MuonAdamW(self.layout, tcfg.schedule_cfg, mcfg.d_model,
                              kernels=kernels() if callable(kernels) else None)
+        # expert-parallel experts are unique to their rank: no reduction, a rank-local optimizer
+        self.expert_layout = self.expert_opt = None
+        if expert_groups:
+            self.expert_layout = ParamLayout(expert_groups, 1, 0)
+            self.expert_opt = MuonAdamW(self.expert_layout, tcfg.schedule_cfg, mcfg.d_model,
+                                        kernels=kernels() if callable(kernels) else None)
+            from .parallel.ep import EPContext
+            self.backend.ep = EPContext(self.group if self.group is not None else dist.group.WORLD, self.device,
+                                        mcfg.moe.n_experts, mcfg.d_model, self.micro_batch * mcfg.seq_len,
+                                        mcfg.moe.top_k, mcfg.moe.capacity_factor)
         self.wsd = WSDState(tcfg.max_steps, tcfg.cooldown_steps, tcfg.schedule_cfg.warmdown_ratio,
                             warmup_steps=int(round(tcfg.schedule_cfg.warmup_ratio * (tcfg.max_steps or 0))))
         self.step = 0
@@ -179,6 +193,8 @@ class Trainer:
         self.timer.mark("start")
         self.wsd.update(self.step, triggered=self._cooldown_triggered())
         self.layout.zero_grad()
+        if self.expert_layout is not None:
+            self.expert_layout.zero_grad()
         self._loss_acc.zero_()
         tokens_micro = self.micro_batch * m.seq_len
         grad_scale = 1.0 / (tokens_micro * self.accum * self.world)
@@ -190,6 +206,8 @@ class Trainer:
             scaled, per_tok = self.model(ids, tgt, grad_scale=grad_scale)
             scaled.backward()
             self.layout.accumulate_autograd_grads()
+            if self.expert_layout is not None:
+                self.expert_layout.accumulate_autograd_grads()
             self._loss_acc += per_tok.sum() / (tokens_micro * self.accum)
         self.timer.mark("bwd_end")
         if t.diagnostic_steps is not None:
@@ -200,7 +218,10 @@ class Trainer:
             return self._loss_acc
         self.comm.reduce_scatter_grads(self.layout)
         progress = self.wsd.progress(self.step)
-        self.opt.step(self.step + 1, progress, warmup_multiplier(self.step + 1, self.wsd.warmup_steps))
+        wm = warmup_multiplier(self.step + 1, self.wsd.warmup_steps)
+        self.opt.step(self.step + 1, progress, wm)
+        if self.expert_opt is not None:
+            self.expert_opt.step(self.step + 1, progress, wm)
         self.comm.all_gather_params(self.layout)
         self.timer.mark("opt_end")
         self.timer.mark("end")
