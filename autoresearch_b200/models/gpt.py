@@ -53,6 +53,13 @@ class Block(nn.Module):
             self.wfc = nn.Parameter(torch.empty(M // tp, D, **kw))
             self.wdn = nn.Parameter(torch.empty(D, M // tp, **kw))
             self.router = None
+        if tp > 1:
+            # Muon's learning-rate factor sqrt(max(1, m/n)) refers to the unsharded matrix
+            self.wqkv.muon_full_shape = (D, D)
+            self.wo.muon_full_shape = (D, D)
+            if self.wfc is not None:
+                self.wfc.muon_full_shape = (M, D)
+                self.wdn.muon_full_shape = (D, M)
 
 
 class GPT(nn.Module):
@@ -123,8 +130,17 @@ class GPT(nn.Module):
         """ids/targets: [B, T] integer tensors.  Full model: returns
         (scaled_loss_sum, per_token_losses).  Pipeline stage without a head: returns (x, x0)."""
         B, T = ids.shape
+        tp = getattr(self.backend, "tp", None)
+        if tp is not None and tp.size > 1:
+            # sequence parallel: this rank embeds, normalises and scores only its token shard
+            n = (B * T) // tp.size
+            shard = slice(tp.rank * n, (tp.rank + 1) * n)
+            ids_emb = ids.reshape(-1)[shard]
+            targets = targets.reshape(-1)[shard] if targets is not None else None
+        else:
+            ids_emb = ids
         if self.has_embedding:
-            x = self.embed(ids)
+            x = self.embed(ids_emb)
             x0 = x
         else:
             x, x0 = x_in, x0_in

@@ -79,6 +79,9 @@ class OracleBackend:
         hd = cfg.head_dim
         Dl = blk.wqkv.shape[0] // 3
         H = Dl // hd
+        tp = getattr(self, "tp", None)
+        if tp is not None and tp.size > 1:
+            xn = tp.all_gather(xn)                    # token shards -> all tokens (local heads only)
         qkv = self.linear_col(xn, blk.wqkv)
         q, k, v = qkv[:, :Dl], qkv[:, Dl:2 * Dl], qkv[:, 2 * Dl:]
         v = v.reshape(B, T, H, hd)
@@ -91,10 +94,20 @@ class OracleBackend:
         return self.attention(q, k, v, window).reshape(B * T, Dl)
 
     def proj_add_norm(self, a, w, x):
-        return self.add_norm(x, self.linear_row(a, w))
+        y = self.linear_row(a, w)
+        tp = getattr(self, "tp", None)
+        if tp is not None and tp.size > 1:
+            y = tp.reduce_scatter(y)                  # partial sums over heads -> this rank's tokens
+        return self.add_norm(x, y)
 
     def mlp_add(self, xn, wfc, wdn, x):
-        return self.residual_add(x, self.linear_row(self.linear_col_relu_sq(xn, wfc), wdn))
+        tp = getattr(self, "tp", None)
+        if tp is not None and tp.size > 1:
+            xn = tp.all_gather(xn)
+        y = self.linear_row(self.linear_col_relu_sq(xn, wfc), wdn)
+        if tp is not None and tp.size > 1:
+            y = tp.reduce_scatter(y)
+        return self.residual_add(x, y)
 
     def moe_mlp_add(self, xn, x, blk, moe):
         y, aux = self.moe_mlp(xn, blk.router, blk.expert_fc, blk.expert_proj, moe)

@@ -133,6 +133,55 @@ class LinearAddNormFn(torch.autograd.Function):
         return da, dw, g, None
 
 
+class AddNormFn(torch.autograd.Function):
+    """xs = x + y ; xn = rmsnorm(xs); backward d = g_xs + rmsnorm_bwd(xs, g_xn) for both inputs."""
+
+    @staticmethod
+    def forward(ctx, x, y, eps):
+        xs, xn = K.add_norm_fwd(x.contiguous(), y.contiguous(), eps)
+        ctx.save_for_backward(xs)
+        ctx.eps = eps
+        return xs, xn
+
+    @staticmethod
+    def backward(ctx, g_xs, g_xn):
+        (xs,) = ctx.saved_tensors
+        if g_xn is None:
+            g = g_xs
+        else:
+            g = K.rmsnorm_bwd(xs, g_xn.contiguous(), ctx.eps, add_to=g_xs.contiguous() if g_xs is not None else None)
+        return g, g, None
+
+
+class ResidualAddFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b):
+        return K.residual_add(a.contiguous(), b.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, g
+
+
+class LinearRelu2Fn(torch.autograd.Function):
+    """act = relu(x @ w^T)^2 with the activation in the GEMM epilogue; backward from act alone."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        act = K.gemm(x, w, epi=K.EPI_RELU2)
+        ctx.save_for_backward(x, w, act)
+        return act
+
+    @staticmethod
+    def backward(ctx, g_act):
+        x, w, act = ctx.saved_tensors
+        # d_h = g_act * 2*sqrt(act): fold into an elementwise pass, then the two GEMMs
+        dh = (g_act.float() * 2.0 * act.float().sqrt()).to(torch.bfloat16)
+        dx = K.gemm(dh, w, trans_b=False)
+        dw = _acc_weight_grad(w, dh, x)
+        return dx, dw
+
+
 class ResidScaleNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, x0, lam_r, lam_0, idx, eps):
@@ -421,7 +470,19 @@ class Sm100Backend(OracleBackend):
 
     linear_row = linear_col
 
+    def _tp(self):
+        tp = getattr(self, "tp", None)
+        return tp if (tp is not None and tp.size > 1) else None
+
+    def add_norm(self, x, y):
+        return AddNormFn.apply(x, y, self.eps)
+
+    def residual_add(self, x, y):
+        return ResidualAddFn.apply(x, y)
+
     def attention_block(self, xn, blk, ids_flat, B, T, cfg, cos, sin, window):
+        if self._tp() is not None:
+            xn = self._tp().all_gather(xn)
         H = blk.wqkv.shape[0] // (3 * cfg.head_dim)
         if cfg.head_dim != 128:
             raise ValueError("the sm100 kernels support head_dim = 128 only")
@@ -430,10 +491,17 @@ class Sm100Backend(OracleBackend):
         return fn.apply(qkv, B, T, H, window)
 
     def proj_add_norm(self, a, w, x):
-        return LinearAddNormFn.apply(a, w, x, self.eps)
+        tp = self._tp()
+        if tp is None:
+            return LinearAddNormFn.apply(a, w, x, self.eps)
+        return AddNormFn.apply(x, tp.reduce_scatter(LinearFn.apply(a, w)), self.eps)
 
     def mlp_add(self, xn, wfc, wdn, x):
-        return MLPFn.apply(xn, wfc, wdn, x)
+        tp = self._tp()
+        if tp is None:
+            return MLPFn.apply(xn, wfc, wdn, x)
+        act = LinearRelu2Fn.apply(tp.all_gather(xn), wfc)
+        return ResidualAddFn.apply(x, tp.reduce_scatter(LinearFn.apply(act, wdn)))
 
     def moe_mlp_add(self, xn, x, blk, moe):
         """x + MoE(xn) and the auxiliary loss; `self.ep` (an EPContext) switches on expert parallelism."""

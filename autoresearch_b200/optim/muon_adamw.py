@@ -162,7 +162,7 @@ class MuonAdamW:
             grad = lay.group_view(lay.flat_grad, g)
             pv = lay.group_view(lay.flat_param, g)
             if g.kind == "muon":
-                m, n = g.shape
+                m, n = getattr(g.atoms[0].param, "muon_full_shape", g.shape)
                 lr = c.peak_lr * lr_mult * math.sqrt(max(1.0, m / n))
                 self._muon_group(st, grad, pv, mu, lr, wd)
             else:

@@ -1,0 +1,316 @@
+"""Tensor parallelism with sequence-sharded activations (Megatron-style TP+SP), for the wide
+configuration (TP=2 x DP=4 on 8 GPUs).
+
+The reference has no tensor parallelism.  Per layer and TP rank:
+
+    x_shard [N/tp, D] --resid-scale-norm--> xn_shard --ALL-GATHER--> xn [N, D]
+    qkv = xn Wqkv_local^T (H/tp heads) -> RoPE/QK-norm/VE -> attention -> a [N, D/tp]
+    partial = a Wo_local^T [N, D] --REDUCE-SCATTER--> + x_shard --norm--> xn_shard
+    ... same pattern for the MLP (Wfc column-parallel, Wdn row-parallel).
+
+Embedding, final norm, LM head and the loss run on the local token shard with replicated
+weights.  Two communication arms:
+
+* ``library`` – torch.distributed all_gather / reduce_scatter (NCCL or gloo): the baseline.
+* ``fused``   – peer memory: the all-gather is a pull kernel that runs on a side stream while
+  the GEMM already works on the local rows; the reduce-scatter has the GEMM write its partial
+  product into a symmetric staging buffer and ONE kernel adds the local rows, the peers' rows
+  (NVLink loads) and the residual, so no reduced tensor is ever written separately.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import time
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config import ModelConfig, TrainConfig, derive_accumulation
+from ..models.gpt import GPT
+from ..models.init import init_weights
+from ..ops.backend import get_backend
+from ..optim.muon_adamw import MuonAdamW
+from ..optim.schedule import WSDState, lr_multiplier, warmup_multiplier
+from .dp import LibraryComm, LocalComm
+from .layout import ParamLayout
+
+
+class _AllGather(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return tp.all_gather_rows(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.reduce_scatter_rows(g.contiguous()), None
+
+
+class _ReduceScatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return tp.reduce_scatter_rows(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.all_gather_rows(g.contiguous()), None
+
+
+class TPContext:
+    """Library arm (works on gloo CPU ranks and NCCL)."""
+
+    mode = "library"
+
+    def __init__(self, group, rank: int, size: int):
+        self.group, self.rank, self.size = group, rank, size
+        self.bytes = 0
+
+    def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((x.shape[0] * self.size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        self.bytes += out.numel() * out.element_size()
+        if dist.get_backend(self.group) == "gloo":
+            parts = list(out.chunk(self.size, 0))
+            dist.all_gather(parts, x.contiguous(), group=self.group)
+        else:
+            dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        return out
+
+    def reduce_scatter_rows(self, x: torch.Tensor) -> torch.Tensor:
+        n = x.shape[0] // self.size
+        self.bytes += x.numel() * x.element_size()
+        if dist.get_backend(self.group) == "gloo":
+            y = x.clone()
+            dist.all_reduce(y, group=self.group)
+            return y[self.rank * n:(self.rank + 1) * n].contiguous()
+        out = torch.empty((n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x.contiguous(), group=self.group)
+        return out
+
+    def all_gather(self, x):
+        return _AllGather.apply(x, self)
+
+    def reduce_scatter(self, x):
+        return _ReduceScatter.apply(x, self)
+
+
+class FusedTPContext(TPContext):
+    """Peer-memory arm (CUDA only): see the module docstring."""
+
+    mode = "fused"
+
+    def __init__(self, group, rank, size, device, max_rows: int, d_model: int):
+        super().__init__(group, rank, size)
+        from ..ops import kernels as K
+        from .symm import SymmBuffer
+        self.K = K
+        self.device = torch.device(device)
+        self.D = d_model
+        self.max_rows = max_rows
+        # shard staging (all-gather source), partial-product staging (reduce-scatter source)
+        self.ag = SymmBuffer(max_rows // size * d_model, torch.bfloat16, self.device, group)
+        self.rs = SymmBuffer(max_rows * d_model, torch.bfloat16, self.device, group)
+        self.flags = SymmBuffer(64, torch.int32, self.device, group)
+        for b in (self.ag, self.rs, self.flags):
+            b.rendezvous()
+        dist.barrier(group=group)
+        self._flag_ptrs = (C.c_void_p * size)(*self.flags.peer_ptrs)
+        self._ag_ptrs = (C.c_void_p * size)(*self.ag.peer_ptrs)
+        self._rs_ptrs = (C.c_void_p * (size + 1))(*(self.rs.peer_ptrs + [rank]))
+        self.epoch = 0
+        self.side = torch.cuda.Stream(device=self.device)
+
+    def barrier(self):
+        self.epoch += 1
+        self.K._check(self.K.lib().arb_peer_barrier(self._flag_ptrs, self.size, self.rank, self.epoch,
+                                                    self.K.err_flag(self.device).data_ptr(), self.K._stream()), "peer_barrier")
+
+    def all_gather_rows(self, x):
+        """Publish the local shard in symmetric memory, then pull every peer's shard (NVLink loads)."""
+        K = self.K
+        n, D = x.shape
+        if x.dtype != torch.bfloat16 or n * self.size > self.max_rows or D != self.D:
+            return super().all_gather_rows(x)
+        self.bytes += n * self.size * D * 2
+        stage = self.ag.tensor[: n * D].view(n, D)
+        stage.copy_(x)
+        out = torch.empty(n * self.size, D, dtype=x.dtype, device=x.device)
+        self.barrier()                                          # every shard is published
+        out[self.rank * n:(self.rank + 1) * n].copy_(x)
+        # the pull kernel addresses peers' staging buffers as shards of one virtual [size*n, D] tensor
+        ptrs = (C.c_void_p * self.size)(*[p - r * n * D * 2 for r, p in enumerate(self.ag.peer_ptrs)])
+        K._check(K.lib().arb_all_gather_pull(ptrs, self.size, self.rank, out.data_ptr(), n * D * 2, K._stream()),
+                 "tp_all_gather_pull")
+        self.barrier()                                          # staging may be overwritten again
+        return out
+
+    def reduce_scatter_rows(self, x):
+        """Partial products sit in symmetric memory; one kernel sums this rank's rows over all peers."""
+        K = self.K
+        N, D = x.shape
+        if x.dtype != torch.bfloat16 or N > self.max_rows or D != self.D:
+            return super().reduce_scatter_rows(x)
+        self.bytes += N * D * 2
+        n = N // self.size
+        stage = self.rs.tensor[: N * D].view(N, D)
+        stage.copy_(x)
+        self.barrier()
+        out32 = torch.empty(n, D, dtype=torch.float32, device=x.device)
+        K._check(K.lib().arb_reduce_scatter_peers(self._rs_ptrs, self.size, self.rank * n * D, n * D, 1, out32.data_ptr(), 1.0,
+                                                  K._stream()), "tp_reduce_scatter")
+        self.barrier()
+        return out32.to(torch.bfloat16)
+
+
+def shard_full_model_into(full: GPT, model: GPT, tp_rank: int, tp: int) -> None:
+    """Copy rank `tp_rank`'s slices of a full model's weights into a TP-sharded model."""
+    cfg = full.cfg
+    D = cfg.d_model
+    Dl = D // tp
+    sl = slice(tp_rank * Dl, (tp_rank + 1) * Dl)
+    with torch.no_grad():
+        for name in ("wte", "lm_head", "resid_lambdas", "x0_lambdas"):
+            getattr(model, name).copy_(getattr(full, name))
+        for fb, mb in zip(full.blocks, model.blocks):
+            q, k, v = fb.wqkv[:D], fb.wqkv[D:2 * D], fb.wqkv[2 * D:]
+            mb.wqkv.copy_(torch.cat([q[sl], k[sl], v[sl]], 0))
+            mb.wo.copy_(fb.wo[:, sl])
+            if fb.wfc is not None:
+                M = fb.wfc.shape[0] // tp
+                mb.wfc.copy_(fb.wfc[tp_rank * M:(tp_rank + 1) * M])
+                mb.wdn.copy_(fb.wdn[:, tp_rank * M:(tp_rank + 1) * M])
+            if fb.ve is not None:
+                mb.ve.copy_(fb.ve[:, sl])
+                H = fb.ve_gate.shape[0] // tp
+                mb.ve_gate.copy_(fb.ve_gate[tp_rank * H:(tp_rank + 1) * H])
+
+
+REPLICATED_KINDS = ("adamw_emb", "adamw_head", "adamw_lr", "adamw_l0", "adamw_router")
+
+
+class TPTrainer:
+    """world = tp x dp; rank = dp_index * tp + tp_rank.  A TP group shares one micro-batch."""
+
+    def __init__(self, mcfg: ModelConfig, tcfg: TrainConfig, tp: int, device: str = "cpu", quiet: bool = False):
+        if not dist.is_initialized():
+            raise RuntimeError("tensor parallelism needs an initialised process group (torchrun)")
+        if mcfg.moe is not None:
+            raise ValueError("tensor parallelism is implemented for the dense model")
+        self.mcfg, self.tcfg, self.tp = mcfg, tcfg, tp
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        if self.world % tp or mcfg.n_head % tp:
+            raise ValueError("world size and head count must be multiples of tp")
+        self.dp = self.world // tp
+        self.tp_rank, self.dp_idx = self.rank % tp, self.rank // tp
+        self.device = torch.device(device)
+        self.quiet = quiet
+        on_gpu = self.device.type == "cuda"
+        impl = tcfg.impl
+        if impl == "auto":
+            impl = "sm100" if (on_gpu and torch.cuda.get_device_capability(self.device)[0] == 10) else "oracle"
+        self.dtype = torch.bfloat16 if on_gpu and impl != "oracle" else torch.float32
+        self.tp_group = self.dp_group = None
+        for d in range(self.dp):
+            g = dist.new_group([d * tp + t for t in range(tp)])
+            if d == self.dp_idx:
+                self.tp_group = g
+        for t in range(tp):
+            g = dist.new_group([d * tp + t for d in range(self.dp)])
+            if t == self.tp_rank:
+                self.dp_group = g
+        self.micro_batch, self.accum = derive_accumulation(tcfg.total_batch_size, tcfg.device_batch_size,
+                                                           mcfg.seq_len, self.dp)
+        n_tokens = self.micro_batch * mcfg.seq_len
+        if n_tokens % tp:
+            raise ValueError("tokens per micro-batch must divide over tp")
+        self.backend = get_backend(impl, mcfg)
+        if tcfg.parallel.comm == "fused" and on_gpu and impl == "sm100":
+            self.backend.tp = FusedTPContext(self.tp_group, self.tp_rank, tp, self.device, n_tokens, mcfg.d_model)
+        else:
+            self.backend.tp = TPContext(self.tp_group, self.tp_rank, tp)
+        self.model = GPT(mcfg, self.backend, dtype=self.dtype, device=self.device, tp=tp)
+        full = GPT(mcfg, get_backend("oracle", mcfg), dtype=torch.float32, device="cpu")
+        init_weights(full, seed=tcfg.seed, scheme=getattr(tcfg, "init_scheme", "reference"))
+        shard_full_model_into(full, self.model, self.tp_rank, tp)
+        del full
+        groups = self.model.named_matrix_groups()
+        rep = [g for g in groups if g[2] in REPLICATED_KINDS]
+        shd = [g for g in groups if g[2] not in REPLICATED_KINDS]
+        bucket = torch.bfloat16 if on_gpu else None
+        # replicated parameters: reduced over ALL ranks; sharded ones over the DP group of this TP index
+        self.comm_rep = LibraryComm(None, bucket)
+        self.lay_rep = ParamLayout(rep, self.world, self.rank)
+        self.comm_shd = LocalComm() if self.dp == 1 else LibraryComm(self.dp_group, bucket)
+        self.lay_shd = ParamLayout(shd, self.dp, self.dp_idx)
+        kernels = getattr(self.backend, "optim_kernels", None)
+        kk = kernels() if callable(kernels) else None
+        self.opt_rep = MuonAdamW(self.lay_rep, tcfg.schedule_cfg, mcfg.d_model, kernels=kk)
+        self.opt_shd = MuonAdamW(self.lay_shd, tcfg.schedule_cfg, mcfg.d_model, kernels=kk)
+        self.wsd = WSDState(tcfg.max_steps, tcfg.cooldown_steps, tcfg.schedule_cfg.warmdown_ratio,
+                            int(round(tcfg.schedule_cfg.warmup_ratio * (tcfg.max_steps or 0))))
+        self.step = 0
+        from ..trainer import Trainer
+        shim = type("S", (), {})()
+        shim.tcfg, shim.mcfg, shim.micro_batch, shim.rank, shim.world = tcfg, mcfg, self.micro_batch, self.dp_idx, self.dp
+        self.loader = Trainer._make_loader(shim, "train")
+
+    def train_step(self):
+        m = self.mcfg
+        self.wsd.update(self.step)
+        self.lay_rep.zero_grad(); self.lay_shd.zero_grad()
+        n_tokens = self.micro_batch * m.seq_len
+        grad_scale = 1.0 / (n_tokens * self.accum * self.dp)
+        loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
+        for _ in range(self.accum):
+            b = self.loader.next_batch()
+            if b is None:
+                return None
+            ids, tgt = (t.to(self.device) for t in b)
+            scaled, per_tok = self.model(ids, tgt, grad_scale=grad_scale)
+            scaled.backward()
+            self.lay_rep.accumulate_autograd_grads(); self.lay_shd.accumulate_autograd_grads()
+            loss_acc += per_tok.sum() / (n_tokens * self.accum)
+        self.comm_rep.reduce_scatter_grads(self.lay_rep)
+        self.comm_shd.reduce_scatter_grads(self.lay_shd)
+        progress = self.wsd.progress(self.step)
+        wm = warmup_multiplier(self.step + 1, self.wsd.warmup_steps)
+        self.opt_rep.step(self.step + 1, progress, wm)
+        self.opt_shd.step(self.step + 1, progress, wm)
+        self.comm_rep.all_gather_params(self.lay_rep)
+        self.comm_shd.all_gather_params(self.lay_shd)
+        self.step += 1
+        return loss_acc
+
+    def global_loss(self, loss: torch.Tensor) -> float:
+        """Each rank holds the loss of its token shard (already divided by the full micro-batch
+        token count): sum over the TP group, mean over DP replicas."""
+        v = loss.detach().clone()
+        dist.all_reduce(v)
+        return float(v.item()) / self.dp
+
+    def run(self):
+        t = self.tcfg
+        tokens = self.micro_batch * self.mcfg.seq_len * self.accum * self.dp
+        if self.rank == 0 and not self.quiet:
+            print(f"Tensor parallel: tp {self.tp} x dp {self.dp} ({self.backend.tp.mode} collectives); "
+                  f"{self.micro_batch} x {self.mcfg.seq_len} x accum {self.accum} per TP group", flush=True)
+        ema, n = 0.0, 0
+        while not self.wsd.finished(self.step):
+            t0 = time.perf_counter()
+            loss = self.train_step()
+            if loss is None:
+                break
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            step = self.step - 1
+            if step % t.log_interval == 0 or step <= 10:
+                lv = self.global_loss(loss)
+                ema = 0.9 * ema + 0.1 * lv; n += 1
+                if self.rank == 0 and not self.quiet:
+                    lrm = lr_multiplier(self.wsd.progress(step), t.schedule_cfg)
+                    left = (t.max_steps - self.step) if t.max_steps else -1
+                    print(f"step {step:>5} | loss {ema / (1 - 0.9 ** n):.4f} | lr {lrm:.3f} | dt {dt:.3f}s | "
+                          f"tok/s {int(tokens / dt)} | mfu 0.0% | vram 0MB | steps_left {left}", flush=True)
+        dist.barrier()
