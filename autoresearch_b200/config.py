@@ -258,6 +258,7 @@ class TrainConfig:
     cooldown_trigger_file: str = "/tmp/autoresearch_cooldown"
     metrics_jsonl: Optional[str] = None
     resume: bool = False
+    heartbeat_timeout_s: float = 0.0  # > 0: watch peer liveness through the process group's store
     parallel: ParallelConfig = field(default_factory=ParallelConfig)
 
     @staticmethod
@@ -285,6 +286,7 @@ class TrainConfig:
             init_weights_path=env.get("INIT_WEIGHTS_PATH") or None,
             num_train_shards=(i("NUM_TRAIN_SHARDS", -1) if i("NUM_TRAIN_SHARDS", -1) >= 0 else None),
             synthetic_data=env.get("SYNTHETIC", "") in ("1", "true"),
+            heartbeat_timeout_s=float(env.get("HEARTBEAT_TIMEOUT", "0") or 0),
             schedule_cfg=ScheduleConfig.from_env(env),
         )
 

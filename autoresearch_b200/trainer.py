@@ -119,6 +119,13 @@ class Trainer:
         self.total_train_s = 0.0
         self.steady_steps = 0
         self.h2d_bytes_per_step = 2 * B * T * 4 * self.accum
+        self.hb = None
+        if self.dist and self.world > 1 and tcfg.heartbeat_timeout_s > 0:
+            from .parallel.heartbeat import Heartbeat
+            store = dist.distributed_c10d._get_default_store()
+            self.hb = Heartbeat(store, dist.get_rank(), dist.get_world_size(),
+                                interval_s=max(tcfg.heartbeat_timeout_s / 10.0, 0.05),
+                                timeout_s=tcfg.heartbeat_timeout_s).start()
         if tcfg.resume and tcfg.checkpoint_dir:
             self._resume()
 
@@ -190,6 +197,8 @@ class Trainer:
         """One optimizer step (accum micro-steps).  Returns the mean loss as a device
         scalar tensor (no host sync) or None when the data source is exhausted."""
         m, t = self.mcfg, self.tcfg
+        if self.hb is not None:
+            self.hb.check()          # a silent peer ends the run here, before any collective waits for it
         self.timer.mark("start")
         self.wsd.update(self.step, triggered=self._cooldown_triggered())
         self.layout.zero_grad()

@@ -1,0 +1,48 @@
+import json
+
+import torch
+
+from autoresearch_b200.tools import compare_train, diagnostic, generate_init_weights, monitor
+
+
+def test_generated_init_weights_are_reproducible_and_loadable(tmp_path):
+    from autoresearch_b200.ckpt.safetensors_io import load_file
+    a, b = tmp_path / "a.safetensors", tmp_path / "b.safetensors"
+    n = generate_init_weights.generate("tiny", str(a))
+    generate_init_weights.generate("tiny", str(b))
+    assert n > 10 and a.read_bytes() == b.read_bytes()
+    sd = load_file(str(a))
+    assert sd["h.0.attn.c_proj.weight"].abs().max() == 0            # zero-initialised projection
+    s = 0.68 * 3 ** 0.5 / 64 ** 0.5
+    assert sd["h.0.attn.c_q.weight"].float().abs().max() <= s * 1.01
+    assert abs(sd["wte.weight"].float().std().item() - 1.0) < 0.05
+    assert sd["resid_lambdas"].tolist() == [1.0, 1.0] and abs(sd["x0_lambdas"][0].item() - 0.1) < 1e-3
+
+
+def test_oracle_dump_files(tmp_path):
+    recs = diagnostic.run("tiny", str(tmp_path), n_batches=2, batch_size=2)
+    assert len(recs) == 2 and len(recs[0]["layers"]) == 2 and recs[0]["layers"][0]["q"] > 0
+    assert (tmp_path / "oracle_weights.safetensors").exists()
+    assert (tmp_path / "oracle_batches.bin").stat().st_size == 2 * 2 * 129 * 2
+    lines = (tmp_path / "oracle_diagnostics.jsonl").read_text().splitlines()
+    assert json.loads(lines[1])["grad_norms"]["lm_head"] > 0
+
+
+def test_compare_train_identical_implementations_agree(tmp_path):
+    r = compare_train.run("tiny", "oracle", "oracle", steps=4, batch=2, csv_path=str(tmp_path / "c.csv"), device="cpu")
+    assert r["max_rel"] == 0.0 and (tmp_path / "c.csv").read_text().startswith("step,oracle,oracle,rel_diff")
+
+
+def test_monitor_parses_reference_log_lines():
+    log = """autoresearch-brain
+step     0 | loss 9.0037 | lr 1.000 | dt 9.960s | tok/s 52643 | mfu 25.5% | vram 53410MB | steps_left 999
+timing | fwd+bwd 9926.0ms  opt 33.0ms  gpu 9959.0ms  wall_gap 0.0ms
+[eval] step 25 | val_bpb 1.2345
+step   995 | loss 2.6008 | lr 0.036 | dt 9.950s | tok/s 52700 | mfu 25.6% | vram 53410MB | steps_left 4
+[eval] final | val_bpb 0.5392
+thread 'main' panicked at src/train.rs
+""".splitlines()
+    p = monitor.parse(log)
+    assert [s["step"] for s in p["steps"]] == [0, 995] and p["steps"][1]["tok_s"] == 52700
+    assert p["evals"] == [{"step": 25, "val_bpb": 1.2345}, {"step": None, "val_bpb": 0.5392}]
+    assert len(p["crashes"]) == 1 and "CRASH" in monitor.summary(p)
