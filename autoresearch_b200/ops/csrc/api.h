@@ -36,6 +36,10 @@ int arb_gemm_bf16(const void* A, const void* B, void* C, const void* aux, int M,
                   long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha, float beta,
                   float gamma, int* err_flag, cudaStream_t stream);
 
+// Tile selection: 0 = automatic (2-CTA 256x256 tiles when M >= 512 and N >= 256, else 1-CTA
+// 128x256/128x128), 1 = always 1-CTA, 2 = always 2-CTA.  Process-wide; meant for tests / benchmarks.
+int arb_gemm_set_mode(int mode);
+
 // ---- flash attention (attn_sm100.cu) ----------------------------------------------------------
 // q, k, v, o: [B, T, H, hd=128] bf16 with token stride `ld*` elements (head h at column
 // h*128); lse: [B, H, T] fp32.  window >= T means plain causal; key j is visible to query i

@@ -39,14 +39,6 @@ struct AttnArgs {
   int* err;
 };
 
-// 16-byte store into a K-major 128-byte-swizzled tile of `rows` rows; columns beyond 64 go
-// to the next (rows*128)-byte half.
-__device__ __forceinline__ void st_sw128(uint32_t base, int rows, int r, int c0, uint4 v) {
-  const uint32_t addr = base + uint32_t(c0 >> 6) * uint32_t(rows) * 128u + uint32_t(r) * 128u +
-                        (uint32_t(((c0 & 63) >> 3) ^ (r & 7)) << 4);
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

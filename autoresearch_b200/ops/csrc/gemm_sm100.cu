@@ -18,6 +18,8 @@
 #include "ptx.cuh"
 #include "tmap.h"
 
+#include <cstring>
+
 namespace arb {
 
 constexpr int BM = 128;
@@ -32,6 +34,7 @@ struct GemmArgs {
   long long ldc, stride_c;      // elements
   float alpha, beta, gamma;
   int* err;
+  int flags;   // experiment switches of the 2-CTA kernel: bit0 = multicast commits, bit1 = leader-only barrier arrive
 };
 
 template <int BN>
@@ -43,6 +46,75 @@ struct SmemLayout {
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // + barriers + alignment slack
 };
+
+// One 32-column chunk of one accumulator row -> global memory, with the fused epilogue.
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], const GemmArgs& p, int row, long long row_off, int col0) {
+  const bool full = (col0 + 32 <= p.N);
+  if (EPI == EPI_ATOMIC_F32) {
+    float* dst = reinterpret_cast<float*>(p.C) + row_off + col0;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(__uint_as_float(v[j])),
+                     "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])), "f"(__uint_as_float(v[j + 3])) : "memory");
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(dst + j, __uint_as_float(v[j]));
+    }
+  } else if (EPI == EPI_STORE_F32) {
+    float* dst = reinterpret_cast<float*>(p.C) + row_off + col0;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                          __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __uint_as_float(v[j]);
+    }
+  } else {
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+    if (EPI == EPI_RELU2) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { float r = fmaxf(f[j], 0.f); f[j] = r * r; }
+    }
+    if (EPI == EPI_NS_COMBINE || EPI == EPI_RELU2_BWD || EPI == EPI_ADD_AUX) {
+      const __nv_bfloat16* ax = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row_off + col0;
+      float a[32];
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 u = *reinterpret_cast<const uint4*>(ax + j);
+          float2 t0 = unpack_bf16(u.x), t1 = unpack_bf16(u.y), t2 = unpack_bf16(u.z), t3 = unpack_bf16(u.w);
+          a[j] = t0.x; a[j + 1] = t0.y; a[j + 2] = t1.x; a[j + 3] = t1.y;
+          a[j + 4] = t2.x; a[j + 5] = t2.y; a[j + 6] = t3.x; a[j + 7] = t3.y;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) a[j] = (col0 + j < p.N) ? __bfloat162float(ax[j]) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (EPI == EPI_NS_COMBINE) f[j] = p.beta * a[j] + p.gamma * f[j] + ((row == col0 + j) ? p.alpha : 0.f);
+        else if (EPI == EPI_RELU2_BWD) f[j] = f[j] * 2.f * sqrtf(fmaxf(a[j], 0.f));
+        else f[j] = f[j] + a[j];
+      }
+    }
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row_off + col0;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 u;
+        u.x = pack_bf16(f[j], f[j + 1]); u.y = pack_bf16(f[j + 2], f[j + 3]);
+        u.z = pack_bf16(f[j + 4], f[j + 5]); u.w = pack_bf16(f[j + 6], f[j + 7]);
+        *reinterpret_cast<uint4*>(dst + j) = u;
+      }
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16(f[j]);
+    }
+  }
+      }
 
 template <bool A_MN, bool B_MN, int EPI, int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -176,70 +248,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_wait_ld();
         const int col0 = nt * BN + c * 32;
         if (!row_ok || col0 >= p.N) continue;
-        const bool full = (col0 + 32 <= p.N);
-        if (EPI == EPI_ATOMIC_F32) {
-          float* dst = reinterpret_cast<float*>(p.C) + row_off + col0;
-          if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(__uint_as_float(v[j])),
-                           "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])), "f"(__uint_as_float(v[j + 3])) : "memory");
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(dst + j, __uint_as_float(v[j]));
-          }
-        } else if (EPI == EPI_STORE_F32) {
-          float* dst = reinterpret_cast<float*>(p.C) + row_off + col0;
-          if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                                __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __uint_as_float(v[j]);
-          }
-        } else {
-          float f[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-          if (EPI == EPI_RELU2) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) { float r = fmaxf(f[j], 0.f); f[j] = r * r; }
-          }
-          if (EPI == EPI_NS_COMBINE || EPI == EPI_RELU2_BWD || EPI == EPI_ADD_AUX) {
-            const __nv_bfloat16* ax = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row_off + col0;
-            float a[32];
-            if (full) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 u = *reinterpret_cast<const uint4*>(ax + j);
-                float2 t0 = unpack_bf16(u.x), t1 = unpack_bf16(u.y), t2 = unpack_bf16(u.z), t3 = unpack_bf16(u.w);
-                a[j] = t0.x; a[j + 1] = t0.y; a[j + 2] = t1.x; a[j + 3] = t1.y;
-                a[j + 4] = t2.x; a[j + 5] = t2.y; a[j + 6] = t3.x; a[j + 7] = t3.y;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) a[j] = (col0 + j < p.N) ? __bfloat162float(ax[j]) : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (EPI == EPI_NS_COMBINE) f[j] = p.beta * a[j] + p.gamma * f[j] + ((row == col0 + j) ? p.alpha : 0.f);
-              else if (EPI == EPI_RELU2_BWD) f[j] = f[j] * 2.f * sqrtf(fmaxf(a[j], 0.f));
-              else f[j] = f[j] + a[j];
-            }
-          }
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row_off + col0;
-          if (full) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 u;
-              u.x = pack_bf16(f[j], f[j + 1]); u.y = pack_bf16(f[j + 2], f[j + 3]);
-              u.z = pack_bf16(f[j + 4], f[j + 5]); u.w = pack_bf16(f[j + 6], f[j + 7]);
-              *reinterpret_cast<uint4*>(dst + j) = u;
-            }
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16(f[j]);
-          }
-        }
+        epilogue_chunk<EPI>(v, p, row, row_off, col0);
       }
       tc_fence_before();
       __syncwarp();
@@ -254,7 +263,280 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 // ------------------------------------------------------------------------------------------
+// 2-CTA variant: a cluster of two CTAs (one SM pair) owns a 256 x 256 tile.  Each CTA loads its
+// own 128 rows of A and 128 of the 256 rows of B (half the B traffic per SM of the 1-CTA kernel,
+// so six 32 KB stages fit), the pair leader issues tcgen05.mma.cta_group::2 (M = 256) which reads
+// both CTAs' shared memory and writes each CTA's half of the accumulator into its own TMEM, and
+// each CTA runs the epilogue for its 128 rows.  Loads carry no cluster multicast.
+// ------------------------------------------------------------------------------------------
+constexpr bool epi_is_bf16(int epi) { return epi != EPI_ATOMIC_F32 && epi != EPI_STORE_F32; }
+constexpr bool epi_has_aux(int epi) { return epi == EPI_NS_COMBINE || epi == EPI_RELU2_BWD || epi == EPI_ADD_AUX; }
+
+// bf16 outputs leave through a swizzled smem staging slab (128 rows x 64 columns, double buffered)
+// and TMA stores, so every request to L2 is a full line; aux operands arrive the same way.
+template <int EPI>
+struct Smem2 {
+  static constexpr bool STAGED = epi_is_bf16(EPI);
+  static constexpr bool AUX = epi_has_aux(EPI);
+  static constexpr int STAGES = AUX ? 5 : 6;
+  static constexpr int A_BYTES = 128 * BK * 2;
+  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int C_STAGE = STAGES * STAGE_BYTES;                       // 2 x 16 KB
+  static constexpr int X_STAGE = C_STAGE + (STAGED ? 32768 : 0);             // 2 x 16 KB
+  static constexpr int BAR_OFFSET = X_STAGE + (AUX ? 32768 : 0);
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+};
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const GemmArgs p) {
+  using L = Smem2<EPI>;
+  constexpr int STAGES = L::STAGES;
+  constexpr int BN2 = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);   // used in the leader only (count 1)
+  uint64_t* empty_bar = full_bar + STAGES;                                   // per CTA (count 1)
+  uint64_t* tfull_bar = empty_bar + STAGES;                                  // per CTA (count 1)
+  uint64_t* tempty_bar = tfull_bar + 2;                                      // used in the leader only (count 8)
+  uint64_t* xfull_bar = tempty_bar + 2;                                      // aux slab landed (count 1)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xfull_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int n_clusters = gridDim.x >> 1;
+  const int items = p.batch * p.m_tiles * p.n_tiles * p.splitk;   // m_tiles counted in 256-row tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); mbar_init(&xfull_bar[a], 1); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc_pair(tmem_slot, 512); tmem_relinquish_pair(); }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = cluster_id; w < items && ok; w += n_clusters) {
+        int t = w;
+        const int nt = t % p.n_tiles; t /= p.n_tiles;
+        const int mt = t % p.m_tiles; t /= p.m_tiles;
+        const int ks = t % p.splitk;
+        const int b = t / p.splitk;
+        const int kb0 = ks * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        const int m0 = mt * 256 + int(rank) * 128;
+        const int n0 = nt * 256 + int(rank) * 128;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + s * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          const uint32_t lead_bar = mapa_u32(smem_u32(&full_bar[s]), 0);
+          // only the leader arrives (and announces both CTAs' bytes); the peer's copies just credit
+          // their bytes to the same barrier - a remote arrive per stage costs a cluster-scope release
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * L::STAGE_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_3d_pair(sa + c * 8192, &tmA, lead_bar, m0 + c * 64, kb * BK, b);
+          } else {
+            tma_load_3d_pair(sa, &tmA, lead_bar, kb * BK, m0, b);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_3d_pair(sb + c * 8192, &tmB, lead_bar, n0 + c * 64, kb * BK, b);
+          } else {
+            tma_load_3d_pair(sb, &tmB, lead_bar, kb * BK, n0, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, BN2, A_MN, B_MN);
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int w = cluster_id; w < items && ok; w += n_clusters, ++tile_it) {
+        int t = w / (p.n_tiles * p.m_tiles);
+        const int ks = t % p.splitk;
+        const int kb0 = ks * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        const int acc = tile_it & 1;
+        const uint32_t aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN2;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 0, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 0, 1024);
+            tc_mma_ss_pair(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          if (p.flags & 1) {
+            tc_commit_pair_mc(&empty_bar[s], 3);
+          } else {
+            const uint32_t eb = smem_u32(&empty_bar[s]);
+            tc_commit_pair(eb);
+            tc_commit_pair(mapa_u32(eb, 1));
+          }
+        }
+        if (ok) {
+          if (p.flags & 1) {
+            tc_commit_pair_mc(&tfull_bar[acc], 3);
+          } else {
+            const uint32_t tb = smem_u32(&tfull_bar[acc]);
+            tc_commit_pair(tb);
+            tc_commit_pair(mapa_u32(tb, 1));
+          }
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t tile_it = 0, slab_it = 0;
+    bool ok = true;
+    for (int w = cluster_id; w < items; w += n_clusters, ++tile_it) {
+      int t = w;
+      const int nt = t % p.n_tiles; t /= p.n_tiles;
+      const int mt = t % p.m_tiles; t /= p.m_tiles;
+      const int b = t / p.splitk;
+      const int acc = tile_it & 1;
+      const uint32_t aph = (tile_it >> 1) & 1;
+      // after a time-out keep walking the loop (named barriers below need all four warps) but skip waits
+      if (ok && !mbar_wait(&tfull_bar[acc], aph, abort_flag)) ok = false;
+      tc_fence_after();
+      const int row = mt * 256 + int(rank) * 128 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const long long row_off = (long long)b * p.stride_c + (long long)row * p.ldc;
+      if (!L::STAGED) {
+#pragma unroll 1
+        for (int c = 0; c < BN2 / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN2 + c * 32), v);
+          tmem_wait_ld();
+          const int col0 = nt * BN2 + c * 32;
+          if (!row_ok || col0 >= p.N) continue;
+          epilogue_chunk<EPI>(v, p, row, row_off, col0);
+        }
+      } else {
+        const bool t0 = (threadIdx.x == 64);              // the thread that drives the TMA copies
+        const int r_local = q * 32 + lane;
+        const int row0 = mt * 256 + int(rank) * 128;
+        if (L::AUX && t0 && tile_it == 0) {               // first aux slab of this CTA's first tile
+          mbar_expect_tx(&xfull_bar[0], 16384);
+          tma_load_3d(smem + L::X_STAGE, &tmX, &xfull_bar[0], nt * BN2, row0, b);
+        }
+#pragma unroll 1
+        for (int sl = 0; sl < 4; ++sl, ++slab_it) {
+          const int buf = slab_it & 1;
+          const int col_s = nt * BN2 + sl * 64;
+          if (t0) tma_store_wait_read_1();                // the store issued two slabs ago has read its buffer
+          named_barrier(2, 128);
+          if (L::AUX) {
+            if (t0) {                                      // prefetch the next aux slab (this tile or the next one)
+              int nsl = sl + 1, nw = w;
+              if (nsl == 4) { nsl = 0; nw = w + n_clusters; }
+              if (nw < items) {
+                int tt = nw;
+                const int nnt = tt % p.n_tiles; tt /= p.n_tiles;
+                const int nmt = tt % p.m_tiles; tt /= p.m_tiles;
+                const int nb = tt / p.splitk;
+                mbar_expect_tx(&xfull_bar[buf ^ 1], 16384);
+                tma_load_3d(smem + L::X_STAGE + (buf ^ 1) * 16384, &tmX, &xfull_bar[buf ^ 1], nnt * BN2 + nsl * 64,
+                            nmt * 256 + int(rank) * 128, nb);
+              }
+            }
+            if (!mbar_wait(&xfull_bar[buf], (slab_it >> 1) & 1, abort_flag)) { ok = false; }
+          }
+          const uint32_t cbase = smem_u32(smem + L::C_STAGE + buf * 16384);
+          const uint32_t xbase = smem_u32(smem + L::X_STAGE + buf * 16384);
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN2 + sl * 64 + hc * 32), v);
+            tmem_wait_ld();
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            if (EPI == EPI_RELU2) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) { const float r = fmaxf(f[j], 0.f); f[j] = r * r; }
+            }
+            if (L::AUX) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                const uint4 u = ld_sw128(xbase, 128, r_local, hc * 32 + j);
+                const float2 a0 = unpack_bf16(u.x), a1 = unpack_bf16(u.y), a2 = unpack_bf16(u.z), a3 = unpack_bf16(u.w);
+                const float ax[8] = {a0.x, a0.y, a1.x, a1.y, a2.x, a2.y, a3.x, a3.y};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  float& x = f[j + e];
+                  if (EPI == EPI_NS_COMBINE) x = p.beta * ax[e] + p.gamma * x + ((row == col_s + hc * 32 + j + e) ? p.alpha : 0.f);
+                  else if (EPI == EPI_RELU2_BWD) x = x * 2.f * sqrtf(fmaxf(ax[e], 0.f));
+                  else x = x + ax[e];
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 u;
+              u.x = pack_bf16(f[j], f[j + 1]); u.y = pack_bf16(f[j + 2], f[j + 3]);
+              u.z = pack_bf16(f[j + 4], f[j + 5]); u.w = pack_bf16(f[j + 6], f[j + 7]);
+              st_sw128(cbase, 128, r_local, hc * 32 + j, u);
+            }
+          }
+          fence_proxy_async_smem();
+          named_barrier(3, 128);
+          if (t0 && col_s < p.N && row0 < p.M) {
+            tma_store_3d(&tmC, smem + L::C_STAGE + buf * 16384, col_s, row0, b);
+            tma_store_commit();
+          } else if (t0) {
+            tma_store_commit();                           // keep the group count in step with the slab count
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive(&tempty_bar[acc]);
+        else mbar_arrive_remote(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
+      }
+    }
+    if (L::STAGED && threadIdx.x == 64) tma_store_wait_all();   // staged tiles are on their way before smem goes away
+  }
+
+  tc_fence_before();
+  cluster_sync_all();
+  if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, ERR_GEMM_TIMEOUT);
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc_pair(tmem_base, 512); }
+}
+
+// ------------------------------------------------------------------------------------------
 static int g_num_sms = 0;
+static int g_gemm_flags = 0;
+static int g_gemm_mode = 0;   // 0 = automatic, 1 = always 1-CTA tiles, 2 = always 2-CTA tiles
 
 template <bool A_MN, bool B_MN, int EPI, int BN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, cudaStream_t st) {
@@ -270,6 +552,61 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
   const int grid = items < g_num_sms ? items : g_num_sms;
   kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, a);
   return int(cudaGetLastError());
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, cudaStream_t st) {
+  auto kern = gemm_pair_kernel<A_MN, B_MN, EPI>;
+  static bool configured = false;
+  CUtensorMap tc, tx;
+  std::memset(&tc, 0, sizeof tc);
+  std::memset(&tx, 0, sizeof tx);
+  if (epi_is_bf16(EPI)) {
+    uint64_t dims[3] = {uint64_t(a.N), uint64_t(a.M), uint64_t(a.batch)};
+    uint64_t str[2] = {uint64_t(a.ldc) * 2, a.batch > 1 ? uint64_t(a.stride_c) * 2 : uint64_t(a.M) * uint64_t(a.ldc) * 2};
+    uint32_t box[3] = {64, 128, 1};
+    int r = make_tmap_bf16(&tc, a.C, 3, dims, str, box);
+    if (r) return 3000 + r;
+    if (epi_has_aux(EPI)) {
+      r = make_tmap_bf16(&tx, a.aux, 3, dims, str, box);
+      if (r) return 4000 + r;
+    }
+  }
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<EPI>::TOTAL);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  const int items = a.batch * a.m_tiles * a.n_tiles * a.splitk;
+  int clusters = g_num_sms / 2;
+  if (items < clusters) clusters = items;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(clusters * 2));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Smem2<EPI>::TOTAL;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return int(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, a));
+}
+
+template <bool A_MN, bool B_MN>
+static int dispatch_pair(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, cudaStream_t st) {
+  switch (epi) {
+    case EPI_STORE_BF16: return launch_pair<A_MN, B_MN, EPI_STORE_BF16>(ta, tb, a, st);
+    case EPI_RELU2: return launch_pair<A_MN, B_MN, EPI_RELU2>(ta, tb, a, st);
+    case EPI_ATOMIC_F32: return launch_pair<A_MN, B_MN, EPI_ATOMIC_F32>(ta, tb, a, st);
+    case EPI_NS_COMBINE: return launch_pair<A_MN, B_MN, EPI_NS_COMBINE>(ta, tb, a, st);
+    case EPI_RELU2_BWD: return launch_pair<A_MN, B_MN, EPI_RELU2_BWD>(ta, tb, a, st);
+    case EPI_STORE_F32: return launch_pair<A_MN, B_MN, EPI_STORE_F32>(ta, tb, a, st);
+    case EPI_ADD_AUX: return launch_pair<A_MN, B_MN, EPI_ADD_AUX>(ta, tb, a, st);
+  }
+  return -2;
 }
 
 template <bool A_MN, bool B_MN, int BN>
@@ -290,6 +627,16 @@ static int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, c
 
 using namespace arb;
 
+extern "C" int arb_gemm_set_mode(int mode) {
+  if (mode < 0 || mode > 2) return -3;
+  g_gemm_mode = mode;
+  return 0;
+}
+extern "C" int arb_gemm_set_flags(int flags) {
+  g_gemm_flags = flags;
+  return 0;
+}
+
 extern "C" int arb_gemm_bf16(const void* A, const void* B, void* C, const void* aux, int M, int N, int K, int batch,
                              long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                              long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha,
@@ -308,16 +655,20 @@ extern "C" int arb_gemm_bf16(const void* A, const void* B, void* C, const void* 
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int BN = (N > 128) ? 256 : 128;
+  // 2-CTA tiles (256 x 256) for problems that are large in both output dimensions
+  const bool pair = (g_gemm_mode != 1) && (g_gemm_mode == 2 || (M >= 512 && N >= 256));
+  const int bm_eff = pair ? 256 : BM;
   GemmArgs a;
   a.M = M; a.N = N; a.K = K; a.batch = batch;
-  a.m_tiles = (M + BM - 1) / BM;
-  a.n_tiles = (N + BN - 1) / BN;
+  a.m_tiles = (M + bm_eff - 1) / bm_eff;
+  a.n_tiles = pair ? (N + 255) / 256 : (N + BN - 1) / BN;
   a.kb_total = (K + BK - 1) / BK;
   if (epi != EPI_ATOMIC_F32) splitk = 1;
   if (splitk <= 0) {  // automatic: fill the SMs when there are few output tiles
     const int tiles = batch * a.m_tiles * a.n_tiles;
+    const int units = pair ? g_num_sms / 2 : g_num_sms;     // CTAs, or CTA pairs, that can run at once
     splitk = 1;
-    if (tiles < g_num_sms) splitk = (g_num_sms + tiles - 1) / tiles;
+    if (tiles < units) splitk = (units + tiles - 1) / tiles;
     const int max_split = a.kb_total / 4 > 0 ? a.kb_total / 4 : 1;  // at least 4 K blocks per split
     if (splitk > max_split) splitk = max_split;
   }
@@ -325,25 +676,31 @@ extern "C" int arb_gemm_bf16(const void* A, const void* B, void* C, const void* 
   a.kb_per_split = (a.kb_total + splitk - 1) / splitk;
   a.splitk = (a.kb_total + a.kb_per_split - 1) / a.kb_per_split;
   a.C = C; a.aux = aux; a.ldc = ldc; a.stride_c = stride_c;
-  a.alpha = alpha; a.beta = beta; a.gamma = gamma; a.err = err_flag;
+  a.alpha = alpha; a.beta = beta; a.gamma = gamma; a.err = err_flag; a.flags = g_gemm_flags;
 
   CUtensorMap ta, tb;
   {
     uint64_t dims[3], str[2];
     uint32_t box[3];
     if (a_mn_major) { dims[0] = uint64_t(M); dims[1] = uint64_t(K); box[0] = 64; box[1] = BK; }
-    else { dims[0] = uint64_t(K); dims[1] = uint64_t(M); box[0] = BK; box[1] = BM; }
+    else { dims[0] = uint64_t(K); dims[1] = uint64_t(M); box[0] = BK; box[1] = 128; }
     dims[2] = uint64_t(batch); box[2] = 1;
     str[0] = uint64_t(lda) * 2;
     str[1] = batch > 1 ? uint64_t(stride_a) * 2 : dims[1] * str[0];
     int r = make_tmap_bf16(&ta, A, 3, dims, str, box);
     if (r) return 1000 + r;
     if (b_mn_major) { dims[0] = uint64_t(N); dims[1] = uint64_t(K); box[0] = 64; box[1] = BK; }
-    else { dims[0] = uint64_t(K); dims[1] = uint64_t(N); box[0] = BK; box[1] = uint32_t(BN); }
+    else { dims[0] = uint64_t(K); dims[1] = uint64_t(N); box[0] = BK; box[1] = uint32_t(pair ? 128 : BN); }
     str[0] = uint64_t(ldb) * 2;
     str[1] = batch > 1 ? uint64_t(stride_b) * 2 : dims[1] * str[0];
     r = make_tmap_bf16(&tb, B, 3, dims, str, box);
     if (r) return 2000 + r;
+  }
+  if (pair) {
+    if (!a_mn_major && !b_mn_major) return dispatch_pair<false, false>(epi, ta, tb, a, stream);
+    if (!a_mn_major && b_mn_major) return dispatch_pair<false, true>(epi, ta, tb, a, stream);
+    if (a_mn_major && b_mn_major) return dispatch_pair<true, true>(epi, ta, tb, a, stream);
+    return dispatch_pair<true, false>(epi, ta, tb, a, stream);
   }
 #define ARB_DISPATCH(AM, BMJ)                                                                              \
   (BN == 256 ? dispatch_epi<AM, BMJ, 256>(epi, ta, tb, a, stream) : dispatch_epi<AM, BMJ, 128>(epi, ta, tb, a, stream))

@@ -185,6 +185,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     return out
 
 
+def gemm_set_mode(mode: int) -> None:
+    """0 = automatic tile choice, 1 = always 1-CTA tiles, 2 = always 2-CTA (cta_group::2) tiles."""
+    f = lib().arb_gemm_set_mode
+    f.restype, f.argtypes = C.c_int, [C.c_int]
+    if f(mode) != 0:
+        raise ValueError(f"bad GEMM mode {mode}")
+
+
 def rmsnorm_fwd(x, eps):
     _bf16(x, "x")
     y = torch.empty_like(x)

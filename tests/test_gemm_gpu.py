@@ -5,6 +5,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=[1, 2, 0], ids=["one_cta", "cta_pair", "auto"])
+def tile_mode(request):
+    """Every case runs on the 1-CTA kernel, on the 2-CTA (cta_group::2) kernel and with the
+    automatic choice."""
+    from autoresearch_b200.ops import kernels as K_
+    K_.gemm_set_mode(request.param)
+    yield request.param
+    K_.gemm_set_mode(0)
+
+
 def _rand(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
 
