@@ -269,14 +269,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 // both CTAs' shared memory and writes each CTA's half of the accumulator into its own TMEM, and
 // each CTA runs the epilogue for its 128 rows.  Loads carry no cluster multicast.
 // ------------------------------------------------------------------------------------------
-constexpr bool epi_is_bf16(int epi) { return epi != EPI_ATOMIC_F32 && epi != EPI_STORE_F32; }
-constexpr bool epi_has_aux(int epi) { return epi == EPI_NS_COMBINE || epi == EPI_RELU2_BWD || epi == EPI_ADD_AUX; }
+__host__ __device__ constexpr bool epi_is_bf16(int epi) { return epi != EPI_ATOMIC_F32 && epi != EPI_STORE_F32; }
+__host__ __device__ constexpr bool epi_has_aux(int epi) { return epi == EPI_NS_COMBINE || epi == EPI_RELU2_BWD || epi == EPI_ADD_AUX; }
 
 // bf16 outputs leave through a swizzled smem staging slab (128 rows x 64 columns, double buffered)
 // and TMA stores, so every request to L2 is a full line; aux operands arrive the same way.
 template <int EPI>
 struct Smem2 {
-  static constexpr bool STAGED = epi_is_bf16(EPI);
+  static constexpr bool STAGED = true;      // fp32 outputs are staged as 128 x 32 slabs (TMA store / reduce-add)
   static constexpr bool AUX = epi_has_aux(EPI);
   static constexpr int STAGES = AUX ? 5 : 6;
   static constexpr int A_BYTES = 128 * BK * 2;
@@ -444,12 +444,38 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool t0 = (threadIdx.x == 64);              // the thread that drives the TMA copies
         const int r_local = q * 32 + lane;
         const int row0 = mt * 256 + int(rank) * 128;
+        if (!epi_is_bf16(EPI)) {
+          // fp32 output: eight slabs of 128 rows x 32 columns; accumulate-mode goes out as a TMA
+          // reduce-add (full-line atomics at L2), store-mode as a TMA store
+#pragma unroll 1
+          for (int sl = 0; sl < 8; ++sl, ++slab_it) {
+            const int buf = slab_it & 1;
+            const int col_s = nt * BN2 + sl * 32;
+            if (t0) tma_store_wait_read_1();
+            named_barrier(2, 128);
+            const uint32_t cbase = smem_u32(smem + L::C_STAGE + buf * 16384);
+            uint32_t v[32];
+            tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN2 + sl * 32), v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) st_sw128(cbase, 128, r_local, j * 2, make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+            fence_proxy_async_smem();
+            named_barrier(3, 128);
+            if (t0) {
+              if (col_s < p.N && row0 < p.M) {
+                if (EPI == EPI_ATOMIC_F32) tma_reduce_add_3d(&tmC, smem + L::C_STAGE + buf * 16384, col_s, row0, b);
+                else tma_store_3d(&tmC, smem + L::C_STAGE + buf * 16384, col_s, row0, b);
+              }
+              tma_store_commit();
+            }
+          }
+        }
         if (L::AUX && t0 && tile_it == 0) {               // first aux slab of this CTA's first tile
           mbar_expect_tx(&xfull_bar[0], 16384);
           tma_load_3d(smem + L::X_STAGE, &tmX, &xfull_bar[0], nt * BN2, row0, b);
         }
 #pragma unroll 1
-        for (int sl = 0; sl < 4; ++sl, ++slab_it) {
+        for (int sl = 0; sl < (epi_is_bf16(EPI) ? 4 : 0); ++sl, ++slab_it) {
           const int buf = slab_it & 1;
           const int col_s = nt * BN2 + sl * 64;
           if (t0) tma_store_wait_read_1();                // the store issued two slabs ago has read its buffer
@@ -561,11 +587,13 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
   CUtensorMap tc, tx;
   std::memset(&tc, 0, sizeof tc);
   std::memset(&tx, 0, sizeof tx);
-  if (epi_is_bf16(EPI)) {
+  {
+    const uint64_t es = epi_is_bf16(EPI) ? 2 : 4;
     uint64_t dims[3] = {uint64_t(a.N), uint64_t(a.M), uint64_t(a.batch)};
-    uint64_t str[2] = {uint64_t(a.ldc) * 2, a.batch > 1 ? uint64_t(a.stride_c) * 2 : uint64_t(a.M) * uint64_t(a.ldc) * 2};
-    uint32_t box[3] = {64, 128, 1};
-    int r = make_tmap_bf16(&tc, a.C, 3, dims, str, box);
+    uint64_t str[2] = {uint64_t(a.ldc) * es, a.batch > 1 ? uint64_t(a.stride_c) * es : uint64_t(a.M) * uint64_t(a.ldc) * es};
+    uint32_t box[3] = {uint32_t(epi_is_bf16(EPI) ? 64 : 32), 128, 1};
+    int r = make_tmap_typed(&tc, a.C, 3, dims, str, box,
+                            epi_is_bf16(EPI) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
     if (r) return 3000 + r;
     if (epi_has_aux(EPI)) {
       r = make_tmap_bf16(&tx, a.aux, 3, dims, str, box);
@@ -667,10 +695,17 @@ extern "C" int arb_gemm_bf16(const void* A, const void* B, void* C, const void* 
   if (splitk <= 0) {  // automatic: fill the SMs when there are few output tiles
     const int tiles = batch * a.m_tiles * a.n_tiles;
     const int units = pair ? g_num_sms / 2 : g_num_sms;     // CTAs, or CTA pairs, that can run at once
+    int max_split = a.kb_total / 8 > 0 ? a.kb_total / 8 : 1;        // at least 8 K blocks per split
+    if (max_split > 32) max_split = 32;
+    // pick the split that fills the last wave best: efficiency = items / (waves * units)
     splitk = 1;
-    if (tiles < units) splitk = (units + tiles - 1) / tiles;
-    const int max_split = a.kb_total / 4 > 0 ? a.kb_total / 4 : 1;  // at least 4 K blocks per split
-    if (splitk > max_split) splitk = max_split;
+    double best = 0.0;
+    for (int sp = 1; sp <= max_split; ++sp) {
+      const long long it = (long long)tiles * sp;
+      const long long waves = (it + units - 1) / units;
+      const double eff = double(it) / double(waves * units);
+      if (eff > best + 0.02) { best = eff; splitk = sp; }
+    }
   }
   if (splitk > a.kb_total) splitk = a.kb_total;
   a.kb_per_split = (a.kb_total + splitk - 1) / splitk;

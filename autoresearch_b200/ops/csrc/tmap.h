@@ -24,8 +24,9 @@ inline EncodeTiledFn get_encode_fn() {
 
 // bf16 tensor, `rank` dims (innermost first); strides[i] = byte stride of dim i+1.
 // Returns 0 on success, the CUresult (or -1) otherwise.
-inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                          const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128 = true) {
+inline int make_tmap_typed(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapDataType dtype,
+                           bool swizzle128 = true) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t d[5];
@@ -33,10 +34,15 @@ inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const ui
   cuuint32_t b[5], e[5];
   for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; e[i] = 1; }
   for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, cuuint32_t(rank), const_cast<void*>(base), d, s, b, e,
+  CUresult r = fn(out, dtype, cuuint32_t(rank), const_cast<void*>(base), d, s, b, e,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return int(r);
+}
+
+inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128 = true) {
+  return make_tmap_typed(out, base, rank, dims, strides_bytes, box, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, swizzle128);
 }
 
 }  // namespace arb
