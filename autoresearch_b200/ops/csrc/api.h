@@ -101,6 +101,16 @@ int arb_adamw(float* master, const float* grad, float* m, float* v, void* shadow
 // buf = mu*buf + (1-mu)*g ; u = (1-mu)*g + mu*buf -> bf16 ; sumsq[mat] += sum(u_bf16^2)
 int arb_muon_nesterov(float* buf, const float* grad, void* u_bf16, float* sumsq, long long per_mat, int n_mat,
                       float mu, cudaStream_t s);
+// The same two updates with the data-parallel reduce-scatter fused in: the gradient of element i
+// is grad_scale * sum_p bucket_p[bucket_offset + i] over all ranks' bf16 buckets, read through
+// NVLink peer pointers (HOST array peer_buckets, world entries) or, when mc_bucket is non-null,
+// with one multimem.ld_reduce through the switch.  n / per_mat / bucket_offset multiples of 8.
+int arb_muon_nesterov_rs(float* buf, const void* const* peer_buckets, int world, int rank, const void* mc_bucket,
+                         long long bucket_offset, float grad_scale, void* u_bf16, float* sumsq, long long per_mat,
+                         int n_mat, float mu, cudaStream_t s);
+int arb_adamw_rs(float* master, const void* const* peer_buckets, int world, int rank, const void* mc_bucket,
+                 long long bucket_offset, float grad_scale, float* m, float* v, void* shadow_bf16, long long n,
+                 float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, cudaStream_t s);
 // x = u / (sqrt(sumsq[mat])*1.02 + 1e-6)
 int arb_muon_frob_scale(void* u_bf16, const float* sumsq, long long per_mat, int n_mat, cudaStream_t s);
 // NorMuon statistics + cautious update, per matrix [m, n]; reduce over columns if m >= n.

@@ -127,6 +127,109 @@ __global__ void muon_update_k(float* __restrict__ master, __nv_bfloat16* __restr
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Reduce-scatter fused into the optimizer: the gradient of an owned element is summed on the fly
+// over every rank's bf16 bucket (NVLink peer loads, or one multimem.ld_reduce through the
+// switch), scaled, and consumed by the momentum / Adam update in the same thread - the reduced
+// fp32 gradient is never written to memory.
+// ---------------------------------------------------------------------------------------------
+constexpr int OPT_MAX_WORLD = 16;
+struct GradPeers { const __nv_bfloat16* p[OPT_MAX_WORLD]; const __nv_bfloat16* mc; int world; int rank; float scale; };
+
+__device__ __forceinline__ void load_grad8(const GradPeers& g, long long idx, float (&o)[8]) {
+  if (g.mc) {
+    uint32_t r0, r1, r2, r3;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "l"(g.mc + idx) : "memory");
+    float2 a = unpack_bf16(r0), b = unpack_bf16(r1), c = unpack_bf16(r2), d = unpack_bf16(r3);
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y; o[4] = c.x; o[5] = c.y; o[6] = d.x; o[7] = d.y;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = 0.f;
+    for (int q = 0; q < g.world; ++q) {
+      const int pr = (g.rank + q) % g.world;
+      const uint4 u = *reinterpret_cast<const uint4*>(g.p[pr] + idx);
+      float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      o[0] += a.x; o[1] += a.y; o[2] += b.x; o[3] += b.y; o[4] += c.x; o[5] += c.y; o[6] += d.x; o[7] += d.y;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] *= g.scale;
+}
+
+// grid (blocks_per_mat, n_mat); elements of matrix `mat` sit at bucket offset `offset + mat*per_mat`
+__global__ void __launch_bounds__(256) muon_nesterov_rs_k(float* __restrict__ buf, GradPeers gp, long long offset,
+                                                          __nv_bfloat16* __restrict__ u, float* __restrict__ sumsq,
+                                                          long long per_mat, float mu) {
+  __shared__ float red[8];
+  const int mat = blockIdx.y;
+  const long long base = (long long)mat * per_mat;
+  float acc = 0.f;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < per_mat; i += (long long)gridDim.x * blockDim.x * 8) {
+    float g[8];
+    load_grad8(gp, offset + base + i, g);
+    float4 b0 = *reinterpret_cast<const float4*>(buf + base + i), b1 = *reinterpret_cast<const float4*>(buf + base + i + 4);
+    float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    float uu[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      b[j] = mu * b[j] + (1.f - mu) * g[j];
+      uu[j] = __bfloat162float(__float2bfloat16((1.f - mu) * g[j] + mu * b[j]));
+      acc += uu[j] * uu[j];
+    }
+    *reinterpret_cast<float4*>(buf + base + i) = make_float4(b[0], b[1], b[2], b[3]);
+    *reinterpret_cast<float4*>(buf + base + i + 4) = make_float4(b[4], b[5], b[6], b[7]);
+    uint4 o;
+    o.x = pack_bf16(uu[0], uu[1]); o.y = pack_bf16(uu[2], uu[3]); o.z = pack_bf16(uu[4], uu[5]); o.w = pack_bf16(uu[6], uu[7]);
+    *reinterpret_cast<uint4*>(u + base + i) = o;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    atomicAdd(sumsq + mat, t);
+  }
+}
+
+__global__ void __launch_bounds__(256) adamw_rs_k(float* __restrict__ p, GradPeers gp, long long offset, float* __restrict__ m,
+                                                  float* __restrict__ v, __nv_bfloat16* __restrict__ shadow, long long n, float lr,
+                                                  float b1, float b2, float eps, float wd, float bc1, float bc2) {
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += (long long)gridDim.x * blockDim.x * 8) {
+    float g[8];
+    load_grad8(gp, offset + i, g);
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float pi = p[i + j], mi = m[i + j], vi = v[i + j];
+      pi -= lr * wd * pi;
+      mi = b1 * mi + (1.f - b1) * g[j];
+      vi = b2 * vi + (1.f - b2) * g[j] * g[j];
+      pi -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+      p[i + j] = pi; m[i + j] = mi; v[i + j] = vi;
+      o[j] = pi;
+    }
+    if (shadow) {
+      uint4 u;
+      u.x = pack_bf16(o[0], o[1]); u.y = pack_bf16(o[2], o[3]); u.z = pack_bf16(o[4], o[5]); u.w = pack_bf16(o[6], o[7]);
+      *reinterpret_cast<uint4*>(shadow + i) = u;
+    }
+  }
+}
+
+static int fill_peers(GradPeers& gp, const void* const* peers, int world, int rank, const void* mc, float scale) {
+  if (world < 1 || world > OPT_MAX_WORLD || rank < 0 || rank >= world) return -3;
+  for (int i = 0; i < world; ++i) {
+    if (!mc && (reinterpret_cast<uintptr_t>(peers[i]) & 15)) return -4;
+    gp.p[i] = reinterpret_cast<const __nv_bfloat16*>(peers ? peers[i] : nullptr);
+  }
+  gp.mc = reinterpret_cast<const __nv_bfloat16*>(mc);
+  gp.world = world; gp.rank = rank; gp.scale = scale;
+  return 0;
+}
+
 static inline int blocks_for(long long n, int threads, int cap) {
   long long b = (n + threads - 1) / threads;
   return int(b < 1 ? 1 : (b > cap ? cap : b));
@@ -150,6 +253,30 @@ int arb_muon_nesterov(float* buf, const float* grad, void* u_bf16, float* sumsq,
   if (e != cudaSuccess) return int(e);
   const int bpm = blocks_for(per_mat, 256 * 4, 64);
   muon_nesterov_k<<<dim3(bpm, n_mat), 256, 0, s>>>(buf, grad, (__nv_bfloat16*)u_bf16, sumsq, per_mat, mu);
+  return int(cudaGetLastError());
+}
+int arb_muon_nesterov_rs(float* buf, const void* const* peer_buckets, int world, int rank, const void* mc_bucket,
+                         long long bucket_offset, float grad_scale, void* u_bf16, float* sumsq, long long per_mat, int n_mat,
+                         float mu, cudaStream_t s) {
+  if (per_mat <= 0 || (per_mat & 7) || (bucket_offset & 7) || n_mat <= 0 || n_mat > 65535) return -3;
+  GradPeers gp;
+  int rc = fill_peers(gp, peer_buckets, world, rank, mc_bucket, grad_scale);
+  if (rc) return rc;
+  cudaError_t e = cudaMemsetAsync(sumsq, 0, sizeof(float) * n_mat, s);
+  if (e != cudaSuccess) return int(e);
+  const int bpm = blocks_for(per_mat / 8, 256, 64);
+  muon_nesterov_rs_k<<<dim3(bpm, n_mat), 256, 0, s>>>(buf, gp, bucket_offset, (__nv_bfloat16*)u_bf16, sumsq, per_mat, mu);
+  return int(cudaGetLastError());
+}
+int arb_adamw_rs(float* master, const void* const* peer_buckets, int world, int rank, const void* mc_bucket,
+                 long long bucket_offset, float grad_scale, float* m, float* v, void* shadow_bf16, long long n, float lr,
+                 float beta1, float beta2, float eps, float wd, float bc1, float bc2, cudaStream_t s) {
+  if (n <= 0 || (n & 7) || (bucket_offset & 7)) return -3;
+  GradPeers gp;
+  int rc = fill_peers(gp, peer_buckets, world, rank, mc_bucket, grad_scale);
+  if (rc) return rc;
+  adamw_rs_k<<<blocks_for(n / 8, 256, 148 * 8), 256, 0, s>>>(master, gp, bucket_offset, m, v, (__nv_bfloat16*)shadow_bf16, n, lr, beta1,
+                                                              beta2, eps, wd, bc1, bc2);
   return int(cudaGetLastError());
 }
 int arb_muon_frob_scale(void* u_bf16, const float* sumsq, long long per_mat, int n_mat, cudaStream_t s) {

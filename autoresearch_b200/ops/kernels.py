@@ -58,6 +58,8 @@ def lib() -> C.CDLL:
         "arb_adamw": [vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, f32, vp],
         "arb_muon_nesterov": [vp, vp, vp, vp, i64, i32, f32, vp],
         "arb_muon_frob_scale": [vp, vp, i64, i32, vp],
+        "arb_muon_nesterov_rs": [vp, vp, i32, i32, vp, i64, f32, vp, vp, i64, i32, f32, vp],
+        "arb_adamw_rs": [vp, vp, i32, i32, vp, i64, f32, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, f32, vp],
         "arb_normuon_stats": [vp, vp, i32, i32, i32, vp],
         "arb_normuon_scales": [vp, vp, vp, i32, i32, i32, f32, vp],
         "arb_muon_update": [vp, vp, vp, vp, i32, i32, i32, f32, f32, vp],

@@ -380,6 +380,22 @@ class LMHeadCEFn(torch.autograd.Function):
 
 
 # ----------------------------------------------------------------------------------------------
+class PeerGrad:
+    """A gradient that still lives in every rank's bf16 bucket: the optimizer kernels sum it over
+    the ranks while they consume it (reduce-scatter fused into the update)."""
+
+    def __init__(self, peer_ptrs, world, rank, mc_ptr, offset, shape, scale=1.0):
+        self.peer_ptrs, self.world, self.rank, self.mc = peer_ptrs, world, rank, mc_ptr
+        self.offset, self.shape, self.scale = offset, tuple(shape), scale
+        self.is_cuda = True
+
+    def numel(self):
+        n = 1
+        for d in self.shape:
+            n *= d
+        return n
+
+
 class OptimKernels:
     """Fused optimizer steps for MuonAdamW (same math as optim.muon_adamw's reference)."""
 
@@ -388,6 +404,15 @@ class OptimKernels:
     def adamw_group(self, st, grad, pv, step, lr, b1, b2, eps, wd):
         n = grad.numel()
         bc1, bc2 = 1.0 - b1 ** step, 1.0 - b2 ** step
+        if isinstance(grad, PeerGrad):
+            shadow = pv if pv.dtype == torch.bfloat16 else None
+            K._check(K.lib().arb_adamw_rs(st["master"].data_ptr(), grad.peer_ptrs, grad.world, grad.rank, grad.mc, grad.offset,
+                                          grad.scale, st["m"].data_ptr(), st["v"].data_ptr(),
+                                          shadow.data_ptr() if shadow is not None else 0, n, lr, b1, b2, eps, wd, bc1, bc2,
+                                          K._stream()), "adamw_rs")
+            if shadow is None:
+                pv.copy_(st["master"])
+            return
         g = grad if grad.dtype == torch.float32 else grad.float()
         shadow = pv if pv.dtype == torch.bfloat16 else None
         K._check(K.lib().arb_adamw(st["master"].data_ptr(), g.data_ptr(), st["m"].data_ptr(), st["v"].data_ptr(),
@@ -400,19 +425,26 @@ class OptimKernels:
         from ..optim import muon_adamw as MA
         G, m, n = grad.shape
         if min(m, n) < self.MIN_GEMM_DIM or pv.dtype != torch.bfloat16 or (m % 8) or (n % 8):
+            if isinstance(grad, PeerGrad):
+                raise RuntimeError("small Muon groups take the unfused path: reduce them first")
             u = MA.muon_nesterov(st["momentum"], grad.float(), mu, torch.bfloat16)
             x = MA.newton_schulz(MA.frob_normalise(u), ns_steps)
             gfin = MA.normuon(x, st["second"], beta2)
             MA.cautious_update(st["master"], gfin, lr, wd)
             pv.copy_(st["master"])
             return
-        dev = grad.device
+        dev = pv.device
         L = K.lib()
         s = K._stream()
         x = torch.empty(G, m, n, dtype=torch.bfloat16, device=dev)
         sumsq = torch.empty(G, dtype=torch.float32, device=dev)
-        K._check(L.arb_muon_nesterov(st["momentum"].data_ptr(), grad.data_ptr(), x.data_ptr(), sumsq.data_ptr(),
-                                     m * n, G, mu, s), "muon_nesterov")
+        if isinstance(grad, PeerGrad):
+            K._check(L.arb_muon_nesterov_rs(st["momentum"].data_ptr(), grad.peer_ptrs, grad.world, grad.rank, grad.mc,
+                                            grad.offset, grad.scale, x.data_ptr(), sumsq.data_ptr(), m * n, G, mu, s),
+                     "muon_nesterov_rs")
+        else:
+            K._check(L.arb_muon_nesterov(st["momentum"].data_ptr(), grad.data_ptr(), x.data_ptr(), sumsq.data_ptr(),
+                                         m * n, G, mu, s), "muon_nesterov")
         K._check(L.arb_muon_frob_scale(x.data_ptr(), sumsq.data_ptr(), m * n, G, s), "muon_frob_scale")
         tall = m > n
         d = n if tall else m

@@ -149,9 +149,11 @@ class MuonAdamW:
         raise KeyError(kind)
 
     @torch.no_grad()
-    def step(self, step: int, progress: float, warmup_mult: float = 1.0) -> None:
+    def step(self, step: int, progress: float, warmup_mult: float = 1.0, grad_source=None) -> None:
         """`step` is 1-indexed.  Expects the summed gradient of every owned group in
-        ``layout.flat_grad``; writes the updated parameters into ``layout.flat_param``."""
+        ``layout.flat_grad``; writes the updated parameters into ``layout.flat_param``.
+        ``grad_source(group)`` may return another gradient object for a group (the fused
+        data-parallel path hands out descriptors of the un-reduced peer buckets)."""
         c = self.cfg
         lr_mult = S.lr_multiplier(progress, c) * warmup_mult
         mu = S.muon_momentum(step, c)
@@ -159,7 +161,9 @@ class MuonAdamW:
         lay = self.layout
         for gi, st in self.state.items():
             g = lay.groups[gi]
-            grad = lay.group_view(lay.flat_grad, g)
+            grad = grad_source(g) if grad_source is not None else None
+            if grad is None:
+                grad = lay.group_view(lay.flat_grad, g)
             pv = lay.group_view(lay.flat_param, g)
             if g.kind == "muon":
                 m, n = getattr(g.atoms[0].param, "muon_full_shape", g.shape)

@@ -64,6 +64,8 @@ class FusedComm:
         dist.barrier(group=self.group)
         self._param_ptrs = self._ptr_array(self._param.peer_ptrs)
         self._bucket_ptrs = self._ptr_array(self._bucket.peer_ptrs + [self.rank])
+        self._bucket_plain_ptrs = self._ptr_array(self._bucket.peer_ptrs)
+        self._small_ranges = None
         self._flag_ptrs = self._ptr_array(self._flags.peer_ptrs)
         self._mc = self._bucket.multicast_ptr if self.use_multimem else 0
 
@@ -78,6 +80,27 @@ class FusedComm:
                                       K.err_flag(self.device).data_ptr(), K._stream())
         K._check(rc, "peer_barrier")
 
+    fuse_into_optimizer = True
+
+    def grad_source(self, layout: ParamLayout):
+        """Per owned group: a descriptor of the un-reduced bf16 buckets, so that the optimizer
+        kernels do the cross-rank sum themselves.  Groups that take the unfused optimizer path
+        (tiny matrices) return None and read the separately reduced fp32 gradient."""
+        from ..ops.sm100 import OptimKernels, PeerGrad
+        if not (self.fuse_into_optimizer and self.bucket_dtype == torch.bfloat16):
+            return None
+
+        def src(g):
+            if g.kind == "muon":
+                m, n = g.shape
+                if min(m, n) < OptimKernels.MIN_GEMM_DIM or (m % 8) or (n % 8):
+                    return None
+            elif g.numel % 8:
+                return None
+            return PeerGrad(self._bucket_plain_ptrs, self.world, self.rank, self._mc or 0, g.offset,
+                            (g.count,) + tuple(g.shape), 1.0)
+        return src
+
     def reduce_scatter_grads(self, layout: ParamLayout) -> None:
         lo, hi = layout.shard_range()
         src_bf16 = self.bucket_dtype == torch.bfloat16
@@ -86,14 +109,22 @@ class FusedComm:
         else:
             self._bucket.tensor.copy_(layout.flat_grad)
         self.barrier()
-        out = layout.flat_grad[lo:hi]
         L = K.lib()
-        if self._mc:
-            rc = L.arb_reduce_scatter_multimem(self._mc, lo, hi - lo, int(src_bf16), out.data_ptr(), 1.0, K._stream())
+        src = self.grad_source(layout)
+        if src is not None:
+            # everything the fused optimizer kernels will sum themselves is skipped here
+            ranges = [(g.offset, g.numel) for g in layout.owned_groups() if src(g) is None]
         else:
-            rc = L.arb_reduce_scatter_peers(self._bucket_ptrs, self.world, lo, hi - lo, int(src_bf16), out.data_ptr(),
-                                            1.0, K._stream())
-        K._check(rc, "reduce_scatter")
+            ranges = [(lo, hi - lo)]
+        for off, n in ranges:
+            n8 = (n + 7) // 8 * 8
+            out = layout.flat_grad[off:off + n8]
+            if self._mc:
+                rc = L.arb_reduce_scatter_multimem(self._mc, off, n8, int(src_bf16), out.data_ptr(), 1.0, K._stream())
+            else:
+                rc = L.arb_reduce_scatter_peers(self._bucket_ptrs, self.world, off, n8, int(src_bf16), out.data_ptr(),
+                                                1.0, K._stream())
+            K._check(rc, "reduce_scatter")
 
     def all_gather_params(self, layout: ParamLayout) -> None:
         self.barrier()

@@ -228,7 +228,8 @@ class Trainer:
         self.comm.reduce_scatter_grads(self.layout)
         progress = self.wsd.progress(self.step)
         wm = warmup_multiplier(self.step + 1, self.wsd.warmup_steps)
-        self.opt.step(self.step + 1, progress, wm)
+        gs = self.comm.grad_source(self.layout) if hasattr(self.comm, "grad_source") else None
+        self.opt.step(self.step + 1, progress, wm, grad_source=gs)
         if self.expert_opt is not None:
             self.expert_opt.step(self.step + 1, progress, wm)
         self.comm.all_gather_params(self.layout)
