@@ -25,8 +25,42 @@ def timeit(fn, iters, warmup):
     return e0.elapsed_time(e1) / iters
 
 
+HEADLINE_SHAPES = [  # (name, M, N, K, layout) at the 428 M config, 131072 tokens per micro-batch
+    ("qkv fwd", 131072, 3072, 1024, "nt"), ("o-proj fwd", 131072, 1024, 1024, "nt"),
+    ("fc1 fwd", 131072, 4096, 1024, "nt"), ("fc2 fwd", 131072, 1024, 4096, "nt"),
+    ("fc2 dX", 131072, 4096, 1024, "nn"), ("qkv dX", 131072, 1024, 3072, "nn"),
+    ("fc1 dW", 4096, 1024, 131072, "tn"), ("o-proj dW", 1024, 1024, 131072, "tn"),
+    ("lm head chunk", 16384, 8192, 1024, "nt"),
+]
+
+
+def table(iters=10, warmup=3):
+    """Markdown table of the headline shapes: own kernel vs torch.matmul, CUDA events."""
+    rows = ["| GEMM | M | N | K | layout | own ms | own TFLOP/s | cuBLAS ms | cuBLAS TFLOP/s | ratio |", "|---|---|---|---|---|---|---|---|---|---|"]
+    g = torch.Generator(device="cuda").manual_seed(0)
+    r = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
+    for name, M, N, Kd, lay in HEADLINE_SHAPES:
+        if lay == "nt":
+            x, w = r(M, Kd), r(N, Kd)
+            f, ref = (lambda: K.gemm(x, w)), (lambda: x @ w.t())
+        elif lay == "nn":
+            x, w = r(M, Kd), r(Kd, N)
+            f, ref = (lambda: K.gemm(x, w, trans_b=False)), (lambda: x @ w)
+        else:
+            x, w = r(Kd, M), r(Kd, N)
+            acc = torch.zeros(M, N, device="cuda")
+            f, ref = (lambda: K.gemm(x, w, trans_a=True, trans_b=False, out=acc, epi=K.EPI_ATOMIC_F32)), (lambda: x.t() @ w)
+        t1, t2 = timeit(f, iters, warmup), timeit(ref, iters, warmup)
+        fl = 2.0 * M * N * Kd / 1e9
+        rows.append(f"| {name} | {M} | {N} | {Kd} | {lay} | {t1:.3f} | {fl / t1:.0f} | {t2:.3f} | {fl / t2:.0f} | {t2 / t1:.2f} |")
+        del x, w
+    K.check_err_flag()
+    return "\n".join(rows)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--table", action="store_true", help="print the headline-shape table and exit")
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=1024)
@@ -37,6 +71,9 @@ def main():
     ap.add_argument("--no-ref", action="store_true")
     ap.add_argument("--flags", type=int, default=0)
     a = ap.parse_args()
+    if a.table:
+        print(table(a.iters, a.warmup))
+        return
     K.gemm_set_mode(a.mode)
     if a.flags:
         import ctypes
