@@ -172,6 +172,35 @@ class BaselineBackend(OracleBackend):
                 self._flash = False
         return self._flash
 
+    # elementwise ops stay in the activation dtype (library kernels, no fp32 copies kept for backward)
+    def rmsnorm(self, x):
+        return F.rms_norm(x, (x.shape[-1],), eps=self.eps)
+
+    def resid_scale_norm(self, x, x0, lam_r, lam_0, i):
+        xs = lam_r[i] * x + lam_0[i] * x0
+        return xs, self.rmsnorm(xs)
+
+    def add_norm(self, x, proj):
+        xs = x + proj
+        return xs, self.rmsnorm(xs)
+
+    def residual_add(self, x, y):
+        return x + y
+
+    def linear_col_relu_sq(self, x, w):
+        return F.relu(R.linear(x, w)).square()
+
+    def rope_qknorm(self, x, cos, sin):
+        B, T, H, hd = x.shape
+        half = hd // 2
+        lo, hi = x[..., :half], x[..., half:]
+        c = cos[:T].to(x.dtype).view(1, T, 1, half)
+        s = sin[:T].to(x.dtype).view(1, T, 1, half)
+        return self.rmsnorm(torch.cat([lo * c + hi * s, hi * c - lo * s], dim=-1))
+
+    def ve_apply(self, v, ve, gate):
+        return v + (2.0 * torch.sigmoid(gate)).unsqueeze(-1).to(v.dtype) * ve
+
     def attention(self, q, k, v, window):
         B, T, H, hd = q.shape
         if not q.is_cuda:

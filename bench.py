@@ -18,6 +18,7 @@ import sys
 import time
 
 BASELINE_TOK_S = 52643.0  # reference, 1x H100 SXM, results/480m_30pct_cooldown/train.log
+PUBLISHED = {"phase2": 52643.0, "phase1": 349500.0}   # reference tokens/s on 1x H100 SXM
 
 
 def main() -> int:
@@ -69,6 +70,8 @@ def main() -> int:
     mcfg = model_preset(args.model, **over)
     sched = ScheduleConfig(peak_lr=0.02, weight_decay=0.3, final_lr_frac=0.02,
                            embedding_lr=0.45, unembedding_lr=0.0025, scalar_lr=0.25)
+    if args.impl == "baseline" and args.micro_batch == 4:
+        args.micro_batch = 2   # the library arm keeps every autograd intermediate: 4 x 32768 tokens do not fit
     tcfg = TrainConfig(device_batch_size=args.micro_batch, total_batch_size=args.total_batch,
                        max_steps=1000, cooldown_steps=300, synthetic_data=True, synthetic_kind="zipf",
                        impl=args.impl, schedule_cfg=sched, cooldown_trigger_file="",
@@ -114,11 +117,13 @@ def main() -> int:
     value = tokens_step * args.steps / (ms / 1e3)
     e2e = tokens_step * args.steps / e2e_s
     valid = args.layers is None and args.seq_len is None and args.model == "phase2" and args.total_batch == 524288
+    published = PUBLISHED.get(args.model) if (args.layers is None and args.seq_len is None and args.total_batch == 524288) else None
     out = {
-        "metric": "train tokens/sec, 428M D1024 L30 T32K (device-timed, max/rank)",
+        "metric": ("train tokens/sec, 428M D1024 L30 T32K (device-timed, max/rank)" if args.model == "phase2"
+                   else f"train tokens/sec, {args.model} (device-timed, max/rank)"),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 2), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": (round(value / BASELINE_TOK_S, 3) if world == 1 and valid else None),
+        "scaling": "strong", "vs_baseline": (round(value / published, 3) if world == 1 and published else None),
         "dtype": "bf16", "data": "synthetic Zipf(1.1) token ids from a seed; random-init weights",
         "impl": args.impl,
         "config": {"model": f"{mcfg.name} {mcfg.num_params()['total'] / 1e6:.1f}M D{mcfg.d_model} L{mcfg.n_layer} T{mcfg.seq_len}",
