@@ -44,6 +44,8 @@ int arb_gemm_set_mode(int mode);
 // q, k, v, o: [B, T, H, hd=128] bf16 with token stride `ld*` elements (head h at column
 // h*128); lse: [B, H, T] fp32.  window >= T means plain causal; key j is visible to query i
 // iff i - window <= j <= i.
+// 1 (default): P / dS reach the second MMA through TMEM; 0: through shared memory (A/B comparison)
+void arb_attn_set_mode(int ts);
 int arb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int H,
                  long long ldq, long long ldk, long long ldv, long long ldo, int window, float scale,
                  int* err_flag, cudaStream_t stream);

@@ -52,32 +52,41 @@ __device__ __forceinline__ void named_bar_sync(int id, int count) {
 // ===============================================================================================
 // Forward
 // ===============================================================================================
-struct FwdSmem {
+// TS = the bf16 probabilities are handed to the P*V MMA through TMEM (A operand from tensor
+// memory) instead of swizzled shared memory.  Shared-memory bandwidth (128 B/clk) is what bounds
+// these kernels: an SS MMA of M=128, N=128, K=16 reads 8 KB of operands for 64 clk of math, so every
+// operand that stays out of shared memory counts.  The freed 64 KB hold a third K/V stage.
+template <bool TS>
+struct FwdSmemT {
+  static constexpr int STAGES = TS ? 3 : 2;
   static constexpr int Q = 0;
-  static constexpr int K0 = 32768;            // 2 stages of 32 KB
-  static constexpr int V0 = K0 + 2 * 32768;   // 2 stages of 32 KB
-  static constexpr int P0 = V0 + 2 * 32768;   // 2 buffers of 32 KB
-  static constexpr int BAR = P0 + 2 * 32768;
+  static constexpr int K0 = 32768;                 // STAGES x 32 KB
+  static constexpr int V0 = K0 + STAGES * 32768;   // STAGES x 32 KB
+  static constexpr int P0 = V0 + STAGES * 32768;   // SS only: 2 buffers of 32 KB
+  static constexpr int BAR = P0 + (TS ? 0 : 2 * 32768);
   static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
+template <bool TS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmV, const AttnArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using FwdSmem = FwdSmemT<TS>;
+  constexpr int ST = FwdSmem::STAGES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FwdSmem::BAR);
   uint64_t* q_full = bars;             // 1
-  uint64_t* k_full = bars + 1;         // 2
-  uint64_t* k_empty = bars + 3;        // 2
-  uint64_t* v_full = bars + 5;         // 2
-  uint64_t* v_empty = bars + 7;        // 2
-  uint64_t* s_full = bars + 9;         // 2
-  uint64_t* s_empty = bars + 11;       // 2
-  uint64_t* p_full = bars + 13;        // 2
-  uint64_t* p_empty = bars + 15;       // 2
-  uint64_t* o_done = bars + 17;        // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* k_full = bars + 1;         // ST
+  uint64_t* k_empty = k_full + ST;     // ST
+  uint64_t* v_full = k_empty + ST;     // ST
+  uint64_t* v_empty = v_full + ST;     // ST
+  uint64_t* s_full = v_empty + ST;     // 2
+  uint64_t* s_empty = s_full + 2;      // 2
+  uint64_t* p_full = s_empty + 2;      // 2
+  uint64_t* p_empty = p_full + 2;      // 2
+  uint64_t* o_done = p_empty + 2;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -92,9 +101,11 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < ST; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
       mbar_init(&p_full[i], 4); mbar_init(&p_empty[i], 1);
     }
@@ -107,7 +118,7 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t TM_S = tmem, TM_O = tmem + 256;
+  const uint32_t TM_S = tmem, TM_O = tmem + 256, TM_P = tmem + 384;   // S[2] x 128, O 128, P[2] x 64 (TS)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -116,8 +127,8 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       tma_load_4d(smem + FwdSmem::Q, &tmQ, q_full, 0, h, m0, b);
       tma_load_4d(smem + FwdSmem::Q + 16384, &tmQ, q_full, 64, h, m0, b);
       for (int t = 0; t < n_tiles; ++t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+        const int s = t % ST;
+        const uint32_t ph = (t / ST) & 1;
         const int n0 = (j_lo + t) * 128;
         if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag)) break;
         mbar_expect_tx(&k_full[s], 32768);
@@ -136,39 +147,44 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const uint32_t sq = smem_u32(smem + FwdSmem::Q);
       bool ok = mbar_wait(q_full, 0, abort_flag);
       auto issue_s = [&](int t) -> bool {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, abort_flag)) return false;
-        if (!mbar_wait(&s_empty[s], ph ^ 1, abort_flag)) return false;
+        const int s = t % ST, sb = t & 1;
+        if (!mbar_wait(&k_full[s], (t / ST) & 1, abort_flag)) return false;
+        if (!mbar_wait(&s_empty[sb], ((t >> 1) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + FwdSmem::K0 + s * 32768);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
-          tc_mma_ss(TM_S + s * 128, make_smem_desc(sq + off, 0, 1024), make_smem_desc(sk + off, 0, 1024), idesc_s, k > 0);
+          tc_mma_ss(TM_S + sb * 128, make_smem_desc(sq + off, 0, 1024), make_smem_desc(sk + off, 0, 1024), idesc_s, k > 0);
         }
         tc_commit(&k_empty[s]);
-        tc_commit(&s_full[s]);
+        tc_commit(&s_full[sb]);
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int t = 0; t < n_tiles && ok; ++t) {
         if (t + 1 < n_tiles) { ok = issue_s(t + 1); if (!ok) break; }
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(&p_full[s], ph, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
+        const int s = t % ST, pb = t & 1;
+        if (!mbar_wait(&p_full[pb], (t >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&v_full[s], (t / ST) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sp = smem_u32(smem + FwdSmem::P0 + s * 32768);
         const uint32_t sv = smem_u32(smem + FwdSmem::V0 + s * 32768);
+        if constexpr (TS) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
-          tc_mma_ss(TM_O, make_smem_desc(sp + aoff, 0, 1024), make_smem_desc(sv + k * 2048, 16384, 1024), idesc_o,
-                    (t > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 8; ++k)
+            tc_mma_ts(TM_O, TM_P + uint32_t(pb * 64 + k * 8), make_smem_desc(sv + k * 2048, 16384, 1024), idesc_o,
+                      (t > 0 || k > 0) ? 1u : 0u);
+        } else {
+          const uint32_t sp = smem_u32(smem + FwdSmem::P0 + pb * 32768);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t aoff = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
+            tc_mma_ss(TM_O, make_smem_desc(sp + aoff, 0, 1024), make_smem_desc(sv + k * 2048, 16384, 1024), idesc_o,
+                      (t > 0 || k > 0) ? 1u : 0u);
+          }
         }
         tc_commit(&v_empty[s]);
-        tc_commit(&p_empty[s]);
+        tc_commit(&p_empty[pb]);
       }
       if (ok) tc_commit(o_done);
     }
@@ -238,19 +254,35 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const float mc = (m_used == -INFINITY) ? 0.f : m_used * c;
       // P buffer s was last read by the PV MMA of tile t-2
       if (t >= 2 && !mbar_wait(&p_empty[s], ((t - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
-      const uint32_t pbase = smem_u32(smem + FwdSmem::P0 + s * 32768);
       float rs = 0.f;
+      if constexpr (TS) {
 #pragma unroll
-      for (int j = 0; j < 128; j += 8) {
-        float e[8];
+        for (int hf = 0; hf < 2; ++hf) {   // 64 keys -> 32 packed columns
+          uint32_t pk[32];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { e[u] = fast_exp2(sc[j + u] * c - mc); rs += e[u]; }
-        uint4 pk;
-        pk.x = pack_bf16(e[0], e[1]); pk.y = pack_bf16(e[2], e[3]); pk.z = pack_bf16(e[4], e[5]); pk.w = pack_bf16(e[6], e[7]);
-        st_sw128(pbase, 128, r, j, pk);
+          for (int j = 0; j < 32; ++j) {
+            const float e0 = fast_exp2(sc[hf * 64 + 2 * j] * c - mc), e1 = fast_exp2(sc[hf * 64 + 2 * j + 1] * c - mc);
+            rs += e0 + e1;
+            pk[j] = pack_bf16(e0, e1);
+          }
+          tmem_st32(TM_P + lane_addr + uint32_t(s * 64 + hf * 32), pk);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+      } else {
+        const uint32_t pbase = smem_u32(smem + FwdSmem::P0 + s * 32768);
+#pragma unroll
+        for (int j = 0; j < 128; j += 8) {
+          float e[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) { e[u] = fast_exp2(sc[j + u] * c - mc); rs += e[u]; }
+          uint4 pk;
+          pk.x = pack_bf16(e[0], e[1]); pk.y = pack_bf16(e[2], e[3]); pk.z = pack_bf16(e[4], e[5]); pk.w = pack_bf16(e[6], e[7]);
+          st_sw128(pbase, 128, r, j, pk);
+        }
+        fence_proxy_async_smem();
       }
       l += rs;
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[s]);
     }
@@ -291,7 +323,7 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 // ===============================================================================================
 constexpr int BWD_STAGES = 4;
 
-// p = exp2(s*c - lse2), ds = p * (dp - delta) * scale for 32 columns of one row; results packed
+// p = exp2(s*c - lse2), ds = p * (dp - delta) for 32 columns of one row; results packed
 // to bf16 pairs.  ROWSTAT: lse2/delta are per-row scalars (dQ kernel); otherwise per-column
 // arrays (dK/dV kernel, transposed scores).
 template <bool MASK, bool ROWSTAT, bool WANT_P>
@@ -312,7 +344,7 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t (&sv)[32], const uint32
       e = vis ? e : 0.f;
     }
     pr[j] = e;
-    ds[j] = e * scale * (__uint_as_float(dv[j]) - dl);
+    ds[j] = e * (__uint_as_float(dv[j]) - dl);   // the 1/sqrt(hd) factor is applied once, to dQ / dK
   }
 #pragma unroll
   for (int j = 0; j < 32; j += 2) {
@@ -329,6 +361,7 @@ struct DqSmem {
   static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
+template <bool TS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const AttnArgs p) {
@@ -341,9 +374,9 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint64_t* v_empty = k_empty + BWD_STAGES;         // [4] released by the dP MMA
   uint64_t* sd_full = v_empty + BWD_STAGES;         // [2]
   uint64_t* sd_empty = sd_full + 2;                 // [2]
-  uint64_t* ds_full = sd_empty + 2;
-  uint64_t* ds_empty = ds_full + 1;
-  uint64_t* done = ds_empty + 1;
+  uint64_t* ds_full = sd_empty + 2;                 // [2] (SS uses [0] only)
+  uint64_t* ds_empty = ds_full + 2;                 // [2]
+  uint64_t* done = ds_empty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -360,7 +393,8 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     mbar_init(q_full, 1);
     for (int i = 0; i < BWD_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&sd_full[i], 1); mbar_init(&sd_empty[i], 4); }
-    mbar_init(ds_full, 4); mbar_init(ds_empty, 1); mbar_init(done, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&ds_full[i], 4); mbar_init(&ds_empty[i], 1); }
+    mbar_init(done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -369,7 +403,12 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t TM_S = tmem, TM_DP = tmem + 128, TM_DQ = tmem + 256;   // S[2] x 64, dP[2] x 64, dQ 128
+  // S[2] x 64, dP[2] x 64, dQ 128, dS[2] x 32 (bf16 pairs; TS only)
+  const uint32_t TM_S = tmem, TM_DP = tmem + 128, TM_DQ = tmem + 256, TM_DS = tmem + 384;
+  // dS hand-off: TS double-buffers it in TMEM, SS has one shared-memory buffer
+  auto ds_buf = [](int t) { return TS ? (t & 1) : 0; };
+  auto ds_phase = [](int t) -> uint32_t { return TS ? uint32_t((t >> 1) & 1) : uint32_t(t & 1); };
+  constexpr int DS_BUFS = TS ? 2 : 1;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -426,15 +465,20 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int t = 0; t < n_sub && ok; ++t) {
         if (t + 1 < n_sub) { ok = issue_sd(t + 1); if (!ok) break; }
         const int s = t % BWD_STAGES;
-        if (!mbar_wait(ds_full, t & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&ds_full[ds_buf(t)], ds_phase(t), abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + DqSmem::KV0 + s * 32768);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(TM_DQ, make_smem_desc(sds + k * 32, 0, 1024), make_smem_desc(sk + k * 2048, 8192, 1024), idesc_o,
-                    (t > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) {
+          if constexpr (TS)
+            tc_mma_ts(TM_DQ, TM_DS + uint32_t(ds_buf(t) * 32 + k * 8), make_smem_desc(sk + k * 2048, 8192, 1024), idesc_o,
+                      (t > 0 || k > 0) ? 1u : 0u);
+          else
+            tc_mma_ss(TM_DQ, make_smem_desc(sds + k * 32, 0, 1024), make_smem_desc(sk + k * 2048, 8192, 1024), idesc_o,
+                      (t > 0 || k > 0) ? 1u : 0u);
+        }
         tc_commit(&k_empty[s]);
-        tc_commit(ds_empty);
+        tc_commit(&ds_empty[ds_buf(t)]);
       }
       if (ok) tc_commit(done);
     }
@@ -468,13 +512,20 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sd_empty[buf]);
-      if (t >= 1 && !mbar_wait(ds_empty, (t - 1) & 1, abort_flag)) { ok = false; break; }
+      // the dQ MMA that last read this dS buffer (sub-tile t - DS_BUFS) has to be complete
+      if (t >= DS_BUFS && !mbar_wait(&ds_empty[ds_buf(t)], ds_phase(t - DS_BUFS), abort_flag)) { ok = false; break; }
+      if constexpr (TS) {
+        tmem_st32(TM_DS + lane_addr + uint32_t(buf * 32), ds_pk);
+        tmem_wait_st();
+        tc_fence_before();
+      } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        st_sw128(dsbase, 128, r, j * 8, make_uint4(ds_pk[j * 4], ds_pk[j * 4 + 1], ds_pk[j * 4 + 2], ds_pk[j * 4 + 3]));
-      fence_proxy_async_smem();
+        for (int j = 0; j < 8; ++j)
+          st_sw128(dsbase, 128, r, j * 8, make_uint4(ds_pk[j * 4], ds_pk[j * 4 + 1], ds_pk[j * 4 + 2], ds_pk[j * 4 + 3]));
+        fence_proxy_async_smem();
+      }
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
+      if (lane == 0) mbar_arrive(&ds_full[ds_buf(t)]);
     }
     if (ok && mbar_wait(done, 0, abort_flag)) {
       tc_fence_after();
@@ -488,10 +539,11 @@ attn_bwd_dq_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             uint4 u;
-            u.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-            u.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-            u.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-            u.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+            const float sc = p.scale;
+            u.x = pack_bf16(__uint_as_float(v[j]) * sc, __uint_as_float(v[j + 1]) * sc);
+            u.y = pack_bf16(__uint_as_float(v[j + 2]) * sc, __uint_as_float(v[j + 3]) * sc);
+            u.z = pack_bf16(__uint_as_float(v[j + 4]) * sc, __uint_as_float(v[j + 5]) * sc);
+            u.w = pack_bf16(__uint_as_float(v[j + 6]) * sc, __uint_as_float(v[j + 7]) * sc);
             *reinterpret_cast<uint4*>(orow + cc * 32 + j) = u;
           }
         }
@@ -517,6 +569,12 @@ struct DkvSmem {
   static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
+// TS: P^T and dS^T (bf16 pairs, 32 columns each) overwrite the first half of the S^T / dP^T
+// buffer they were computed from; every thread overwrites only its own lane after reading it.  The
+// S^T / dP^T MMAs of sub-tile t+2 reuse those columns and are issued after the dV / dK MMAs of
+// sub-tile t (MMAs of one thread execute in issue order), which in turn are issued only after the
+// softmax warps have signalled pd_full(t); no separate "empty" barriers are needed.
+template <bool TS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const AttnArgs p) {
@@ -528,8 +586,8 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint64_t* q_empty = q_full + BWD_STAGES;          // [4] released by the dV/dK MMAs
   uint64_t* sd_full = q_empty + BWD_STAGES;         // [2]
   uint64_t* sd_empty = sd_full + 2;                 // [2]
-  uint64_t* pd_full = sd_empty + 2;
-  uint64_t* pd_empty = pd_full + 1;
+  uint64_t* pd_full = sd_empty + 2;                 // [2] (SS uses [0] only)
+  uint64_t* pd_empty = pd_full + 2;
   uint64_t* done = pd_empty + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -548,7 +606,7 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_init(kv_full, 1);
     for (int i = 0; i < BWD_STAGES; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&sd_full[i], 1); mbar_init(&sd_empty[i], 4); }
-    mbar_init(pd_full, 4); mbar_init(pd_empty, 1); mbar_init(done, 1);
+    mbar_init(&pd_full[0], 4); mbar_init(&pd_full[1], 4); mbar_init(pd_empty, 1); mbar_init(done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -590,7 +648,7 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       auto issue_sd = [&](int t) -> bool {
         const int s = t % BWD_STAGES, buf = t & 1;
         if (!mbar_wait(&q_full[s], (t / BWD_STAGES) & 1, abort_flag)) return false;
-        if (!mbar_wait(&sd_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag)) return false;
+        if (!TS && !mbar_wait(&sd_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + DkvSmem::QD0 + s * 32768), sdo = sq + 16384;
 #pragma unroll
@@ -612,19 +670,28 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int t = 0; t < n_sub && ok; ++t) {
         if (t + 1 < n_sub) { ok = issue_sd(t + 1); if (!ok) break; }
         const int s = t % BWD_STAGES;
-        if (!mbar_wait(pd_full, t & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&pd_full[TS ? (t & 1) : 0], TS ? uint32_t((t >> 1) & 1) : uint32_t(t & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + DkvSmem::QD0 + s * 32768), sdo = sq + 16384;
+        const uint32_t acc = (t > 0) ? 1u : 0u;
+        if constexpr (TS) {
+          const uint32_t buf = uint32_t(t & 1);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(TM_DV, make_smem_desc(spt + k * 32, 0, 1024), make_smem_desc(sdo + k * 2048, 8192, 1024), idesc_o,
-                    (t > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            tc_mma_ts(TM_DV, TM_S + buf * 64 + k * 8, make_smem_desc(sdo + k * 2048, 8192, 1024), idesc_o, k > 0 ? 1u : acc);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ss(TM_DK, make_smem_desc(sdst + k * 32, 0, 1024), make_smem_desc(sq + k * 2048, 8192, 1024), idesc_o,
-                    (t > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            tc_mma_ts(TM_DK, TM_DP + buf * 64 + k * 8, make_smem_desc(sq + k * 2048, 8192, 1024), idesc_o, k > 0 ? 1u : acc);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_ss(TM_DV, make_smem_desc(spt + k * 32, 0, 1024), make_smem_desc(sdo + k * 2048, 8192, 1024), idesc_o, k > 0 ? 1u : acc);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_ss(TM_DK, make_smem_desc(sdst + k * 32, 0, 1024), make_smem_desc(sq + k * 2048, 8192, 1024), idesc_o, k > 0 ? 1u : acc);
+        }
         tc_commit(&q_empty[s]);
-        tc_commit(pd_empty);
+        if (!TS) tc_commit(pd_empty);
       }
       if (ok) tc_commit(done);
     }
@@ -668,19 +735,28 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (need_mask) bwd_chunk<true, false, true>(sv, dv, c, p.scale, 0.f, 0.f, cl, cd, key, q0 + cc * 32, p.window, p.T, false, p_pk + cc * 16, ds_pk + cc * 16);
           else bwd_chunk<false, false, true>(sv, dv, c, p.scale, 0.f, 0.f, cl, cd, key, q0 + cc * 32, p.window, p.T, false, p_pk + cc * 16, ds_pk + cc * 16);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sd_empty[buf]);
-        if (t >= 1 && !mbar_wait(pd_empty, (t - 1) & 1, abort_flag)) ok = false;
-        if (ok) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            st_sw128(ptbase, 128, r, j * 8, make_uint4(p_pk[j * 4], p_pk[j * 4 + 1], p_pk[j * 4 + 2], p_pk[j * 4 + 3]));
-            st_sw128(dstbase, 128, r, j * 8, make_uint4(ds_pk[j * 4], ds_pk[j * 4 + 1], ds_pk[j * 4 + 2], ds_pk[j * 4 + 3]));
-          }
-          fence_proxy_async_smem();
+        if constexpr (TS) {
+          tmem_st32(TM_S + lane_addr + uint32_t(buf * 64), p_pk);
+          tmem_st32(TM_DP + lane_addr + uint32_t(buf * 64), ds_pk);
+          tmem_wait_st();
+          tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(pd_full);
+          if (lane == 0) mbar_arrive(&pd_full[buf]);
+        } else {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sd_empty[buf]);
+          if (t >= 1 && !mbar_wait(pd_empty, (t - 1) & 1, abort_flag)) ok = false;
+          if (ok) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              st_sw128(ptbase, 128, r, j * 8, make_uint4(p_pk[j * 4], p_pk[j * 4 + 1], p_pk[j * 4 + 2], p_pk[j * 4 + 3]));
+              st_sw128(dstbase, 128, r, j * 8, make_uint4(ds_pk[j * 4], ds_pk[j * 4 + 1], ds_pk[j * 4 + 2], ds_pk[j * 4 + 3]));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pd_full[0]);
+          }
         }
       }
       (tid < 64 ? stat_lse : stat_dl)[((t + 1) & 1) * 64 + (tid & 63)] = next_stat;
@@ -698,13 +774,14 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tmem_wait_ld();
           if (key < p.T) {
             __nv_bfloat16* dst = (which ? dkrow : dvrow) + cc * 32;
+            const float sc = which ? p.scale : 1.f;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               uint4 u;
-              u.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-              u.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-              u.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-              u.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+              u.x = pack_bf16(__uint_as_float(v[j]) * sc, __uint_as_float(v[j + 1]) * sc);
+              u.y = pack_bf16(__uint_as_float(v[j + 2]) * sc, __uint_as_float(v[j + 3]) * sc);
+              u.z = pack_bf16(__uint_as_float(v[j + 4]) * sc, __uint_as_float(v[j + 5]) * sc);
+              u.w = pack_bf16(__uint_as_float(v[j + 6]) * sc, __uint_as_float(v[j + 7]) * sc);
               *reinterpret_cast<uint4*>(dst + j) = u;
             }
           }
@@ -758,6 +835,38 @@ static int set_smem(Kern k, int bytes) {
 
 using namespace arb;
 
+// 1 (default): P / dS operands through TMEM; 0: through swizzled shared memory (kept for A/B runs)
+static int g_attn_ts = 1;
+extern "C" void arb_attn_set_mode(int ts) { g_attn_ts = ts ? 1 : 0; }
+
+template <bool TS>
+static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a, dim3 grid,
+                      cudaStream_t stream) {
+  static bool cfg = false;
+  int r;
+  if (!cfg) { if ((r = set_smem(attn_fwd_k<TS>, FwdSmemT<TS>::TOTAL))) return r; cfg = true; }
+  attn_fwd_k<TS><<<grid, ATT_THREADS, FwdSmemT<TS>::TOTAL, stream>>>(tq, tk, tv, a);
+  return int(cudaGetLastError());
+}
+template <bool TS>
+static int launch_dq(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                     const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+  static bool cfg = false;
+  int r;
+  if (!cfg) { if ((r = set_smem(attn_bwd_dq_k<TS>, DqSmem::TOTAL))) return r; cfg = true; }
+  attn_bwd_dq_k<TS><<<grid, ATT_THREADS, DqSmem::TOTAL, stream>>>(tq, tk, tv, tdo, a);
+  return int(cudaGetLastError());
+}
+template <bool TS>
+static int launch_dkv(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                      const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+  static bool cfg = false;
+  int r;
+  if (!cfg) { if ((r = set_smem(attn_bwd_dkv_k<TS>, DkvSmem::TOTAL))) return r; cfg = true; }
+  attn_bwd_dkv_k<TS><<<grid, ATT_THREADS, DkvSmem::TOTAL, stream>>>(tq, tk, tv, tdo, a);
+  return int(cudaGetLastError());
+}
+
 extern "C" int arb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int H,
                             long long ldq, long long ldk, long long ldv, long long ldo, int window, float scale,
                             int* err_flag, cudaStream_t stream) {
@@ -769,14 +878,11 @@ extern "C" int arb_attn_fwd(const void* q, const void* k, const void* v, void* o
   if ((r = make_qkv_tmap(&tq, q, B, T, H, ldq, 128))) return 1000 + r;
   if ((r = make_qkv_tmap(&tk, k, B, T, H, ldk, 128))) return 1000 + r;
   if ((r = make_qkv_tmap(&tv, v, B, T, H, ldv, 128))) return 1000 + r;
-  static bool cfg = false;
-  if (!cfg) { if ((r = set_smem(attn_fwd_k, FwdSmem::TOTAL))) return r; cfg = true; }
   AttnArgs a{};
   a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
   a.o = o; a.ldo = ldo; a.lse = lse; a.err = err_flag;
   dim3 grid((T + 127) / 128, H, B);
-  attn_fwd_k<<<grid, ATT_THREADS, FwdSmem::TOTAL, stream>>>(tq, tk, tv, a);
-  return int(cudaGetLastError());
+  return g_attn_ts ? launch_fwd<true>(tq, tk, tv, a, grid, stream) : launch_fwd<false>(tq, tk, tv, a, grid, stream);
 }
 
 extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
@@ -790,12 +896,6 @@ extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const v
   int r;
   attn_delta_k<<<unsigned(((long long)B * T * H + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, T, H, ldo, lddo);
   if ((r = int(cudaGetLastError()))) return r;
-  static bool cfg = false;
-  if (!cfg) {
-    if ((r = set_smem(attn_bwd_dq_k, DqSmem::TOTAL))) return r;
-    if ((r = set_smem(attn_bwd_dkv_k, DkvSmem::TOTAL))) return r;
-    cfg = true;
-  }
   AttnArgs a{};
   a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
   a.lse = const_cast<float*>(lse); a.delta = delta; a.err = err_flag;
@@ -807,8 +907,7 @@ extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const v
     if ((r = make_qkv_tmap(&tdo, d_o, B, T, H, lddo, 128))) return 1000 + r;
     a.o = dq; a.ldo = lddq;
     dim3 grid((T + 127) / 128, H, B);
-    attn_bwd_dq_k<<<grid, ATT_THREADS, DqSmem::TOTAL, stream>>>(tq, tk, tv, tdo, a);
-    if ((r = int(cudaGetLastError()))) return r;
+    if ((r = g_attn_ts ? launch_dq<true>(tq, tk, tv, tdo, a, grid, stream) : launch_dq<false>(tq, tk, tv, tdo, a, grid, stream))) return r;
   }
   {
     CUtensorMap tq, tk, tv, tdo;
@@ -818,8 +917,7 @@ extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const v
     if ((r = make_qkv_tmap(&tdo, d_o, B, T, H, lddo, 64))) return 1000 + r;
     a.dk = dk; a.dv = dv; a.lddk = lddk; a.lddv = lddv;
     dim3 grid((T + 127) / 128, H, B);
-    attn_bwd_dkv_k<<<grid, ATT_THREADS, DkvSmem::TOTAL, stream>>>(tq, tk, tv, tdo, a);
-    if ((r = int(cudaGetLastError()))) return r;
+    if ((r = g_attn_ts ? launch_dkv<true>(tq, tk, tv, tdo, a, grid, stream) : launch_dkv<false>(tq, tk, tv, tdo, a, grid, stream))) return r;
   }
   return 0;
 }

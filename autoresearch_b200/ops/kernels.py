@@ -195,6 +195,13 @@ def gemm_set_mode(mode: int) -> None:
         raise ValueError(f"bad GEMM mode {mode}")
 
 
+def attn_set_mode(ts: int) -> None:
+    """1 (default) = P / dS operands of the second attention MMAs live in TMEM, 0 = in shared memory."""
+    f = lib().arb_attn_set_mode
+    f.restype, f.argtypes = None, [C.c_int]
+    f(int(ts))
+
+
 def rmsnorm_fwd(x, eps):
     _bf16(x, "x")
     y = torch.empty_like(x)

@@ -7,7 +7,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(B, T, H, window, seed=0):
+def _run(B, T, H, window, seed=0, tmem_operands=1):
+    from autoresearch_b200.ops import kernels as K, reference as R, sm100
+    K.attn_set_mode(tmem_operands)
+    try:
+        _check(B, T, H, window, seed)
+    finally:
+        K.attn_set_mode(1)
+
+
+def _check(B, T, H, window, seed):
     from autoresearch_b200.ops import kernels as K, reference as R, sm100
     torch.manual_seed(seed)
     Dl = H * 128
@@ -39,6 +48,12 @@ def _run(B, T, H, window, seed=0):
                                          (1, 640, 1, 64), (2, 320, 1, 100), (1, 1536, 2, 1536)])
 def test_attention_matches_reference(B, T, H, window):
     _run(B, T, H, window)
+
+
+@pytest.mark.parametrize("B,T,H,window", [(1, 512, 2, 256), (2, 320, 1, 100), (1, 1536, 2, 1536)])
+def test_attention_smem_operand_path(B, T, H, window):
+    """The variant that stages P / dS in shared memory stays selectable and correct."""
+    _run(B, T, H, window, tmem_operands=0)
 
 
 def test_lse_matches_reference():
