@@ -22,11 +22,11 @@ def main():
     ap.add_argument("--window", type=int, default=None)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=1)
-    ap.add_argument("--smem-operands", action="store_true",
-                    help="hand P / dS to the second MMAs through shared memory instead of TMEM")
+    ap.add_argument("--mode", type=int, default=2,
+                    help="2 = wide backward (default), 1 = 64-wide sub-tiles / TMEM operands, 0 = shared-memory operands")
     a = ap.parse_args()
     W = a.window if a.window is not None else a.T
-    K.attn_set_mode(0 if a.smem_operands else 1)
+    K.attn_set_mode(a.mode)
     Dl = a.H * 128
     torch.manual_seed(0)
     qkv = torch.randn(a.B * a.T, 3 * Dl, device="cuda").to(torch.bfloat16).requires_grad_(True)
@@ -57,7 +57,7 @@ def main():
     tb /= a.iters
     keys = sum(min(i, W) + 1 for i in range(a.T))  # visible (query, key) pairs per head
     flops_f = 4.0 * keys * 128 * a.H * a.B
-    print(json.dumps({"B": a.B, "T": a.T, "H": a.H, "window": W, "operands": "smem" if a.smem_operands else "tmem", "fwd_ms": round(tf, 3), "bwd_ms": round(tb, 3),
+    print(json.dumps({"B": a.B, "T": a.T, "H": a.H, "window": W, "mode": a.mode, "fwd_ms": round(tf, 3), "bwd_ms": round(tb, 3),
                       "fwd_tflops": round(flops_f / tf / 1e9, 1), "bwd_tflops": round(2.5 * flops_f / tb / 1e9, 1)}))
 
 

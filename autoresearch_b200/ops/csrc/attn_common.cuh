@@ -1,0 +1,57 @@
+// Shared pieces of the attention kernels (attn_sm100.cu, attn_wide_sm100.cu).
+#pragma once
+#include "api.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace arb {
+
+constexpr int HD = 128;
+constexpr int ATT_THREADS = 192;        // producer warp, MMA warp, 4 softmax warps
+constexpr int ATT_WIDE_THREADS = 320;   // producer warp, MMA warp, 8 softmax warps
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnArgs {
+  int B, T, H, window;
+  float scale;
+  // forward / dq
+  void* o; long long ldo;            // forward: O [B,T,H,128] bf16 ; dq kernel: dQ
+  float* lse;                        // [B,H,T]
+  const float* delta;                // [B,H,T] (backward)
+  // dkv
+  void* dk; void* dv; long long lddk, lddv;
+  int* err;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// [B, T, H, 128] bf16 view with token stride ld: dims {128, H, T, B}; box {64, 1, rows, 1}
+inline int make_qkv_tmap(CUtensorMap* m, const void* base, int B, int T, int H, long long ld, int box_rows) {
+  uint64_t dims[4] = {128, uint64_t(H), uint64_t(T), uint64_t(B)};
+  uint64_t str[3] = {256, uint64_t(ld) * 2, uint64_t(ld) * 2 * uint64_t(T)};
+  uint32_t box[4] = {64, 1, uint32_t(box_rows), 1};
+  return make_tmap_bf16(m, base, 4, dims, str, box);
+}
+
+inline bool bad_ptr(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
+
+template <typename Kern>
+inline int set_smem(Kern k, int bytes) {
+  return int(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+}
+
+
+// attn_wide_sm100.cu
+int attn_wide_bwd_launch(const void* q, const void* k, const void* v, const void* d_o, void* dq, void* dk, void* dv,
+                         long long ldq, long long ldk, long long ldv, long long lddo, long long lddq, long long lddk,
+                         long long lddv, AttnArgs a, cudaStream_t stream);
+
+}  // namespace arb

@@ -20,34 +20,9 @@
 #include "api.h"
 #include "ptx.cuh"
 #include "tmap.h"
+#include "attn_common.cuh"
 
 namespace arb {
-
-constexpr int HD = 128;
-constexpr int ATT_THREADS = 192;
-constexpr float LOG2E = 1.4426950408889634f;
-
-struct AttnArgs {
-  int B, T, H, window;
-  float scale;
-  // forward / dq
-  void* o; long long ldo;            // forward: O [B,T,H,128] bf16 ; dq kernel: dQ
-  float* lse;                        // [B,H,T]
-  const float* delta;                // [B,H,T] (backward)
-  // dkv
-  void* dk; void* dv; long long lddk, lddv;
-  int* err;
-};
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-__device__ __forceinline__ void named_bar_sync(int id, int count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
 
 // ===============================================================================================
 // Forward
@@ -816,28 +791,14 @@ __global__ void __launch_bounds__(256) attn_delta_k(const __nv_bfloat16* __restr
   }
 }
 
-// [B, T, H, 128] bf16 view with token stride ld: dims {128, H, T, B}; box {64, 1, rows, 1}
-static int make_qkv_tmap(CUtensorMap* m, const void* base, int B, int T, int H, long long ld, int box_rows) {
-  uint64_t dims[4] = {128, uint64_t(H), uint64_t(T), uint64_t(B)};
-  uint64_t str[3] = {256, uint64_t(ld) * 2, uint64_t(ld) * 2 * uint64_t(T)};
-  uint32_t box[4] = {64, 1, uint32_t(box_rows), 1};
-  return make_tmap_bf16(m, base, 4, dims, str, box);
-}
-
-static bool bad_ptr(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
-
-template <typename Kern>
-static int set_smem(Kern k, int bytes) {
-  return int(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-}
-
 }  // namespace arb
 
 using namespace arb;
 
-// 1 (default): P / dS operands through TMEM; 0: through swizzled shared memory (kept for A/B runs)
+// 2 (default): wide backward; 1: 64-wide sub-tiles with TMEM operands; 0: with shared-memory operands
+static int g_attn_mode = 2;
 static int g_attn_ts = 1;
-extern "C" void arb_attn_set_mode(int ts) { g_attn_ts = ts ? 1 : 0; }
+extern "C" void arb_attn_set_mode(int mode) { g_attn_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode); g_attn_ts = g_attn_mode ? 1 : 0; }
 
 template <bool TS>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a, dim3 grid,
@@ -899,6 +860,8 @@ extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const v
   AttnArgs a{};
   a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
   a.lse = const_cast<float*>(lse); a.delta = delta; a.err = err_flag;
+  if (g_attn_mode == 2)
+    return attn_wide_bwd_launch(q, k, v, d_o, dq, dk, dv, ldq, ldk, ldv, lddo, lddq, lddk, lddv, a, stream);
   {
     CUtensorMap tq, tk, tv, tdo;
     if ((r = make_qkv_tmap(&tq, q, B, T, H, ldq, 128))) return 1000 + r;

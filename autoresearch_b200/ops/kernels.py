@@ -17,7 +17,8 @@ _err_flag = {}
 
 EPI_STORE_BF16, EPI_RELU2, EPI_ATOMIC_F32, EPI_NS_COMBINE, EPI_RELU2_BWD, EPI_STORE_F32, EPI_ADD_AUX = range(7)
 ERR_NAMES = {1: "GEMM barrier wait timed out", 2: "attention barrier wait timed out",
-             3: "peer barrier wait timed out", 4: "MoE dispatch wait timed out"}
+             3: "peer barrier wait timed out", 4: "MoE dispatch wait timed out",
+             5: "dynamic shared memory base is not 1 KB aligned"}
 
 launch_count = 0  # number of kernel-launching calls made through this module
 
@@ -195,11 +196,12 @@ def gemm_set_mode(mode: int) -> None:
         raise ValueError(f"bad GEMM mode {mode}")
 
 
-def attn_set_mode(ts: int) -> None:
-    """1 (default) = P / dS operands of the second attention MMAs live in TMEM, 0 = in shared memory."""
+def attn_set_mode(mode: int) -> None:
+    """2 (default) = backward on 128 x 128 tiles with the two-phase softmax; 1 = 64-wide sub-tiles with
+    P / dS operands in TMEM; 0 = 64-wide sub-tiles with P / dS in shared memory (forward too)."""
     f = lib().arb_attn_set_mode
     f.restype, f.argtypes = None, [C.c_int]
-    f(int(ts))
+    f(int(mode))
 
 
 def rmsnorm_fwd(x, eps):

@@ -7,13 +7,13 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(B, T, H, window, seed=0, tmem_operands=1):
+def _run(B, T, H, window, seed=0, mode=2):
     from autoresearch_b200.ops import kernels as K, reference as R, sm100
-    K.attn_set_mode(tmem_operands)
+    K.attn_set_mode(mode)
     try:
         _check(B, T, H, window, seed)
     finally:
-        K.attn_set_mode(1)
+        K.attn_set_mode(2)
 
 
 def _check(B, T, H, window, seed):
@@ -50,10 +50,17 @@ def test_attention_matches_reference(B, T, H, window):
     _run(B, T, H, window)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("B,T,H,window", [(1, 512, 2, 256), (2, 320, 1, 100), (1, 1536, 2, 1536)])
-def test_attention_smem_operand_path(B, T, H, window):
-    """The variant that stages P / dS in shared memory stays selectable and correct."""
-    _run(B, T, H, window, tmem_operands=0)
+def test_attention_narrow_variants(B, T, H, window, mode):
+    """The 64-wide sub-tile backward (operands in shared memory or TMEM) stays selectable and correct."""
+    _run(B, T, H, window, mode=mode)
+
+
+def test_attention_long_sequence():
+    """Enough tiles for every ring slot and barrier phase to wrap several times."""
+    _run(1, 4096, 1, 4096)
+    _run(1, 4096, 1, 512, seed=3)
 
 
 def test_lse_matches_reference():
