@@ -23,6 +23,8 @@ STAMP = _DIR / "_arb_kernels.stamp"
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+# extra flags for experiments (e.g. ARB_NVCC_EXTRA="-DARB_ATTN_POLY_OF_8=0"); part of the rebuild hash
+NVCC_FLAGS += os.environ.get("ARB_NVCC_EXTRA", "").split()
 
 
 def sources():

@@ -45,9 +45,9 @@ int arb_gemm_set_mode(int mode);
 // q, k, v, o: [B, T, H, hd=128] bf16 with token stride `ld*` elements (head h at column
 // h*128); lse: [B, H, T] fp32.  window >= T means plain causal; key j is visible to query i
 // iff i - window <= j <= i.
-// Backward / operand variant: 2 (default) = 128 x 128 tiles with the two-phase softmax (attn_wide_sm100.cu);
+// Backward variant: 2 (default) = 128 x 128 tiles with the two-phase softmax (attn_wide_sm100.cu);
 // 1 = 64-wide sub-tiles, P / dS through TMEM; 0 = 64-wide sub-tiles, P / dS through shared memory.
-// The forward uses TMEM operands unless the mode is 0.
+// The forward hands P to the second MMA through TMEM unless the mode is 0.
 void arb_attn_set_mode(int mode);
 int arb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int H,
                  long long ldq, long long ldk, long long ldv, long long ldo, int window, float scale,

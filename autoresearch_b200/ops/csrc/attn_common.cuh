@@ -23,6 +23,27 @@ struct AttnArgs {
   int* err;
 };
 
+// Optional per-role cycle accounting (compile with -DARB_ATTN_PROF): each role of the CTA with
+// blockIdx == (0,0,0) sums clock64() deltas between PROF_TOC marks and stores eight counters at
+// arb_attn_prof_buffer[role * 8 ..]; counter 0 is the role's total.  Compiled out by default.
+#ifdef ARB_ATTN_PROF
+__device__ long long* arb_attn_prof_buffer;
+#define PROF_DECL() long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t0 = clock64(); const long long prof_begin = prof_t0
+#define PROF_TIC() prof_t0 = clock64()
+#define PROF_TOC(i) do { const long long prof_t1 = clock64(); prof_acc[i] += prof_t1 - prof_t0; prof_t0 = prof_t1; } while (0)
+#define PROF_DUMP(role)                                                                                   \
+  do {                                                                                                    \
+    prof_acc[0] = clock64() - prof_begin;                                                                 \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && arb_attn_prof_buffer)                    \
+      for (int prof_i = 0; prof_i < 8; ++prof_i) arb_attn_prof_buffer[(role) * 8 + prof_i] = prof_acc[prof_i]; \
+  } while (0)
+#else
+#define PROF_DECL() do { } while (0)
+#define PROF_TIC() do { } while (0)
+#define PROF_TOC(i) do { } while (0)
+#define PROF_DUMP(role) do { } while (0)
+#endif
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -3,8 +3,12 @@
 // What bounds these kernels on sm_100a is not the tensor pipe's arithmetic rate but (a) the cost of
 // issuing tcgen05.mma instructions, about 50-65 clk each whatever their size, so every MMA here is
 // M=128, N=128, K=16 (64 clk of tensor work), never N=64; and (b) the ex2 unit, 1024 clk per
-// 128 x 128 tile, so the exponentials must overlap the MMAs.  Ten warps: TMA producer, MMA issuer,
-// eight softmax warps (two per TMEM lane quarter, each owning 64 of the 128 columns of a tile).
+// 128 x 128 tile, so the exponentials must overlap the MMAs.  Ten warps: TMA producer, MMA issuer, eight
+// softmax warps (two per TMEM lane quarter, each owning 64 of the 128 columns of a tile).  Measured dead
+// ends, for the record: (1) two issuing threads: the tensor pipe interleaves their instructions and the
+// tile the softmax warps wait for finishes later than when one thread queues the work in the order it is
+// needed; (2) evaluating part of the exponentials with a polynomial on the FMA pipe: the extra
+// instructions take issue slots from the issuing thread, which shares a scheduler with two softmax warps.
 //
 // The softmax of a tile is split in two phases so that the score buffer is released early:
 //   phase A  needs only S: p = exp2(S*c - lse) is kept in fp32 registers (64 per thread);
@@ -12,7 +16,7 @@
 //            of the next MMA.
 //
 //   attn_bwd_dq_wide_k (query-stationary): per key tile  S = Q K^T, dP = dO V^T, dQ += dS K.
-//     MMA order   S(t+1) after phase A(t);  dP(t+1), dQ(t) after phase B(t).
+//     MMA order   S(t+1) after phase A(t) has loaded S(t);  dP(t+1), dQ(t) after phase B(t).
 //     TMEM        S 128 | dP 128 | dQ 128 | dS[2] x 64 columns.
 //   attn_bwd_dkv_wide_k (key-stationary, transposed scores): S^T = K Q^T, dP^T = V dO^T,
 //     dV += P^T dO, dK += dS^T Q.
@@ -59,6 +63,24 @@ __device__ __forceinline__ void mma_tile_ts(uint32_t d_tmem, uint32_t a_lo, uint
               (accumulate || k > 0) ? 1u : 0u);
 }
 
+// exp2 of 64 scores of one row/lane; the offsets are one per-row value or 64 per-column values
+template <bool ROW_STAT>
+__device__ __forceinline__ void exp2_64(const uint32_t (&s0)[32], const uint32_t (&s1)[32], float c, float row_off,
+                                        const float4* col_off, float (&pr)[64]) {
+#pragma unroll
+  for (int g = 0; g < 16; ++g) {
+    float4 o = make_float4(row_off, row_off, row_off, row_off);
+    if (!ROW_STAT) o = col_off[g];
+    const float off[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = g * 4 + u;
+      const float x = __uint_as_float(j < 32 ? s0[j] : s1[j - 32]) * c - off[u];
+      pr[j] = fast_exp2(x);
+    }
+  }
+}
+
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&a)[32], uint32_t (&b)[32]) {
   tmem_ld32(taddr, a);
   tmem_ld32(taddr + 32, b);
@@ -85,7 +107,7 @@ attn_bwd_dq_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* dp_full = bars + 8;       // [2] dP(t) complete; also frees V(t)'s slot
   uint64_t* ds_full = bars + 10;      // [2] phase B(t) wrote dS(t) and has read dP(t) (8 arrivals)
   uint64_t* dq_done = bars + 12;      // [6] dQ(t) MMAs complete: frees K(t)'s slot and dS buffer t&1
-  uint64_t* done = bars + 18;
+  uint64_t* done = bars + 18;         // all dQ MMAs complete
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -123,15 +145,15 @@ attn_bwd_dq_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tma_load_4d(smem + WideSmem::RES0 + 16384, &tmQ, q_full, 64, h, m0, b);
       tma_load_4d(smem + WideSmem::RES1, &tmDO, q_full, 0, h, m0, b);
       tma_load_4d(smem + WideSmem::RES1 + 16384, &tmDO, q_full, 64, h, m0, b);
+      // A TMA load takes about 1 us under load, so every tile is requested at least a tile period before its
+      // first use: K(t) when dQ(t-3) has released its slot, V(t) when dP(t-2) has.
       for (int t = 0; t < n_tiles; ++t) {
         const int n0 = (j_lo + t) * 128;
-        // K(t) reuses the slot of K(t-3): wait for dQ(t-3)
         if (t >= 3 && !mbar_wait(&dq_done[(t - 3) % 6], uint32_t((t - 3) / 6) & 1u, abort_flag)) break;
         uint8_t* ks = smem + WideSmem::RING3 + (t % 3) * 32768;
         mbar_expect_tx(&k_full[t % 3], 32768);
         tma_load_4d(ks, &tmK, &k_full[t % 3], 0, h, n0, b);
         tma_load_4d(ks + 16384, &tmK, &k_full[t % 3], 64, h, n0, b);
-        // V(t) reuses the slot of V(t-2): wait for dP(t-2)
         if (t >= 2 && !mbar_wait(&dp_full[t & 1], uint32_t((t - 2) >> 1) & 1u, abort_flag)) break;
         uint8_t* vs = smem + WideSmem::RING2 + (t & 1) * 32768;
         mbar_expect_tx(&v_full[t & 1], 32768);
@@ -193,11 +215,14 @@ attn_bwd_dq_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float lse2 = (row < p.T) ? p.lse[stat] * LOG2E : INFINITY;
     const float dlt = (row < p.T) ? p.delta[stat] : 0.f;
     bool ok = true;
+    PROF_DECL();
     for (int t = 0; t < n_tiles && ok; ++t) {
       const int n0 = (j_lo + t) * 128 + hf * 64;   // first key of this thread's 64 columns
       float pr[64];
       // ---- phase A ----
+      PROF_TIC();
       if (!mbar_wait(s_full, uint32_t(t & 1), abort_flag)) { ok = false; break; }
+      PROF_TOC(1);
       tc_fence_after();
       {
         uint32_t s0[32], s1[32];
@@ -207,11 +232,7 @@ attn_bwd_dq_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (lane == 0) mbar_arrive(a_done);
         const bool need_mask = (n0 + 63 > m0) || (p.window < p.T && n0 < m0 + 127 - p.window) || (n0 + 63 >= p.T) ||
                                (m0 + 127 >= p.T);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          pr[j] = fast_exp2(__uint_as_float(s0[j]) * c - lse2);
-          pr[32 + j] = fast_exp2(__uint_as_float(s1[j]) * c - lse2);
-        }
+        exp2_64<true>(s0, s1, c, lse2, nullptr, pr);
         if (need_mask) {
 #pragma unroll
           for (int j = 0; j < 64; ++j) {
@@ -222,7 +243,9 @@ attn_bwd_dq_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       // ---- phase B ----
+      PROF_TOC(2);
       if (!mbar_wait(&dp_full[t & 1], uint32_t(t >> 1) & 1u, abort_flag)) { ok = false; break; }
+      PROF_TOC(3);
       tc_fence_after();
       uint32_t pk[32];
       {
@@ -236,14 +259,18 @@ attn_bwd_dq_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       // dS buffer t&1 was last read by the dQ MMAs of tile t-2
+      PROF_TOC(4);
       if (t >= 2 && !mbar_wait(&dq_done[(t - 2) % 6], uint32_t((t - 2) / 6) & 1u, abort_flag)) { ok = false; break; }
+      PROF_TOC(5);
       tc_fence_after();
       tmem_st32(TM_DS + lane_addr + uint32_t((t & 1) * 64 + hf * 32), pk);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_full[t & 1]);
+      PROF_TOC(6);
     }
+    if (lane == 0 && (sw == 0 || sw == 5)) PROF_DUMP(sw == 0 ? 2 : 3);
     if (ok && mbar_wait(done, 0, abort_flag)) {
       tc_fence_after();
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + ((long long)b * p.T + row) * p.ldo + h * HD + hf * 64;
@@ -408,27 +435,27 @@ attn_bwd_dkv_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     };
     (tid < 128 ? stat_lse : stat_dl)[tid & 127] = load_stat(0);
     bool ok = true;
+    PROF_DECL();
     for (int t = 0; t < n_tiles; ++t) {
       const int q0 = (i_lo + t) * 128 + hf * 64;   // first query of this thread's 64 columns
       const int buf = t & 1;
+      PROF_TIC();
       named_bar_sync(1, 256);                    // statistics of tile t are visible to all softmax warps
       const float next_stat = load_stat(t + 1);  // in flight while this tile is processed
-      const float* cl = stat_lse + buf * 128 + hf * 64;
-      const float* cd = stat_dl + buf * 128 + hf * 64;
+      const float4* cl = reinterpret_cast<const float4*>(stat_lse + buf * 128 + hf * 64);
+      const float4* cd = reinterpret_cast<const float4*>(stat_dl + buf * 128 + hf * 64);
       float pr[64];
       // ---- phase A: P^T = exp2(S^T * c - lse2[query]) ----
+      PROF_TOC(1);
       if (ok && !mbar_wait(s_full, uint32_t(t & 1), abort_flag)) ok = false;
+      PROF_TOC(2);
       if (ok) {
         tc_fence_after();
         uint32_t s0[32], s1[32];
         tmem_ld64(TM_S + lane_addr + uint32_t(hf * 64), s0, s1);
         const bool need_mask = (q0 < n0 + 127) || (p.window < p.T && q0 + 63 > n0 + p.window) || (q0 + 63 >= p.T) ||
                                (n0 + 127 >= p.T);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          pr[j] = fast_exp2(__uint_as_float(s0[j]) * c - cl[j]);
-          pr[32 + j] = fast_exp2(__uint_as_float(s1[j]) * c - cl[32 + j]);
-        }
+        exp2_64<false>(s0, s1, c, 0.f, cl, pr);
         if (need_mask) {
 #pragma unroll
           for (int j = 0; j < 64; ++j) {
@@ -447,18 +474,24 @@ attn_bwd_dkv_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (lane == 0) mbar_arrive(p_full);
       }
       // ---- phase B: dS^T = P^T * (dP^T - delta[query]) ----
+      PROF_TOC(3);
       if (ok && !mbar_wait(dp_full, uint32_t(t & 1), abort_flag)) ok = false;
+      PROF_TOC(4);
       if (ok) {
         tc_fence_after();
         uint32_t d0[32], d1[32];
         tmem_ld64(TM_DP + lane_addr + uint32_t(hf * 64), d0, d1);
         uint32_t pk[32];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          pk[j] = pack_bf16(pr[2 * j] * (__uint_as_float(d0[2 * j]) - cd[2 * j]),
-                            pr[2 * j + 1] * (__uint_as_float(d0[2 * j + 1]) - cd[2 * j + 1]));
-          pk[16 + j] = pack_bf16(pr[32 + 2 * j] * (__uint_as_float(d1[2 * j]) - cd[32 + 2 * j]),
-                                 pr[32 + 2 * j + 1] * (__uint_as_float(d1[2 * j + 1]) - cd[32 + 2 * j + 1]));
+        for (int g = 0; g < 8; ++g) {
+          const float4 e0 = cd[g], e1 = cd[8 + g];
+          pk[2 * g] = pack_bf16(pr[4 * g] * (__uint_as_float(d0[4 * g]) - e0.x), pr[4 * g + 1] * (__uint_as_float(d0[4 * g + 1]) - e0.y));
+          pk[2 * g + 1] = pack_bf16(pr[4 * g + 2] * (__uint_as_float(d0[4 * g + 2]) - e0.z),
+                                    pr[4 * g + 3] * (__uint_as_float(d0[4 * g + 3]) - e0.w));
+          pk[16 + 2 * g] = pack_bf16(pr[32 + 4 * g] * (__uint_as_float(d1[4 * g]) - e1.x),
+                                     pr[32 + 4 * g + 1] * (__uint_as_float(d1[4 * g + 1]) - e1.y));
+          pk[16 + 2 * g + 1] = pack_bf16(pr[32 + 4 * g + 2] * (__uint_as_float(d1[4 * g + 2]) - e1.z),
+                                         pr[32 + 4 * g + 3] * (__uint_as_float(d1[4 * g + 3]) - e1.w));
         }
         tmem_st32(TM_DP + lane_addr + uint32_t(hf * 64), pk);
         tmem_wait_st();
@@ -466,8 +499,10 @@ attn_bwd_dkv_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         __syncwarp();
         if (lane == 0) mbar_arrive(ds_full);
       }
+      PROF_TOC(5);
       (tid < 128 ? stat_lse : stat_dl)[((t + 1) & 1) * 128 + (tid & 127)] = next_stat;
     }
+    if (lane == 0 && (sw == 0 || sw == 5)) PROF_DUMP(sw == 0 ? 6 : 7);
     if (ok && mbar_wait(done, 0, abort_flag)) {
       tc_fence_after();
       __nv_bfloat16* dkrow = reinterpret_cast<__nv_bfloat16*>(p.dk) + ((long long)b * p.T + key) * p.lddk + h * HD + hf * 64;
@@ -501,6 +536,7 @@ attn_bwd_dkv_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, ERR_ATTN_TIMEOUT);
   if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
+
 
 // Launches both kernels of the wide backward; `a` carries sizes, lse, delta and the error flag.
 int attn_wide_bwd_launch(const void* q, const void* k, const void* v, const void* d_o, void* dq, void* dk, void* dv,
