@@ -180,28 +180,36 @@ attn_bwd_dq_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mma_tile_kk(TM_DP, sdo, sv0, idesc_kk);
         tc_commit(&dp_full[0]);
       }
+      PROF_DECL();
       for (int t = 0; t < n_tiles && ok; ++t) {
         const bool more = t + 1 < n_tiles;
+        PROF_TIC();
         if (more) {
           if (!mbar_wait(a_done, uint32_t(t & 1), abort_flag)) { ok = false; break; }
           if (!mbar_wait(&k_full[(t + 1) % 3], uint32_t((t + 1) / 3) & 1u, abort_flag)) { ok = false; break; }
+          PROF_TOC(1);
           tc_fence_after();
           mma_tile_kk(TM_S, sq, sk0 + uint32_t((t + 1) % 3) * 32768u, idesc_kk);
           tc_commit(s_full);
+          PROF_TOC(2);
         }
         if (!mbar_wait(&ds_full[t & 1], uint32_t(t >> 1) & 1u, abort_flag)) { ok = false; break; }
         if (more) {
           if (!mbar_wait(&v_full[(t + 1) & 1], uint32_t((t + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+          PROF_TOC(3);
           tc_fence_after();
           mma_tile_kk(TM_DP, sdo, sv0 + uint32_t((t + 1) & 1) * 32768u, idesc_kk);
           tc_commit(&dp_full[(t + 1) & 1]);
+          PROF_TOC(4);
         }
         tc_fence_after();
         const uint32_t ds = TM_DS + uint32_t(t & 1) * 64u;
         mma_tile_ts(TM_DQ, ds, ds + 32, sk0 + uint32_t(t % 3) * 32768u, idesc_mn, t > 0);
         tc_commit(&dq_done[t % 6]);
+        PROF_TOC(5);
       }
       if (ok) tc_commit(done);
+      PROF_DUMP(0);
     }
   } else {
     const int sw = warp - 2;             // 0..7
@@ -391,11 +399,14 @@ attn_bwd_dkv_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         mma_tile_kk(TM_DP, sv, sdo0, idesc_kk);
         tc_commit(dp_full);
       }
+      PROF_DECL();
       for (int t = 0; t < n_tiles && ok; ++t) {
         const bool more = t + 1 < n_tiles;
         const uint32_t sq = sq0 + uint32_t(t % 3) * 32768u, sdo = sdo0 + uint32_t(t & 1) * 32768u;
+        PROF_TIC();
         // dV(t) reads P^T(t) from the S^T tile; S^T(t+1) is issued after it and may then overwrite it
         if (!mbar_wait(p_full, uint32_t(t & 1), abort_flag)) { ok = false; break; }
+        PROF_TOC(1);
         tc_fence_after();
         mma_tile_ts(TM_DV, TM_S, TM_S + 64, sdo, idesc_mn, t > 0);
         tc_commit(&do_empty[t & 1]);
@@ -405,7 +416,9 @@ attn_bwd_dkv_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mma_tile_kk(TM_S, sk, sq0 + uint32_t((t + 1) % 3) * 32768u, idesc_kk);
           tc_commit(s_full);
         }
+        PROF_TOC(2);
         if (!mbar_wait(ds_full, uint32_t(t & 1), abort_flag)) { ok = false; break; }
+        PROF_TOC(3);
         tc_fence_after();
         mma_tile_ts(TM_DK, TM_DP, TM_DP + 64, sq, idesc_mn, t > 0);
         tc_commit(&q_empty[t % 3]);
@@ -415,8 +428,10 @@ attn_bwd_dkv_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mma_tile_kk(TM_DP, sv, sdo0 + uint32_t((t + 1) & 1) * 32768u, idesc_kk);
           tc_commit(dp_full);
         }
+        PROF_TOC(4);
       }
       if (ok) tc_commit(done);
+      PROF_DUMP(4);
     }
   } else {
     const int sw = warp - 2;
@@ -564,3 +579,17 @@ int attn_wide_bwd_launch(const void* q, const void* k, const void* v, const void
 }
 
 }  // namespace arb
+
+#ifdef ARB_ATTN_PROF
+// Entry point of the profiling build (bench/attn_roles.py): runs the wide backward once and leaves the
+// per-role cycle counters of CTA (0,0,0) in `prof` (device, 64 x int64).
+extern "C" int arb_attn_prof_wide_bwd(const void* q, const void* k, const void* v, const void* d_o, void* dq, void* dk,
+                                      void* dv, const float* lse, const float* delta, int B, int T, int H, long long ld,
+                                      long long ldo, int window, float scale, int* err, long long* prof) {
+  cudaMemcpyToSymbol(arb::arb_attn_prof_buffer, &prof, sizeof(prof));
+  arb::AttnArgs a{};
+  a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
+  a.lse = const_cast<float*>(lse); a.delta = delta; a.err = err;
+  return arb::attn_wide_bwd_launch(q, k, v, d_o, dq, dk, dv, ld, ld, ld, ldo, ld, ld, ld, a, 0);
+}
+#endif
