@@ -95,6 +95,47 @@ class MLPFn(torch.autograd.Function):
         return dxn, dwfc, dwdn, g
 
 
+class TPRowLinearFn(torch.autograd.Function):
+    """Row-parallel linear with sequence-sharded output: y_shard = reduce-scatter(a @ w^T), the transfer
+    riding on the GEMM epilogue (FusedTPContext.gemm_rs).  Backward: all-gather(g) -> GEMM."""
+
+    @staticmethod
+    def forward(ctx, a, w, tp):
+        ctx.tp = tp
+        ctx.save_for_backward(a, w)
+        return tp.gemm_rs(a, w)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, w = ctx.saved_tensors
+        da, g_full = ctx.tp.ag_gemm(g.contiguous(), w, trans_b=False)
+        dw = _acc_weight_grad(w, g_full, a)
+        return da, dw, None
+
+
+class TPMLPFn(torch.autograd.Function):
+    """Tensor-parallel MLP on a sequence shard: out = resid + RS(relu(AG(xn) @ wfc^T)^2 @ wdn^T)."""
+
+    @staticmethod
+    def forward(ctx, xn, wfc, wdn, resid, tp):
+        ctx.tp = tp
+        act, xn_full = tp.ag_gemm(xn, wfc, epi=K.EPI_RELU2)
+        y = tp.gemm_rs(act, wdn)
+        ctx.save_for_backward(xn_full, wfc, wdn, act)
+        return K.residual_add(resid, y)
+
+    @staticmethod
+    def backward(ctx, g):
+        xn_full, wfc, wdn, act = ctx.saved_tensors
+        tp = ctx.tp
+        g = g.contiguous()
+        dh, g_full = tp.ag_gemm(g, wdn, trans_b=False, epi=K.EPI_RELU2_BWD, aux=act)
+        dwdn = _acc_weight_grad(wdn, g_full, act)
+        dwfc = _acc_weight_grad(wfc, dh, xn_full)
+        dxn = tp.gemm_rs(dh, wfc, trans_b=False)
+        return dxn, dwfc, dwdn, g, None
+
+
 class RMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, eps):
@@ -228,9 +269,14 @@ class AttnPreFn(torch.autograd.Function):
     """packed qkv = post(xn @ wqkv^T): RoPE + QK-norm on q, k; value embedding on v."""
 
     @staticmethod
-    def forward(ctx, xn, wqkv, ids, ve_w, gate_w, cos, sin, T, H, gate_ch, eps):
+    def forward(ctx, xn, wqkv, ids, ve_w, gate_w, cos, sin, T, H, gate_ch, eps, tp=None):
+        # tp (a FusedTPContext): xn is this rank's sequence shard; the gather is overlapped with the GEMM
+        ctx.tp = tp
+        if tp is not None:
+            qkv, xn = tp.ag_gemm(xn, wqkv)
+        else:
+            qkv = K.gemm(xn, wqkv)
         N, D = xn.shape
-        qkv = K.gemm(xn, wqkv)
         rstd = torch.empty(N, 2 * H, dtype=torch.float32, device=xn.device)
         gate = torch.empty(N, H, dtype=torch.float32, device=xn.device) if ve_w is not None else None
         rc = K.lib().arb_qkv_post_fwd(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), rstd.data_ptr(),
@@ -268,7 +314,13 @@ class AttnPreFn(torch.autograd.Function):
                                       dgl.data_ptr() if has_ve else 0, N, T, H, D, gate_ch, K._stream())
         K._check(rc, "qkv_post_bwd")
         dw = _acc_weight_grad(wqkv, d_qkv, xn)
-        dxn = K.gemm(d_qkv, wqkv, trans_b=False)
+        tp = ctx.tp
+        if tp is not None:
+            dxn = tp.gemm_rs(d_qkv, wqkv, trans_b=False)
+            if has_ve:   # the gate's contribution to d(xn) is a partial sum over the head shards as well
+                d_xn_gate = tp.reduce_scatter_rows(d_xn_gate)
+        else:
+            dxn = K.gemm(d_qkv, wqkv, trans_b=False)
         g_ve = g_gate = None
         if has_ve:
             K.add_cols_(dxn, d_xn_gate)
@@ -281,7 +333,7 @@ class AttnPreFn(torch.autograd.Function):
                 g_ve = tmp.to(ve_w.dtype)
             if _main_grad(gate_w) is None:
                 g_gate = dgw.to(gate_w.dtype)
-        return dxn, dw, None, g_ve, g_gate, None, None, None, None, None, None
+        return dxn, dw, None, g_ve, g_gate, None, None, None, None, None, None, None
 
 
 class AttentionFn(torch.autograd.Function):
@@ -513,12 +565,15 @@ class Sm100Backend(OracleBackend):
         return ResidualAddFn.apply(x, y)
 
     def attention_block(self, xn, blk, ids_flat, B, T, cfg, cos, sin, window):
-        if self._tp() is not None:
-            xn = self._tp().all_gather(xn)
+        tp = self._tp()
+        fused_tp = tp if (tp is not None and tp.mode == "fused") else None
+        if tp is not None and fused_tp is None:
+            xn = tp.all_gather(xn)
         H = blk.wqkv.shape[0] // (3 * cfg.head_dim)
         if cfg.head_dim != 128:
             raise ValueError("the sm100 kernels support head_dim = 128 only")
-        qkv = AttnPreFn.apply(xn, blk.wqkv, ids_flat, blk.ve, blk.ve_gate, cos, sin, T, H, cfg.ve_gate_ch, self.eps)
+        qkv = AttnPreFn.apply(xn, blk.wqkv, ids_flat, blk.ve, blk.ve_gate, cos, sin, T, H, cfg.ve_gate_ch, self.eps,
+                              fused_tp)
         fn = AttentionFn if self.attn == "own" else LibraryAttentionFn
         return fn.apply(qkv, B, T, H, window)
 
@@ -526,12 +581,16 @@ class Sm100Backend(OracleBackend):
         tp = self._tp()
         if tp is None:
             return LinearAddNormFn.apply(a, w, x, self.eps)
+        if tp.mode == "fused":
+            return AddNormFn.apply(x, TPRowLinearFn.apply(a, w, tp), self.eps)
         return AddNormFn.apply(x, tp.reduce_scatter(LinearFn.apply(a, w)), self.eps)
 
     def mlp_add(self, xn, wfc, wdn, x):
         tp = self._tp()
         if tp is None:
             return MLPFn.apply(xn, wfc, wdn, x)
+        if tp.mode == "fused":
+            return TPMLPFn.apply(xn, wfc, wdn, x, tp)
         act = LinearRelu2Fn.apply(tp.all_gather(xn), wfc)
         return ResidualAddFn.apply(x, tp.reduce_scatter(LinearFn.apply(act, wdn)))
 

@@ -43,6 +43,11 @@ class SymmBuffer:
     def peer_ptrs(self) -> List[int]:
         return [int(p) for p in self.handle.buffer_ptrs]
 
+    def peer_tensor(self, rank: int, shape, dtype: Optional[torch.dtype] = None, offset: int = 0) -> torch.Tensor:
+        """A tensor that aliases `rank`'s buffer (its own memory, mapped here over NVLink), starting
+        `offset` elements into it.  Kernels of this package may write it (peer stores) or read it."""
+        return self.handle.get_buffer(int(rank), tuple(int(x) for x in shape), dtype or self.tensor.dtype, int(offset))
+
     @property
     def multicast_ptr(self) -> int:
         if os.environ.get("ARB_DISABLE_MULTIMEM", "0") == "1":

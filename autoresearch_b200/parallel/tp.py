@@ -12,10 +12,14 @@ Embedding, final norm, LM head and the loss run on the local token shard with re
 weights.  Two communication arms:
 
 * ``library`` – torch.distributed all_gather / reduce_scatter (NCCL or gloo): the baseline.
-* ``fused``   – peer memory: the all-gather is a pull kernel that runs on a side stream while
-  the GEMM already works on the local rows; the reduce-scatter has the GEMM write its partial
-  product into a symmetric staging buffer and ONE kernel adds the local rows, the peers' rows
-  (NVLink loads) and the residual, so no reduced tensor is ever written separately.
+* ``fused``   – peer memory, tied into the tcgen05 GEMMs (``FusedTPContext.gemm_rs`` /
+  ``ag_gemm``): GEMM -> reduce-scatter runs the GEMM once per destination rank with that rank's
+  staging slab as its output, so every finished 256 x 256 tile leaves the epilogue as TMA stores
+  over NVLink while the tensor cores work on the next tile, and a local kernel sums the slabs;
+  all-gather -> GEMM pulls the peers' row blocks (NVLink loads) on a side stream while the GEMM
+  already multiplies the local rows, and multiplies the pulled rows when they have arrived.  The
+  pulled rows are kept in local memory because each of them is read by every column tile of the
+  GEMM; reading them from the peer inside the GEMM would cross NVLink once per column tile.
 """
 from __future__ import annotations
 
@@ -108,17 +112,19 @@ class FusedTPContext(TPContext):
         self.device = torch.device(device)
         self.D = d_model
         self.max_rows = max_rows
-        # shard staging (all-gather source), partial-product staging (reduce-scatter source)
-        self.ag = SymmBuffer(max_rows // size * d_model, torch.bfloat16, self.device, group)
-        self.rs = SymmBuffer(max_rows * d_model, torch.bfloat16, self.device, group)
+        self.n_max = max_rows // size
+        # Both staging areas are double buffered: a rank writes half k%2 of a peer during operation k and the
+        # peer reads it after barrier k; the same half is written again only in operation k+2, i.e. after the
+        # writer has passed barrier k+1, which the reader enters only after its reads of operation k.
+        self.ag = SymmBuffer(2 * self.n_max * d_model, torch.bfloat16, self.device, group)       # [2][n, D] my shard
+        self.rs = SymmBuffer(2 * max_rows * d_model, torch.bfloat16, self.device, group)         # [2][src][n, D]
         self.flags = SymmBuffer(64, torch.int32, self.device, group)
         for b in (self.ag, self.rs, self.flags):
             b.rendezvous()
         dist.barrier(group=group)
         self._flag_ptrs = (C.c_void_p * size)(*self.flags.peer_ptrs)
-        self._ag_ptrs = (C.c_void_p * size)(*self.ag.peer_ptrs)
-        self._rs_ptrs = (C.c_void_p * (size + 1))(*(self.rs.peer_ptrs + [rank]))
         self.epoch = 0
+        self.n_ag = self.n_rs = 0
         self.side = torch.cuda.Stream(device=self.device)
 
     def barrier(self):
@@ -126,41 +132,114 @@ class FusedTPContext(TPContext):
         self.K._check(self.K.lib().arb_peer_barrier(self._flag_ptrs, self.size, self.rank, self.epoch,
                                                     self.K.err_flag(self.device).data_ptr(), self.K._stream()), "peer_barrier")
 
-    def all_gather_rows(self, x):
-        """Publish the local shard in symmetric memory, then pull every peer's shard (NVLink loads)."""
+    # ---- all-gather ---------------------------------------------------------------------------
+    def _publish_and_pull(self, x, out):
+        """Copy the local shard into this rank's staging half, then, on the side stream, pull every peer's shard
+        into its rows of `out`.  Returns the event that marks the arrival of the pulled rows."""
         K = self.K
         n, D = x.shape
-        if x.dtype != torch.bfloat16 or n * self.size > self.max_rows or D != self.D:
+        half = self.n_ag & 1
+        self.n_ag += 1
+        off = half * self.n_max * self.D
+        self.ag.tensor[off: off + n * D].view(n, D).copy_(x)
+        self.barrier()                                          # every shard of this operation is published
+        self.bytes += n * (self.size - 1) * D * 2
+        main = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ready)
+            # the pull kernel addresses the peers' staging halves as shards of one virtual [size*n, D] tensor
+            ptrs = (C.c_void_p * self.size)(*[p + off * 2 - r * n * D * 2 for r, p in enumerate(self.ag.peer_ptrs)])
+            K._check(K.lib().arb_all_gather_pull(ptrs, self.size, self.rank, out.data_ptr(), n * D * 2, self.side.cuda_stream),
+                     "tp_all_gather_pull")
+            arrived = torch.cuda.Event()
+            arrived.record(self.side)
+        out.record_stream(self.side)
+        return arrived
+
+    def all_gather_rows(self, x):
+        n, D = x.shape
+        if x.dtype != torch.bfloat16 or n > self.n_max or D != self.D:
             return super().all_gather_rows(x)
-        self.bytes += n * self.size * D * 2
-        stage = self.ag.tensor[: n * D].view(n, D)
-        stage.copy_(x)
         out = torch.empty(n * self.size, D, dtype=x.dtype, device=x.device)
-        self.barrier()                                          # every shard is published
+        arrived = self._publish_and_pull(x, out)
         out[self.rank * n:(self.rank + 1) * n].copy_(x)
-        # the pull kernel addresses peers' staging buffers as shards of one virtual [size*n, D] tensor
-        ptrs = (C.c_void_p * self.size)(*[p - r * n * D * 2 for r, p in enumerate(self.ag.peer_ptrs)])
-        K._check(K.lib().arb_all_gather_pull(ptrs, self.size, self.rank, out.data_ptr(), n * D * 2, K._stream()),
-                 "tp_all_gather_pull")
-        self.barrier()                                          # staging may be overwritten again
+        torch.cuda.current_stream(self.device).wait_event(arrived)
         return out
 
-    def reduce_scatter_rows(self, x):
-        """Partial products sit in symmetric memory; one kernel sums this rank's rows over all peers."""
+    def ag_gemm(self, x, w, trans_b=True, epi=None, aux=None):
+        """(all-gather of the row shards x) @ op(w): returns the product [size*n, cols] and the gathered
+        operand (the backward needs it).  The local rows are multiplied while the peers' rows travel."""
         K = self.K
-        N, D = x.shape
-        if x.dtype != torch.bfloat16 or N > self.max_rows or D != self.D:
-            return super().reduce_scatter_rows(x)
-        self.bytes += N * D * 2
-        n = N // self.size
-        stage = self.rs.tensor[: N * D].view(N, D)
-        stage.copy_(x)
-        self.barrier()
-        out32 = torch.empty(n, D, dtype=torch.float32, device=x.device)
-        K._check(K.lib().arb_reduce_scatter_peers(self._rs_ptrs, self.size, self.rank * n * D, n * D, 1, out32.data_ptr(), 1.0,
-                                                  K._stream()), "tp_reduce_scatter")
-        self.barrier()
+        n, D = x.shape
+        if x.dtype != torch.bfloat16 or n > self.n_max or D != self.D:
+            xf = super().all_gather_rows(x)
+            return K.gemm(xf, w, trans_b=trans_b, epi=epi if epi is not None else K.EPI_STORE_BF16, aux=aux), xf
+        epi = K.EPI_STORE_BF16 if epi is None else epi
+        N = n * self.size
+        cols = w.shape[0] if trans_b else w.shape[1]
+        xf = torch.empty(N, D, dtype=x.dtype, device=x.device)
+        y = torch.empty(N, cols, dtype=torch.bfloat16, device=x.device)
+        arrived = self._publish_and_pull(x, xf)
+        lo, hi = self.rank * n, (self.rank + 1) * n
+        xf[lo:hi].copy_(x)
+        K.gemm(x, w, trans_b=trans_b, out=y[lo:hi], epi=epi, aux=None if aux is None else aux[lo:hi])
+        torch.cuda.current_stream(self.device).wait_event(arrived)
+        for a, b in ((0, lo), (hi, N)):                         # the row blocks of the other ranks
+            if b > a:
+                K.gemm(xf[a:b], w, trans_b=trans_b, out=y[a:b], epi=epi, aux=None if aux is None else aux[a:b])
+        return y, xf
+
+    # ---- reduce-scatter -----------------------------------------------------------------------
+    def _reduce_slabs(self, half, n, D):
+        """Sum of the `size` source slabs of staging half `half` -> [n, D] bf16 (local reads only)."""
+        K = self.K
+        base = self.rs.tensor.data_ptr() + half * self.max_rows * self.D * 2
+        ptrs = (C.c_void_p * (self.size + 1))(*([base + s * self.n_max * self.D * 2 for s in range(self.size)] + [0]))
+        out32 = torch.empty(n, D, dtype=torch.float32, device=self.device)
+        K._check(K.lib().arb_reduce_scatter_peers(ptrs, self.size, 0, n * D, 1, out32.data_ptr(), 1.0, K._stream()),
+                 "tp_reduce_slabs")
         return out32.to(torch.bfloat16)
+
+    def _slab(self, dst_rank, half, n, D):
+        """Rank `dst_rank`'s staging slab for rows sent by this rank, as an [n, D] tensor."""
+        off = (half * self.max_rows + self.rank * self.n_max) * self.D
+        if dst_rank == self.rank:
+            return self.rs.tensor[off: off + n * D].view(n, D)
+        return self.rs.peer_tensor(dst_rank, (n, D), torch.bfloat16, off)
+
+    def reduce_scatter_rows(self, x):
+        N, D = x.shape
+        if x.dtype != torch.bfloat16 or N > self.max_rows or D != self.D or N % self.size:
+            return super().reduce_scatter_rows(x)
+        n = N // self.size
+        half = self.n_rs & 1
+        self.n_rs += 1
+        self.bytes += (N - n) * D * 2
+        for i in range(self.size):
+            r = (self.rank + 1 + i) % self.size
+            self._slab(r, half, n, D).copy_(x[r * n:(r + 1) * n])
+        self.barrier()
+        return self._reduce_slabs(half, n, D)
+
+    def gemm_rs(self, a, w, trans_b=True):
+        """Row block `rank` of sum over ranks of (a @ op(w)).  The GEMM runs once per destination rank with that
+        rank's staging slab as its output: the tiles leave the epilogue as TMA stores over NVLink."""
+        K = self.K
+        N = a.shape[0]
+        D = w.shape[0] if trans_b else w.shape[1]
+        if a.dtype != torch.bfloat16 or N > self.max_rows or D != self.D or N % self.size:
+            return super().reduce_scatter_rows(K.gemm(a, w, trans_b=trans_b))
+        n = N // self.size
+        half = self.n_rs & 1
+        self.n_rs += 1
+        self.bytes += (N - n) * D * 2
+        for i in range(self.size):                              # peers first: their tiles have the longer way
+            r = (self.rank + 1 + i) % self.size
+            K.gemm(a[r * n:(r + 1) * n], w, trans_b=trans_b, out=self._slab(r, half, n, D))
+        self.barrier()                                          # all slabs of this operation have arrived
+        return self._reduce_slabs(half, n, D)
 
 
 def shard_full_model_into(full: GPT, model: GPT, tp_rank: int, tp: int) -> None:

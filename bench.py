@@ -33,6 +33,8 @@ def main() -> int:
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--total-batch", type=int, default=524288)
     ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (world = tp x dp); dense models")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel group size (MoE models; 1 or the world size)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: marks the result invalid")
     args = ap.parse_args()
 
@@ -75,8 +77,16 @@ def main() -> int:
     tcfg = TrainConfig(device_batch_size=args.micro_batch, total_batch_size=args.total_batch,
                        max_steps=1000, cooldown_steps=300, synthetic_data=True, synthetic_kind="zipf",
                        impl=args.impl, schedule_cfg=sched, cooldown_trigger_file="",
-                       parallel=ParallelConfig(dp=world, comm=args.comm))
-    tr = Trainer(mcfg, tcfg, device=f"cuda:{local}", quiet=True)
+                       parallel=ParallelConfig(dp=world // max(1, args.tp), tp=args.tp, ep=args.ep, comm=args.comm))
+    if args.tp > 1:
+        from autoresearch_b200.parallel.tp import TPTrainer
+        tr = TPTrainer(mcfg, tcfg, tp=args.tp, device=f"cuda:{local}", quiet=True)
+        tr.comm = type("C", (), {"name": f"tp-{tr.backend.tp.mode}"})()
+        tr.h2d_bytes_per_step = tr.micro_batch * mcfg.seq_len * 8 * tr.accum
+        from autoresearch_b200.utils.timing import measured_peak_flops
+        tr.peak_flops = measured_peak_flops()
+    else:
+        tr = Trainer(mcfg, tcfg, device=f"cuda:{local}", quiet=True)
     if args.attn and hasattr(tr.backend, "attn"):
         tr.backend.attn = args.attn
 
@@ -113,7 +123,7 @@ def main() -> int:
         t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_s = float(t[0].item()), float(t[1].item())
-    tokens_step = tr.micro_batch * mcfg.seq_len * tr.accum * world
+    tokens_step = tr.micro_batch * mcfg.seq_len * tr.accum * (world // max(1, args.tp))
     value = tokens_step * args.steps / (ms / 1e3)
     e2e = tokens_step * args.steps / e2e_s
     valid = args.layers is None and args.seq_len is None and args.model == "phase2" and args.total_batch == 524288
@@ -129,7 +139,8 @@ def main() -> int:
         "config": {"model": f"{mcfg.name} {mcfg.num_params()['total'] / 1e6:.1f}M D{mcfg.d_model} L{mcfg.n_layer} T{mcfg.seq_len}",
                    "global_batch": tokens_step, "seq_len": mcfg.seq_len,
                    "micro_batch_per_gpu": tr.micro_batch, "grad_accum": tr.accum,
-                   "parallelism": f"dp{world}", "comm": tr.comm.name,
+                   "parallelism": (f"tp{args.tp}xdp{world // args.tp}" if args.tp > 1 else
+                                   (f"dp{world} ep{args.ep}" if args.ep > 1 else f"dp{world}")), "comm": tr.comm.name,
                    "attention": getattr(tr.backend, "attn", "library"),
                    "l2": "inputs larger than L2 (per-step working set of tens of GB)",
                    "valid_headline_config": valid},
