@@ -59,18 +59,20 @@ class MoEFn(torch.autograd.Function):
         gates = torch.empty(N, top_k, dtype=torch.float32, device=dev)
         K._check(L.arb_moe_router_fwd(xn.data_ptr(), router_w.data_ptr(), probs.data_ptr(), idx.data_ptr(),
                                       gates.data_ptr(), N, D, E, top_k, s), "moe_router_fwd")
-        # slot bookkeeping on small integer tensors: position of each slot inside its expert, token order
-        flat = idx.view(-1).long()
-        onehot = F.one_hot(flat, E)
-        pos = (onehot.cumsum(0) - 1).gather(1, flat.view(-1, 1)).squeeze(1)
-        counts = onehot.sum(0)
+        # position of each slot inside its expert (token order) and the slots per expert
+        S = N * top_k
+        pos = torch.empty(S, dtype=torch.int32, device=dev)
+        counts = torch.empty(E, dtype=torch.int32, device=dev)
+        scratch = torch.empty(((S + 1023) // 1024) * E, dtype=torch.int32, device=dev)
+        K._check(L.arb_moe_slot_positions(idx.data_ptr(), S, E, scratch.data_ptr(), pos.data_ptr(), counts.data_ptr(), s),
+                 "moe_slot_positions")
         if ep is not None:
             cap = ep.cap_src
         elif capacity_factor > 0:
             cap = R.moe_capacity(N, E, top_k, capacity_factor)
         else:
             cap = (int(counts.max().item()) + 7) // 8 * 8     # never drop: one host read per layer
-        row = torch.where(pos < cap, pos, torch.full_like(pos, -1)).to(torch.int32).contiguous()
+        row = torch.where(pos < cap, pos, torch.full_like(pos, -1)).contiguous()
         f = counts.float() / float(N * top_k)
         aux = aux_coeff * E * (f * probs.mean(0)).sum()
         if ep is None:

@@ -155,6 +155,9 @@ int arb_moe_router_bwd(const float* probs, const int* idx, const float* gates, c
                        cudaStream_t s);
 // expert_bufs: HOST array of E device pointers (local or NVLink peer mappings) to [rows, D] bf16
 // buffers; row [N,K] = destination row of each slot inside its expert's buffer, -1 = dropped.
+// pos[s] = rank of slot s among the slots of its expert (token-major order), counts[e] = slots per expert;
+// scratch holds ceil(S / 1024) * E ints
+int arb_moe_slot_positions(const int* idx, long long S, int E, int* scratch, int* pos, int* counts, cudaStream_t s);
 int arb_moe_dispatch(const void* x, void* const* expert_bufs, const int* idx, const int* row, long long N, int K,
                      int D, int E, cudaStream_t s);
 // out[t] = resid[t] + sum_k gates[t,k] * buf[idx][row]  (resid / gates may be null: 0 / 1)

@@ -174,6 +174,61 @@ static int fill_ptrs(ExpertPtrs& ep, void* const* host_ptrs, int E) {
 using namespace arb;
 typedef __nv_bfloat16 bf16;
 
+
+// ------------------------------------------------------------------------------------------------
+// Slot positions: pos[s] = number of earlier slots (token-major order) routed to the same expert,
+// i.e. the row a slot takes in its expert's buffer; counts[e] = slots per expert.  Deterministic
+// two-pass prefix sum over chunks of 1024 slots (the reference uses atomics and a host-synchronised
+// offset table, brain/kernels/moe_dispatch.cu:154-230).
+// ------------------------------------------------------------------------------------------------
+constexpr int SLOT_CHUNK = 1024;
+
+__global__ void __launch_bounds__(SLOT_CHUNK) moe_slot_count_k(const int* __restrict__ idx, long long S, int E, int* __restrict__ chunk_counts) {
+  __shared__ int cnt[MOE_MAX_E];
+  if (threadIdx.x < E) cnt[threadIdx.x] = 0;
+  __syncthreads();
+  const long long s = (long long)blockIdx.x * SLOT_CHUNK + threadIdx.x;
+  const int e = (s < S) ? idx[s] : -1;
+  for (int x = 0; x < E; ++x) {
+    const unsigned m = __ballot_sync(0xffffffffu, e == x);
+    if ((threadIdx.x & 31) == 0 && m) atomicAdd(&cnt[x], __popc(m));   // integer adds: order does not matter
+  }
+  __syncthreads();
+  if (threadIdx.x < E) chunk_counts[(long long)blockIdx.x * E + threadIdx.x] = cnt[threadIdx.x];
+}
+
+__global__ void __launch_bounds__(SLOT_CHUNK) moe_slot_pos_k(const int* __restrict__ idx, long long S, int E,
+                                                           const int* __restrict__ chunk_counts, int n_chunks,
+                                                           int* __restrict__ pos, int* __restrict__ counts) {
+  __shared__ int base[MOE_MAX_E];               // slots of expert e in earlier chunks
+  __shared__ int warp_cnt[32][MOE_MAX_E + 1];   // per warp, per expert, inside this chunk
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x < E) {
+    int b = 0, tot = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+      const int v = chunk_counts[(long long)c * E + threadIdx.x];
+      if (c < int(blockIdx.x)) b += v;
+      tot += v;
+    }
+    base[threadIdx.x] = b;
+    if (blockIdx.x == 0) counts[threadIdx.x] = tot;
+  }
+  const long long s = (long long)blockIdx.x * SLOT_CHUNK + threadIdx.x;
+  const int e = (s < S) ? idx[s] : -1;
+  int in_warp = 0;
+  for (int x = 0; x < E; ++x) {
+    const unsigned m = __ballot_sync(0xffffffffu, e == x);
+    if (e == x) in_warp = __popc(m & ((1u << lane) - 1u));
+    if (lane == 0) warp_cnt[warp][x] = __popc(m);
+  }
+  __syncthreads();
+  if (e >= 0) {
+    int before = base[e];
+    for (int w = 0; w < warp; ++w) before += warp_cnt[w][e];
+    pos[s] = before + in_warp;
+  }
+}
+
 extern "C" {
 
 int arb_moe_router_fwd(const void* xn, const void* wr, float* probs, int* idx, float* gates, long long N, int D, int E, int K,
@@ -227,6 +282,16 @@ int arb_moe_combine_bwd(const void* d_out, void* const* y_bufs, const void* y_ro
   if (rc || N <= 0 || (D & 7)) return rc ? rc : -3;
   moe_combine_bwd_k<<<unsigned((N * K + 7) / 8), 256, 0, s>>>((const bf16*)d_out, ey, (const bf16*)y_rows, ed, idx, row, gates, d_gates,
                                                              N * K, K, D);
+  return int(cudaGetLastError());
+}
+
+// pos[S], counts[E]; scratch: int[ceil(S/1024) * E]
+int arb_moe_slot_positions(const int* idx, long long S, int E, int* scratch, int* pos, int* counts, cudaStream_t s) {
+  if (S <= 0 || E < 1 || E > MOE_MAX_E) return -3;
+  const long long chunks = (S + SLOT_CHUNK - 1) / SLOT_CHUNK;
+  if (chunks > 65535) return -3;
+  moe_slot_count_k<<<unsigned(chunks), SLOT_CHUNK, 0, s>>>(idx, S, E, scratch);
+  moe_slot_pos_k<<<unsigned(chunks), SLOT_CHUNK, 0, s>>>(idx, S, E, scratch, int(chunks), pos, counts);
   return int(cudaGetLastError());
 }
 

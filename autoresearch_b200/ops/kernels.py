@@ -71,6 +71,7 @@ def lib() -> C.CDLL:
         "arb_peer_barrier": [vp, i32, i32, i32, vp, vp],
         "arb_moe_router_fwd": [vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
         "arb_moe_router_bwd": [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, vp],
+        "arb_moe_slot_positions": [vp, i64, i32, vp, vp, vp, vp],
         "arb_moe_dispatch": [vp, vp, vp, vp, i64, i32, i32, i32, vp],
         "arb_moe_combine_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
         "arb_moe_combine_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],

@@ -100,3 +100,20 @@ def test_expert_parallel_two_gpus_matches_single_gpu():
     assert one["ep"] == 1 and two["ep"] == 2 and two["experts_local"] == 2
     for a, b in zip(one["losses"], two["losses"]):
         assert abs(a - b) < 0.05 * abs(a) + 0.02, (one, two)
+
+
+def test_slot_positions_match_token_order_prefix_sum():
+    """pos[s] counts the earlier slots of the same expert; counts[e] the slots per expert."""
+    from autoresearch_b200.ops import kernels as K
+    torch.manual_seed(5)
+    for S, E in ((1, 4), (1000, 8), (5000, 3), (70001, 32)):
+        idx = torch.randint(0, E, (S,), device="cuda", dtype=torch.int32)
+        pos = torch.empty(S, dtype=torch.int32, device="cuda")
+        counts = torch.empty(E, dtype=torch.int32, device="cuda")
+        scratch = torch.empty(((S + 1023) // 1024) * E, dtype=torch.int32, device="cuda")
+        K._check(K.lib().arb_moe_slot_positions(idx.data_ptr(), S, E, scratch.data_ptr(), pos.data_ptr(), counts.data_ptr(),
+                                                K._stream()), "moe_slot_positions")
+        onehot = torch.nn.functional.one_hot(idx.long(), E)
+        ref = (onehot.cumsum(0) - 1).gather(1, idx.long().view(-1, 1)).squeeze(1)
+        assert torch.equal(pos.long(), ref)
+        assert torch.equal(counts.long(), onehot.sum(0))
