@@ -21,7 +21,7 @@ _lock = threading.Lock()
 _lib = None
 
 LIB_SOURCES = ["rng.cpp", "data.cpp", "packer.cpp", "safetensors.cpp", "tokenizer.cpp",
-               "unicode_tables.cpp"]
+               "unicode_tables.cpp", "bpe_train.cpp"]
 
 
 def _hash() -> str:

@@ -74,6 +74,12 @@ int64_t ar_st_dim(void* r, int32_t i, int32_t d);
 const void* ar_st_data(void* r, int32_t i, int64_t* nbytes);
 void ar_st_close(void* r);
 
+// ---- BPE vocabulary training ---------------------------------------------------------------
+// words: concatenated bytes, word w = bytes[offsets[w] .. offsets[w+1]) seen counts[w] times.  Writes up to
+// vocab_size-256 merges as (left id, right id) pairs (merge i creates id 256+i) and returns their number.
+int32_t ar_bpe_train(const uint8_t* bytes, const int64_t* offsets, const int64_t* counts, int64_t n_words,
+                     int32_t vocab_size, int32_t* merges_out);
+
 // ---- BPE tokenizer -----------------------------------------------------------------------
 void* ar_tok_load_json(const char* path, char* err, int32_t errlen);
 void* ar_tok_load_tiktoken(const char* tiktoken_path, const char* config_path, char* err,

@@ -89,3 +89,53 @@ def test_tiktoken_format_roundtrip(tok, tmp_path):
 def test_token_bytes_table_matches_reference_artifact(tok):
     ref = json.loads((DATA / "token_bytes.json").read_text())
     assert tok.token_bytes() == ref
+
+
+def test_bpe_training_matches_a_plain_python_trainer(tmp_path):
+    """The native trainer against a direct restatement of byte-pair merging (most frequent pair,
+    ties to the smaller pair of ids), and the written tokenizer round-trips text."""
+    import json
+    from collections import Counter
+    from autoresearch_b200.tools import prepare
+
+    corpus = ("the quick brown fox jumps over the lazy dog. " * 20 + "pack my box with five dozen liquor jugs! " * 13 +
+              "sphinx of black quartz, judge my vow? 12345 67890 " * 7 + "naïve café déjà vu — ünïcödé tëxt. " * 5)
+    (tmp_path / "c.txt").write_text(corpus)
+    prepare.main(["--input", str(tmp_path / "c.txt"), "--out", str(tmp_path / "tok"), "--vocab-size", "300"])
+    d = json.loads((tmp_path / "tok" / "tokenizer.json").read_text())
+    assert len(d["mergeable_ranks"]) == 296 and len(d["special_tokens"]) == 4
+    from autoresearch_b200.data.tokenizer import Tokenizer
+    tok = Tokenizer(tmp_path / "tok")
+    assert tok.vocab_size == 300 and tok.bos_token_id == 296
+    assert tok.decode(tok.encode(corpus)) == corpus
+    assert len(tok.encode(corpus)) < len(corpus.encode()) // 2
+    tb = json.loads((tmp_path / "tok" / "token_bytes.json").read_text())
+    assert len(tb) == 300 and tb[-4:] == [0, 0, 0, 0]
+
+    # plain trainer on the same pre-tokenised words
+    words = Counter(tok.split(corpus))
+    seqs = {w: list(w.encode()) for w in words}
+    merges = []
+    for new_id in range(256, 296):
+        stat = Counter()
+        for w, ids in seqs.items():
+            for a, b in zip(ids, ids[1:]):
+                stat[(a, b)] += words[w]
+        if not stat:
+            break
+        best = min(stat, key=lambda p: (-stat[p], p))
+        merges.append(best)
+        for w, ids in seqs.items():
+            out, i = [], 0
+            while i < len(ids):
+                if i + 1 < len(ids) and (ids[i], ids[i + 1]) == best:
+                    out.append(new_id); i += 2
+                else:
+                    out.append(ids[i]); i += 1
+            seqs[w] = out
+    import base64
+    table = [bytes([i]) for i in range(256)]
+    for a, b in merges:
+        table.append(table[a] + table[b])
+    got = [base64.b64decode(k) for k, _ in d["mergeable_ranks"]]
+    assert got == table[:296]
