@@ -46,3 +46,28 @@ thread 'main' panicked at src/train.rs
     assert [s["step"] for s in p["steps"]] == [0, 995] and p["steps"][1]["tok_s"] == 52700
     assert p["evals"] == [{"step": 25, "val_bpb": 1.2345}, {"step": None, "val_bpb": 0.5392}]
     assert len(p["crashes"]) == 1 and "CRASH" in monitor.summary(p)
+
+
+def test_launch_lifecycle_and_plot(tmp_path):
+    """start runs a tiny CPU job to the end, salvages its checkpoint and writes the report; plot_live draws it."""
+    import json
+    import sys
+    from autoresearch_b200.tools import launch, plot_live
+    out = tmp_path / "run"
+    (out / "live_checkpoints" / "rank_0").mkdir(parents=True)     # synthetic-data runs write no checkpoint themselves
+    (out / "live_checkpoints" / "rank_0" / "model.safetensors").write_bytes(b"stand-in")
+    rc = launch.main(["start", "--out", str(out), "--gpus", "1", "--poll-seconds", "0.5", "--cost-per-gpu-hour", "2.0", "--",
+                      "MODEL=tiny", "SYNTHETIC=1", "MAX_STEPS=4", "COOLDOWN_STEPS=2", "BATCH_SIZE=2", "TOTAL_BATCH=256",
+                      "EVAL_EVERY=0"])
+    log = (out / "train.log").read_text()
+    assert rc == 0, log[-2000:]
+    rep = json.loads((out / "report.json").read_text())
+    assert rep["status"] == "finished" and rep["last_step"] is not None and rep["cost"] is not None
+    state = json.loads((out / "run_state.json").read_text())
+    assert "ended" in state
+    assert (out / "checkpoints" / "rank_0" / "model.safetensors").read_bytes() == b"stand-in", "checkpoints were not salvaged"
+    assert launch.main(["status", "--out", str(out)]) == 0
+    assert launch.main(["teardown", "--out", str(out)]) == 0          # nothing left to stop: only salvages
+    plot_live.main([str(out / "train.log"), "--out", str(tmp_path / "c.svg")])
+    svg = (tmp_path / "c.svg").read_text()
+    assert svg.startswith("<svg") and "polyline" in svg
