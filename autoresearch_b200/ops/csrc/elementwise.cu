@@ -29,6 +29,10 @@ __device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
 
 constexpr int ROWS_PER_CTA = 8;  // 8 warps, one row each
 
@@ -162,20 +166,24 @@ __global__ void __launch_bounds__(256) resid_norm_bwd_k(const __nv_bfloat16* __r
   const float l0 = __bfloat162float(lam_0[idx]);
   float sr = 0.f, s0 = 0.f;
   if (row < rows) {
-    float xv[NV][8], bv[NV][8], gv[NV][8];
+    // the row is kept as packed bf16 (4 registers per 8 values) between the two passes: with fp32 copies of
+    // three arrays the kernel needed 127 registers and ran at a quarter of the possible occupancy
+    uint4 xq[NV], bq[NV], gq[NV];
     float ss = 0.f, dot = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int c = lane + 32 * i;
       if (c < nch) {
-        ld8(x + row * D + c * 8, xv[i]);
-        ld8(x0 + row * D + c * 8, bv[i]);
-        ld8(g_xn + row * D + c * 8, gv[i]);
+        xq[i] = *reinterpret_cast<const uint4*>(x + row * D + c * 8);
+        bq[i] = *reinterpret_cast<const uint4*>(x0 + row * D + c * 8);
+        gq[i] = *reinterpret_cast<const uint4*>(g_xn + row * D + c * 8);
+        float xv[8], bv[8], gv[8];
+        unpack8(xq[i], xv); unpack8(bq[i], bv); unpack8(gq[i], gv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float xs = bf16_round(lr * xv[i][j] + l0 * bv[i][j]);
+          const float xs = bf16_round(lr * xv[j] + l0 * bv[j]);
           ss += xs * xs;
-          dot += xs * gv[i][j];
+          dot += xs * gv[j];
         }
       }
     }
@@ -187,16 +195,17 @@ __global__ void __launch_bounds__(256) resid_norm_bwd_k(const __nv_bfloat16* __r
     for (int i = 0; i < NV; ++i) {
       const int c = lane + 32 * i;
       if (c < nch) {
-        float gs[8], o1[8], o2[8];
+        float gs[8], o1[8], o2[8], xv[8], bv[8], gv[8];
         ld8(g_xs + row * D + c * 8, gs);
+        unpack8(xq[i], xv); unpack8(bq[i], bv); unpack8(gq[i], gv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float xs = bf16_round(lr * xv[i][j] + l0 * bv[i][j]);
-          const float t = gs[j] + r * (gv[i][j] - xs * coef);
+          const float xs = bf16_round(lr * xv[j] + l0 * bv[j]);
+          const float t = gs[j] + r * (gv[j] - xs * coef);
           o1[j] = lr * t;
           o2[j] = l0 * t;
-          sr += xv[i][j] * t;
-          s0 += bv[i][j] * t;
+          sr += xv[j] * t;
+          s0 += bv[j] * t;
         }
         st8(d_x + row * D + c * 8, o1);
         st8(d_x0 + row * D + c * 8, o2);
@@ -315,6 +324,9 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&f)[4]) {
   *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]));
 }
 
+// One warp per token: the cos/sin row of the token is loaded once and reused by all 2H q/k heads, the
+// token-index arithmetic is done once, and two heads are in flight per iteration.  (One warp per
+// (token, head) made these kernels instruction-bound: 2-3 million warps, each with two 64-bit divisions.)
 __global__ void __launch_bounds__(256) qkv_post_fwd_k(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ cos_t,
                                                       const __nv_bfloat16* __restrict__ sin_t, float* __restrict__ rstd_qk,
                                                       const __nv_bfloat16* __restrict__ xn, const int* __restrict__ ids,
@@ -322,51 +334,59 @@ __global__ void __launch_bounds__(256) qkv_post_fwd_k(__nv_bfloat16* __restrict_
                                                       float* __restrict__ gate_out, long long N, int T, int H, int D_model,
                                                       int gate_ch, float eps) {
   const int lane = threadIdx.x & 31;
-  const int slots = ve_w ? 3 * H : 2 * H;
-  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (wid >= N * slots) return;
-  const long long tok = wid / slots;
-  const int slot = int(wid - tok * slots);
+  const long long tok = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tok >= N) return;
   const int Dl = H * 128;
-  __nv_bfloat16* row = qkv + tok * 3 * Dl + slot * 128;  // slot < 2H: q/k head; else v head
-  if (slot < 2 * H) {
-    const int t = int(tok % T);
-    float v[4], c[4], s[4];
-    ld4(row + lane * 4, v);
-    const int hi = lane >> 4;                 // 0: low half, 1: high half
-    const int pos = (lane & 15) * 4;          // index inside the half
-    ld4(cos_t + (long long)t * 64 + pos, c);
-    ld4(sin_t + (long long)t * 64 + pos, s);
-    float o[4], ss = 0.f;
+  __nv_bfloat16* base = qkv + tok * 3 * Dl + lane * 4;
+  const int t = int(tok % T);
+  const int hi = lane >> 4;                 // 0: low half of the head, 1: high half
+  const int pos = (lane & 15) * 4;          // index inside the half
+  float c[4], sn[4];
+  ld4(cos_t + (long long)t * 64 + pos, c);
+  ld4(sin_t + (long long)t * 64 + pos, sn);
+  if (hi) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sn[j] = -sn[j];   // lo' = lo*c + hi*s ; hi' = hi*c - lo*s
+  }
+  for (int slot = 0; slot < 2 * H; slot += 2) {
+    float v0[4], v1[4], o0[4], o1[4];
+    ld4(base + slot * 128, v0);
+    ld4(base + (slot + 1) * 128, v1);
+    float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-      // lo' = lo*c + hi*s ; hi' = -lo*s + hi*c
-      o[j] = hi ? (v[j] * c[j] - other * s[j]) : (v[j] * c[j] + other * s[j]);
-      ss += o[j] * o[j];
+      const float p0 = __shfl_xor_sync(0xffffffffu, v0[j], 16), p1 = __shfl_xor_sync(0xffffffffu, v1[j], 16);
+      o0[j] = v0[j] * c[j] + p0 * sn[j];
+      o1[j] = v1[j] * c[j] + p1 * sn[j];
+      s0 += o0[j] * o0[j];
+      s1 += o1[j] * o1[j];
     }
-    ss = warp_sum(ss);
-    const float r = rsqrtf(ss / 128.f + eps);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[j] *= r;
-    st4(row + lane * 4, o);
-    if (lane == 0) rstd_qk[tok * 2 * H + slot] = r;
-  } else {
-    const int h = slot - 2 * H;
-    // gate logit = xn[tok, :gate_ch] . Wg[h, :]
-    float part = 0.f;
-    for (int j = lane; j < gate_ch; j += 32)
-      part += __bfloat162float(xn[tok * D_model + j]) * __bfloat162float(gate_w[h * gate_ch + j]);
-    const float gl = warp_sum(part);
-    if (lane == 0) gate_out[tok * H + h] = gl;
-    const float gs = 2.f / (1.f + __expf(-gl));
-    int id = ids[tok];
-    float v[4], e[4];
-    ld4(row + lane * 4, v);
-    ld4(ve_w + (long long)id * Dl + h * 128 + lane * 4, e);
+    for (int m = 16; m > 0; m >>= 1) { s0 += __shfl_xor_sync(0xffffffffu, s0, m); s1 += __shfl_xor_sync(0xffffffffu, s1, m); }
+    const float r0 = rsqrtf(s0 / 128.f + eps), r1 = rsqrtf(s1 / 128.f + eps);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] += gs * e[j];
-    st4(row + lane * 4, v);
+    for (int j = 0; j < 4; ++j) { o0[j] *= r0; o1[j] *= r1; }
+    st4(base + slot * 128, o0);
+    st4(base + (slot + 1) * 128, o1);
+    if (lane == 0) *reinterpret_cast<float2*>(rstd_qk + tok * 2 * H + slot) = make_float2(r0, r1);
+  }
+  if (ve_w) {
+    const int id = ids[tok];
+    // gate logit of head h = xn[tok, :gate_ch] . Wg[h, :]; lane j holds xn[tok, j], xn[tok, j+32], ...
+    for (int h = 0; h < H; ++h) {
+      float part = 0.f;
+      for (int j = lane; j < gate_ch; j += 32)
+        part += __bfloat162float(xn[tok * D_model + j]) * __bfloat162float(gate_w[h * gate_ch + j]);
+      const float gl = warp_sum(part);
+      if (lane == 0) gate_out[tok * H + h] = gl;
+      const float gs = 2.f / (1.f + __expf(-gl));
+      float v[4], e[4];
+      ld4(base + (2 * H + h) * 128, v);
+      ld4(ve_w + (long long)id * Dl + h * 128 + lane * 4, e);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] += gs * e[j];
+      st4(base + (2 * H + h) * 128, v);
+    }
   }
 }
 
@@ -378,50 +398,59 @@ __global__ void __launch_bounds__(256) qkv_post_bwd_k(__nv_bfloat16* __restrict_
                                                       __nv_bfloat16* __restrict__ d_ve, float* __restrict__ d_gate_logit,
                                                       long long N, int T, int H) {
   const int lane = threadIdx.x & 31;
-  const int slots = ve_w ? 3 * H : 2 * H;
-  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (wid >= N * slots) return;
-  const long long tok = wid / slots;
-  const int slot = int(wid - tok * slots);
+  const long long tok = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tok >= N) return;
   const int Dl = H * 128;
-  const long long off = tok * 3 * Dl + slot * 128 + lane * 4;
-  if (slot < 2 * H) {
-    const int t = int(tok % T);
-    float y[4], g[4], c[4], s[4];
-    ld4(qkv + off, y);
-    ld4(dqkv + off, g);
-    const float r = rstd_qk[tok * 2 * H + slot];
-    float dot = 0.f;
+  const long long off = tok * 3 * Dl + lane * 4;
+  const int t = int(tok % T);
+  const int hi = lane >> 4;
+  const int pos = (lane & 15) * 4;
+  float c[4], sn[4];
+  ld4(cos_t + (long long)t * 64 + pos, c);
+  ld4(sin_t + (long long)t * 64 + pos, sn);
+  if (!hi) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) dot += y[j] * g[j];
-    dot = warp_sum(dot) / 128.f;
-    const int hi = lane >> 4;
-    const int pos = (lane & 15) * 4;
-    ld4(cos_t + (long long)t * 64 + pos, c);
-    ld4(sin_t + (long long)t * 64 + pos, s);
-    float o[4];
+    for (int j = 0; j < 4; ++j) sn[j] = -sn[j];   // transpose of the rotation: d_lo = g_lo*c - g_hi*s ; d_hi = g_hi*c + g_lo*s
+  }
+  for (int slot = 0; slot < 2 * H; slot += 2) {
+    float y0[4], y1[4], g0[4], g1[4];
+    ld4(qkv + off + slot * 128, y0);
+    ld4(qkv + off + (slot + 1) * 128, y1);
+    ld4(dqkv + off + slot * 128, g0);
+    ld4(dqkv + off + (slot + 1) * 128, g1);
+    const float2 r = *reinterpret_cast<const float2*>(rstd_qk + tok * 2 * H + slot);
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { d0 += y0[j] * g0[j]; d1 += y1[j] * g1[j]; }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) { d0 += __shfl_xor_sync(0xffffffffu, d0, m); d1 += __shfl_xor_sync(0xffffffffu, d1, m); }
+    d0 *= (1.f / 128.f); d1 *= (1.f / 128.f);
+    float o0[4], o1[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float gr = r * (g[j] - y[j] * dot);  // grad wrt the rotated (pre-norm) value
-      const float other = __shfl_xor_sync(0xffffffffu, gr, 16);
-      // transpose of the rotation: d_lo = g_lo*c - g_hi*s ; d_hi = g_lo*s + g_hi*c
-      o[j] = hi ? (other * s[j] + gr * c[j]) : (gr * c[j] - other * s[j]);
+      const float a0 = r.x * (g0[j] - y0[j] * d0), a1 = r.y * (g1[j] - y1[j] * d1);   // grad wrt the rotated value
+      const float p0 = __shfl_xor_sync(0xffffffffu, a0, 16), p1 = __shfl_xor_sync(0xffffffffu, a1, 16);
+      o0[j] = a0 * c[j] + p0 * sn[j];
+      o1[j] = a1 * c[j] + p1 * sn[j];
     }
-    st4(dqkv + off, o);
-  } else {
-    const int h = slot - 2 * H;
-    const float gl = gate[tok * H + h];
-    const float sg = 1.f / (1.f + __expf(-gl));
-    float g[4], e[4], o[4];
-    ld4(dqkv + off, g);
+    st4(dqkv + off + slot * 128, o0);
+    st4(dqkv + off + (slot + 1) * 128, o1);
+  }
+  if (ve_w) {
     const int id = ids[tok];
-    ld4(ve_w + (long long)id * Dl + h * 128 + lane * 4, e);
-    float dot = 0.f;
+    for (int h = 0; h < H; ++h) {
+      const float gl = gate[tok * H + h];
+      const float sg = 1.f / (1.f + __expf(-gl));
+      float g[4], e[4], o[4];
+      ld4(dqkv + off + (2 * H + h) * 128, g);
+      ld4(ve_w + (long long)id * Dl + h * 128 + lane * 4, e);
+      float dot = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { o[j] = 2.f * sg * g[j]; dot += e[j] * g[j]; }
-    st4(d_ve + tok * Dl + h * 128 + lane * 4, o);
-    dot = warp_sum(dot);
-    if (lane == 0) d_gate_logit[tok * H + h] = 2.f * sg * (1.f - sg) * dot;
+      for (int j = 0; j < 4; ++j) { o[j] = 2.f * sg * g[j]; dot += e[j] * g[j]; }
+      st4(d_ve + tok * Dl + h * 128 + lane * 4, o);
+      dot = warp_sum(dot);
+      if (lane == 0) d_gate_logit[tok * H + h] = 2.f * sg * (1.f - sg) * dot;
+    }
   }
 }
 
@@ -542,8 +571,7 @@ int arb_qkv_post_fwd(void* qkv, const void* cos_t, const void* sin_t, float* rst
                      int gate_ch, float eps, cudaStream_t s) {
   if (N <= 0 || T <= 0 || H <= 0 || misaligned(qkv) || (reinterpret_cast<uintptr_t>(cos_t) & 7) || (reinterpret_cast<uintptr_t>(sin_t) & 7)) return -3;
   if (ve_w && (!gate_w || !gate_out || !xn || !ids || misaligned(ve_w))) return -3;
-  const long long warps = N * (ve_w ? 3 * H : 2 * H);
-  qkv_post_fwd_k<<<int((warps + 7) / 8), 256, 0, s>>>((bf16*)qkv, (const bf16*)cos_t, (const bf16*)sin_t, rstd_qk, (const bf16*)xn, ids,
+  qkv_post_fwd_k<<<int((N + 7) / 8), 256, 0, s>>>((bf16*)qkv, (const bf16*)cos_t, (const bf16*)sin_t, rstd_qk, (const bf16*)xn, ids,
                                                       (const bf16*)ve_w, (const bf16*)gate_w, gate_out, N, T, H, D_model, gate_ch, eps);
   return int(cudaGetLastError());
 }
@@ -552,8 +580,7 @@ int arb_qkv_post_bwd(void* d_qkv, const void* qkv, const void* cos_t, const void
                      void* d_xn_gate, float* dgl, long long N, int T, int H, int D_model, int gate_ch, cudaStream_t s) {
   if (N <= 0 || T <= 0 || H <= 0 || misaligned(d_qkv) || misaligned(qkv)) return -3;
   if (ve_w && (!gate_w || !gate || !xn || !ids || !d_ve || !d_gate_w || !d_xn_gate || !dgl || H * gate_ch > 256)) return -3;
-  const long long warps = N * (ve_w ? 3 * H : 2 * H);
-  qkv_post_bwd_k<<<int((warps + 7) / 8), 256, 0, s>>>((bf16*)d_qkv, (const bf16*)qkv, (const bf16*)cos_t, (const bf16*)sin_t, rstd_qk,
+  qkv_post_bwd_k<<<int((N + 7) / 8), 256, 0, s>>>((bf16*)d_qkv, (const bf16*)qkv, (const bf16*)cos_t, (const bf16*)sin_t, rstd_qk,
                                                       (const bf16*)xn, ids, (const bf16*)ve_w, (const bf16*)gate_w, gate, (bf16*)d_ve,
                                                       dgl, N, T, H);
   int rc = int(cudaGetLastError());
