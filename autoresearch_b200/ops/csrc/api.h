@@ -40,6 +40,8 @@ int arb_gemm_bf16(const void* A, const void* B, void* C, const void* aux, int M,
 // Tile selection: 0 = automatic (2-CTA 256x256 tiles when M >= 512 and N >= 256, else 1-CTA
 // 128x256/128x128), 1 = always 1-CTA, 2 = always 2-CTA.  Process-wide; meant for tests / benchmarks.
 int arb_gemm_set_mode(int mode);
+// one-shot: the next arb_gemm_bf16 of the calling thread pulls `bytes` from `src` to `dst` in its prologue
+int arb_gemm_pull_next(const void* src, void* dst, long long bytes);
 
 // ---- flash attention (attn_sm100.cu) ----------------------------------------------------------
 // q, k, v, o: [B, T, H, hd=128] bf16 with token stride `ld*` elements (head h at column
@@ -142,6 +144,8 @@ int arb_all_gather_pull(const void* const* peer_bufs, int world, int rank, void*
                         cudaStream_t s);
 // Bounded flag barrier among ranks: each rank writes `epoch` to flags[rank] of every peer,
 // then waits (<= 2 s) until all of its own flags reach `epoch`.
+// dst[i][0..bytes[i]) = src[i][0..bytes[i]) for n ranges (peer or local memory), 16-byte granularity
+int arb_pull_ranges(const void* const* src, void* const* dst, const long long* bytes, int n, cudaStream_t s);
 int arb_peer_barrier(int* const* peer_flags, int world, int rank, int epoch, int* err_flag, cudaStream_t s);
 
 // ---- mixture of experts (moe.cu) ---------------------------------------------------------------

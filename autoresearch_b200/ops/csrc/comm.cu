@@ -87,6 +87,24 @@ __global__ void __launch_bounds__(256) all_gather_pull_k(PeerPtrs peers, int wor
   }
 }
 
+// Copies up to PULL_MAX_RANGES address ranges (16-byte units) from peer memory into local memory.
+constexpr int PULL_MAX_RANGES = 96;
+struct PullRanges {
+  const uint4* src[PULL_MAX_RANGES];
+  uint4* dst[PULL_MAX_RANGES];
+  long long end16[PULL_MAX_RANGES];   // running end of each range in the concatenated index space
+  int n;
+};
+__global__ void pull_ranges_k(const __grid_constant__ PullRanges r) {
+  const long long total = r.end16[r.n - 1];
+  int k = 0;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    while (i >= r.end16[k]) ++k;                       // indices only grow inside a thread
+    const long long j = i - (k ? r.end16[k - 1] : 0);
+    r.dst[k][j] = r.src[k][j];
+  }
+}
+
 __global__ void all_gather_push_k(PeerPtrsMut peers, int world, int rank, const uint4* __restrict__ src, long long off16, long long n16) {
   const long long total = n16 * (world - 1);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -176,6 +194,29 @@ int arb_peer_barrier(int* const* peer_flags, int world, int rank, int epoch, int
   for (int i = 0; i < world; ++i) pp.p[i] = peer_flags[i];
   peer_barrier_k<<<1, 32, 0, s>>>(pp, world, rank, epoch, err_flag);
   return int(cudaGetLastError());
+}
+
+// n ranges: dst[i][0..bytes[i]) = src[i][0..bytes[i]); pointers and sizes multiples of 16 bytes; one launch per
+// PULL_MAX_RANGES ranges.
+int arb_pull_ranges(const void* const* src, void* const* dst, const long long* bytes, int n, cudaStream_t s) {
+  if (n < 0) return -3;
+  for (int base = 0; base < n; base += PULL_MAX_RANGES) {
+    PullRanges r;
+    r.n = (n - base < PULL_MAX_RANGES) ? n - base : PULL_MAX_RANGES;
+    long long run = 0;
+    for (int i = 0; i < r.n; ++i) {
+      const long long b = bytes[base + i];
+      if (b <= 0 || (b & 15) || ((reinterpret_cast<uintptr_t>(src[base + i]) | reinterpret_cast<uintptr_t>(dst[base + i])) & 15)) return -3;
+      r.src[i] = reinterpret_cast<const uint4*>(src[base + i]);
+      r.dst[i] = reinterpret_cast<uint4*>(dst[base + i]);
+      run += b / 16;
+      r.end16[i] = run;
+    }
+    pull_ranges_k<<<comm_grid(run), 256, 0, s>>>(r);
+    const int rc = int(cudaGetLastError());
+    if (rc) return rc;
+  }
+  return 0;
 }
 
 }  // extern "C"

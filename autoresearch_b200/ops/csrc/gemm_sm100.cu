@@ -35,7 +35,47 @@ struct GemmArgs {
   float alpha, beta, gamma;
   int* err;
   int flags;   // experiment switches of the 2-CTA kernel: bit0 = multicast commits, bit1 = leader-only barrier arrive
+  // Optional prologue: before any tile is loaded, all CTAs of this (fully resident, persistent) grid copy
+  // pull_n16 16-byte units from pull_src (the owner rank's copy of the B operand, NVLink peer loads) to
+  // pull_dst (the local operand) and meet at a counter barrier.  Fuses the data-parallel all-gather of an
+  // updated weight into the first GEMM that consumes it.
+  const uint4* pull_src;
+  uint4* pull_dst;
+  long long pull_n16;
+  unsigned* pull_counter;
+  unsigned pull_target;
 };
+
+// Runs in every thread of every CTA at kernel start.  The waits are bounded; on expiry the error word is set
+// and the kernel goes on (the result is then wrong, the host raises on the error word).
+__device__ __forceinline__ void pull_prologue(const GemmArgs& p) {
+  if (p.pull_n16 <= 0) return;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < p.pull_n16; i += stride) {
+    uint4 v;
+    asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p.pull_src + i));
+    p.pull_dst[i] = v;
+  }
+  __threadfence();
+  asm volatile("fence.proxy.async;" ::: "memory");   // the copies are read by TMA (async proxy) below
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.pull_counter) : "memory");
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+      unsigned v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.pull_counter) : "memory");
+      if (int(v - p.pull_target) >= 0) break;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        if (p.err) atomicExch(p.err, ERR_GEMM_TIMEOUT);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
 
 template <int BN>
 struct SmemLayout {
@@ -133,6 +173,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int items = p.batch * p.m_tiles * p.n_tiles * p.splitk;
+  pull_prologue(p);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -312,6 +353,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int cluster_id = blockIdx.x >> 1;
   const int n_clusters = gridDim.x >> 1;
   const int items = p.batch * p.m_tiles * p.n_tiles * p.splitk;   // m_tiles counted in 256-row tiles
+  pull_prologue(p);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -562,6 +604,33 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ------------------------------------------------------------------------------------------
 static int g_num_sms = 0;
 static int g_gemm_flags = 0;
+// one-shot request set by arb_gemm_pull_next and consumed by the next arb_gemm_bf16 of this thread
+struct PullRequest { const void* src; void* dst; long long bytes; };
+static thread_local PullRequest g_pull = {nullptr, nullptr, 0};
+constexpr int PULL_MAX_DEV = 64;
+static unsigned* g_pull_counter[PULL_MAX_DEV] = {nullptr};
+static unsigned g_pull_total[PULL_MAX_DEV] = {0};
+
+// Fills the pull fields for a launch of `grid_ctas` CTAs; 0 on success.
+static int arm_pull(GemmArgs& a, int grid_ctas) {
+  a.pull_src = nullptr; a.pull_dst = nullptr; a.pull_n16 = 0; a.pull_counter = nullptr; a.pull_target = 0;
+  if (!g_pull.src) return 0;
+  const PullRequest rq = g_pull;
+  g_pull = {nullptr, nullptr, 0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PULL_MAX_DEV) return -7;
+  if (!g_pull_counter[dev]) {
+    if (cudaMalloc(&g_pull_counter[dev], sizeof(unsigned)) != cudaSuccess) return -7;
+    if (cudaMemset(g_pull_counter[dev], 0, sizeof(unsigned)) != cudaSuccess) return -7;
+  }
+  g_pull_total[dev] += unsigned(grid_ctas);
+  a.pull_src = reinterpret_cast<const uint4*>(rq.src);
+  a.pull_dst = reinterpret_cast<uint4*>(rq.dst);
+  a.pull_n16 = rq.bytes / 16;
+  a.pull_counter = g_pull_counter[dev];
+  a.pull_target = g_pull_total[dev];
+  return 0;
+}
 static int g_gemm_mode = 0;   // 0 = automatic, 1 = always 1-CTA tiles, 2 = always 2-CTA tiles
 
 template <bool A_MN, bool B_MN, int EPI, int BN>
@@ -576,7 +645,9 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
   }
   const int items = a.batch * a.m_tiles * a.n_tiles * a.splitk;
   const int grid = items < g_num_sms ? items : g_num_sms;
-  kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, a);
+  GemmArgs args = a;
+  if (int r = arm_pull(args, grid)) return r;
+  kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, args);
   return int(cudaGetLastError());
 }
 
@@ -620,7 +691,9 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return int(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, a));
+  GemmArgs args = a;
+  if (int r = arm_pull(args, clusters * 2)) return r;
+  return int(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, args));
 }
 
 template <bool A_MN, bool B_MN>
@@ -658,6 +731,13 @@ using namespace arb;
 extern "C" int arb_gemm_set_mode(int mode) {
   if (mode < 0 || mode > 2) return -3;
   g_gemm_mode = mode;
+  return 0;
+}
+// The next arb_gemm_bf16 call of this thread first copies `bytes` (a multiple of 16) from `src` (typically a
+// peer rank's copy of its B operand) to `dst` inside the GEMM kernel; see GemmArgs::pull_src.
+extern "C" int arb_gemm_pull_next(const void* src, void* dst, long long bytes) {
+  if (!src || !dst || bytes <= 0 || (bytes & 15) || ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return -3;
+  g_pull = {src, dst, bytes};
   return 0;
 }
 extern "C" int arb_gemm_set_flags(int flags) {

@@ -21,6 +21,9 @@ ERR_NAMES = {1: "GEMM barrier wait timed out", 2: "attention barrier wait timed 
              5: "dynamic shared memory base is not 1 KB aligned"}
 
 launch_count = 0  # number of kernel-launching calls made through this module
+# B operands whose up-to-date copy still sits on another rank: data_ptr -> (peer pointer, bytes).  The first
+# GEMM that consumes such an operand pulls it inside the kernel (parallel/fused_dp.py registers the entries).
+pending_pulls = {}
 
 
 class KernelError(RuntimeError):
@@ -69,6 +72,8 @@ def lib() -> C.CDLL:
         "arb_all_gather_push": [vp, i32, i32, vp, i64, i64, vp],
         "arb_all_gather_pull": [vp, i32, i32, vp, i64, vp],
         "arb_peer_barrier": [vp, i32, i32, i32, vp, vp],
+        "arb_pull_ranges": [vp, vp, vp, i32, vp],
+        "arb_gemm_pull_next": [vp, vp, i64],
         "arb_moe_router_fwd": [vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
         "arb_moe_router_bwd": [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, vp],
         "arb_moe_slot_positions": [vp, i64, i32, vp, vp, vp, vp],
@@ -174,6 +179,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     if tuple(o2.shape) != (M, N) or out.dtype != (torch.float32 if f32_out else torch.bfloat16):
         raise ValueError("out has the wrong shape or dtype")
     so = out.stride(0) if batched else 0
+    if pending_pulls:
+        pull = pending_pulls.pop(b.data_ptr(), None)
+        if pull is not None:
+            _check(lib().arb_gemm_pull_next(pull[0], b.data_ptr(), pull[1]), "gemm_pull_next")
     auxp = 0
     if aux is not None:
         _bf16(aux, "aux")
@@ -195,6 +204,19 @@ def gemm_set_mode(mode: int) -> None:
     f.restype, f.argtypes = C.c_int, [C.c_int]
     if f(mode) != 0:
         raise ValueError(f"bad GEMM mode {mode}")
+
+
+def flush_pending_pulls() -> None:
+    """Materialise every operand that no GEMM has pulled yet (before anything else reads the parameters)."""
+    if not pending_pulls:
+        return
+    items = list(pending_pulls.items())
+    pending_pulls.clear()
+    n = len(items)
+    src = (C.c_void_p * n)(*[v[0] for _, v in items])
+    dst = (C.c_void_p * n)(*[k for k, _ in items])
+    nb = (C.c_longlong * n)(*[v[1] for _, v in items])
+    _check(lib().arb_pull_ranges(src, dst, nb, n, _stream()), "pull_ranges")
 
 
 def attn_set_mode(mode: int) -> None:

@@ -11,7 +11,10 @@ Per optimizer step, on the compute stream:
    fp32, applying the scale and writing the fp32 gradient the optimizer consumes;
 4. the optimizer updates the owned matrices and writes bf16 parameters into the symmetric
    parameter buffer;
-5. a second barrier, then one kernel pulls every peer's updated shard into the local copy.
+5. a second barrier; the dense weight matrices (wqkv, wo, wfc, wdn: 99 % of the bytes) are NOT
+   copied here: each is registered as pending and the first GEMM that uses it as its B operand
+   pulls it from the owner's memory in its own prologue (``GemmArgs::pull_src``); one small kernel
+   pulls everything else (embeddings, head, scalars, gates, experts).
 
 The library arm (``LibraryComm``) does the same with ncclReduceScatter / ncclAllGather and is
 what this path is measured against.
@@ -102,6 +105,7 @@ class FusedComm:
         return src
 
     def reduce_scatter_grads(self, layout: ParamLayout) -> None:
+        K.flush_pending_pulls()   # normally empty: the forward pass has pulled every weight it used
         lo, hi = layout.shard_range()
         src_bf16 = self.bucket_dtype == torch.bfloat16
         if src_bf16:
@@ -126,11 +130,56 @@ class FusedComm:
                                                 1.0, K._stream())
             K._check(rc, "reduce_scatter")
 
+    fuse_into_gemm = True
+    GEMM_OPERANDS = (".wqkv", ".wo", ".wfc", ".wdn")
+
+    def _plan_gather(self, layout: ParamLayout):
+        """Per non-owned atom: pulled by its first GEMM, or part of a range copied right away.  Ranges are
+        the complement of the GEMM operands inside each peer's shard, merged and widened to 16 bytes (a
+        peer's shard holds only atoms that peer owns, so the neighbours copied along are current too)."""
+        es = layout.flat_param.element_size()
+        gemm_atoms, ranges = [], []
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            lo, hi = layout.shard_range(r)
+            atoms = sorted((a for a in layout.atoms if a.owner == r), key=lambda a: a.offset)
+            cur = None
+            for a in atoms:
+                is_gemm = (self.fuse_into_gemm and a.name.endswith(self.GEMM_OPERANDS) and a.param.dim() == 2
+                           and (a.numel * es) % 16 == 0 and (a.offset * es) % 16 == 0)
+                if is_gemm:
+                    gemm_atoms.append((a, r))
+                    continue
+                b0 = (a.offset * es) // 16 * 16
+                b1 = min(((a.offset + a.numel) * es + 15) // 16 * 16, hi * es)
+                if cur is not None and b0 <= cur[1]:
+                    cur[1] = max(cur[1], b1)
+                else:
+                    cur = [b0, b1, r]
+                    ranges.append(cur)
+        return gemm_atoms, ranges
+
     def all_gather_params(self, layout: ParamLayout) -> None:
         self.barrier()
-        shard_bytes = layout.shard_size * layout.flat_param.element_size()
-        rc = K.lib().arb_all_gather_pull(self._param_ptrs, self.world, self.rank, layout.flat_param.data_ptr(),
-                                         shard_bytes, K._stream())
-        K._check(rc, "all_gather_pull")
+        if getattr(self, "_plan", None) is None:
+            self._plan = self._plan_gather(layout)
+        gemm_atoms, ranges = self._plan
+        base = layout.flat_param.data_ptr()
+        es = layout.flat_param.element_size()
+        peers = self._param.peer_ptrs
+        for a, r in gemm_atoms:
+            K.pending_pulls[base + a.offset * es] = (peers[r] + a.offset * es, a.numel * es)
+        if ranges:
+            n = len(ranges)
+            src = (C.c_void_p * n)(*[peers[r] + b0 for b0, _, r in ranges])
+            dst = (C.c_void_p * n)(*[base + b0 for b0, _, _ in ranges])
+            nb = (C.c_longlong * n)(*[b1 - b0 for b0, b1, _ in ranges])
+            K._check(K.lib().arb_pull_ranges(src, dst, nb, n, K._stream()), "pull_ranges")
         # peers may start overwriting their shards (next optimizer step) only after everyone has
-        # pulled: the barrier that opens the next reduce-scatter provides that ordering.
+        # pulled: the barrier that opens the next reduce-scatter provides that ordering, and every
+        # pending operand is pulled by the forward pass (or by flush()) before that barrier.
+
+    def flush(self) -> None:
+        """Pull whatever no GEMM has pulled yet (before parameters are read by anything else)."""
+        K.flush_pending_pulls()

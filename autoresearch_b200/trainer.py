@@ -344,6 +344,8 @@ class Trainer:
                         group=self.group if self.world > 1 else None)
 
     def save(self, step: Optional[int]) -> Optional[str]:
+        if hasattr(self.comm, "flush"):
+            self.comm.flush()     # weights whose pull is still pending are read below
         state = dict(step=self.step, loss_ema=self.loss_ema, ema_steps=self.ema_steps,
                      wsd=self.wsd.state_dict(), world=self.world,
                      data=(self.train_loader.state_dict() if hasattr(self.train_loader, "state_dict") else None))

@@ -32,7 +32,7 @@ for _ in range(8):
     losses.append(tr.mean_loss_across_ranks(l))
 torch.cuda.synchronize(); K.check_err_flag()
 if int(os.environ.get("RANK", "0")) == 0:
-    print("RESULT " + json.dumps({"losses": losses, "comm": tr.comm.name}))
+    print("RESULT " + json.dumps({"losses": losses, "comm": tr.comm.name, "pending_pulls": len(K.pending_pulls)}))
 if world > 1:
     dist.destroy_process_group()
 """
@@ -63,6 +63,8 @@ def test_dp2_matches_single_gpu():
     fused = _run(2, "fused", 29612)
     lib = _run(2, "nccl", 29613)
     assert fused["comm"] == "fused" and lib["comm"] == "library"
+    # after a step the dense weights owned by the other rank wait for the GEMMs that will pull them
+    assert fused["pending_pulls"] > 0 and lib["pending_pulls"] == 0
     for a, b, c in zip(one["losses"], fused["losses"], lib["losses"]):
         assert abs(a - b) < 0.05 * abs(a) + 0.02, (one, fused)
         assert abs(a - c) < 0.05 * abs(a) + 0.02, (one, lib)

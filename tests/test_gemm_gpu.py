@@ -117,3 +117,29 @@ def test_rejects_bad_arguments():
     a, b = _rand(128, 60), _rand(128, 60)      # K not a multiple of 8
     with pytest.raises(K_.KernelError):
         K_.gemm(a, b)
+
+
+@pytest.mark.parametrize("shape", [(1024, 512, 256), (192, 128, 64), (4096, 3072, 1024)])
+def test_gemm_pulls_its_b_operand_in_the_prologue(shape):
+    """A registered pending pull makes the GEMM copy its B operand from another buffer first (the mechanism
+    that fuses the parameter all-gather into the first consuming GEMM); here the source is local memory."""
+    from autoresearch_b200.ops import kernels as K
+    M, N, Kd = shape
+    torch.manual_seed(3)
+    x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
+    w_new = (torch.randn(N, Kd, device="cuda") * 0.05).to(torch.bfloat16)
+    w = torch.zeros_like(w_new)                       # stale local copy
+    K.pending_pulls[w.data_ptr()] = (w_new.data_ptr(), w.numel() * 2)
+    for _ in range(3):                                # the counter barrier must work launch after launch
+        y = K.gemm(x, w)
+        torch.cuda.synchronize()
+        K.check_err_flag()
+        assert w.data_ptr() not in K.pending_pulls
+        assert torch.equal(w, w_new)
+        ref = x.float() @ w_new.float().t()
+        assert ((y.float() - ref).norm() / ref.norm()).item() < 1e-2
+        w.zero_()
+        K.pending_pulls[w.data_ptr()] = (w_new.data_ptr(), w.numel() * 2)
+    K.flush_pending_pulls()
+    torch.cuda.synchronize()
+    assert torch.equal(w, w_new) and not K.pending_pulls
