@@ -91,11 +91,14 @@ class MoEFn(torch.autograd.Function):
             ep.barrier()                                      # all routed tokens have arrived
             xg = ep.local("x").clone()
             act = K.gemm(xg, w_fc, epi=K.EPI_RELU2)
-            K.gemm(act, w_proj, out=ep.local("y"))
-            ep.barrier()                                      # expert outputs are visible to the sources
-            out = _gather_rows(ep.table("y"), idx, row, N, top_k, D, E, resid, gates)
+            cs = ep.cap_src
+            for i in range(ep.world):                         # peers first: their tiles have the longer way
+                r = (ep.rank + 1 + i) % ep.world
+                K.gemm(act[:, r * cs:(r + 1) * cs], w_proj, out=ep.recv_view("y", r))
+            ep.barrier()                                      # every expert's outputs for my tokens have arrived
+            out = _gather_rows(ep.recv_table("y"), idx, row, N, top_k, D, E, resid, gates)
             # unscaled expert outputs of this rank's own slots, kept for the gate gradient
-            y_rows = _gather_rows(ep.table("y"), idx.view(-1, 1), row.view(-1, 1), N * top_k, 1, D, E)
+            y_rows = _gather_rows(ep.recv_table("y"), idx.view(-1, 1), row.view(-1, 1), N * top_k, 1, D, E)
             y = None
         ctx.save_for_backward(xn, router_w, w_fc, w_proj, probs, idx, gates, row, xg, act,
                               y if y is not None else y_rows, f)
@@ -132,9 +135,12 @@ class MoEFn(torch.autograd.Function):
             d_xg = K.gemm(d_act, w_fc, trans_b=False)
             d_xn = _gather_rows(_ptr_table(d_xg), idx, row, N, top_k, D, E)
         else:
-            K.gemm(d_act, w_fc, trans_b=False, out=ep.local("dx"))
-            ep.barrier()                                      # input gradients are visible to the sources
-            d_xn = _gather_rows(ep.table("dx"), idx, row, N, top_k, D, E)
+            cs = ep.cap_src
+            for i in range(ep.world):
+                r = (ep.rank + 1 + i) % ep.world
+                K.gemm(d_act[:, r * cs:(r + 1) * cs], w_fc, trans_b=False, out=ep.recv_view("dx", r))
+            ep.barrier()                                      # the input gradients of my tokens have arrived
+            d_xn = _gather_rows(ep.recv_table("dx"), idx, row, N, top_k, D, E)
         aux_dp = None
         if g_aux is not None and aux_coeff != 0.0:
             aux_dp = ((g_aux.float() * (aux_coeff * E / float(N))) * f).contiguous()

@@ -63,6 +63,27 @@ class EPContext:
         """This rank's staging buffer viewed as [E_local, world * cap_src, D]."""
         return self.bufs[name].tensor.view(self.E_local, self.world * self.cap_src, self.D)
 
+    # ---- receive side of the expert-output exchange -------------------------------------------------
+    # The "y" and "dx" buffers are laid out by the rank that RECEIVES them: [E, cap_src, D], expert e's rows for
+    # this rank's tokens.  The owner of expert e writes them with the epilogue of its output GEMM (TMA stores
+    # over NVLink), so the combine kernels read local memory only.
+    def recv_view(self, name: str, dst_rank: int) -> torch.Tensor:
+        """Rank `dst_rank`'s receive area for this rank's experts: [E_local, cap_src, D]."""
+        shape = (self.E_local, self.cap_src, self.D)
+        off = self.rank * self.E_local * self.cap_src * self.D
+        if dst_rank == self.rank:
+            return self.bufs[name].tensor[off: off + self.E_local * self.cap_src * self.D].view(shape)
+        return self.bufs[name].peer_tensor(dst_rank, shape, torch.bfloat16, off)
+
+    def recv_table(self, name: str):
+        """Local pointer of every expert's rows in this rank's receive area (host array of E pointers)."""
+        key = ("recv", name)
+        if key not in self._tables:
+            base = self.bufs[name].tensor.data_ptr()
+            slab = self.cap_src * self.D * 2
+            self._tables[key] = (C.c_void_p * self.E)(*[base + e * slab for e in range(self.E)])
+        return self._tables[key]
+
     def barrier(self):
         self.epoch += 1
         rc = K.lib().arb_peer_barrier(self._flag_ptrs, self.world, self.rank, self.epoch,
