@@ -50,6 +50,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+#ifndef ARB_FWD_POLY_OF_8
+#define ARB_FWD_POLY_OF_8 0
+#endif
+// 2^x on the FMA pipe for x <= ~1: round-to-nearest split x = n + f, |f| <= 0.5, cubic for 2^f (max relative
+// error 7.5e-5; the results are rounded to bf16, 3.9e-3), n added to the exponent field.  Very negative
+// arguments (masked scores) give 2^-126, i.e. zero for every purpose here.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = __fadd_rn(x, 12582912.f);             // 1.5 * 2^23: n sits in the low mantissa bits of t
+  const float f = __fsub_rn(x, __fsub_rn(t, 12582912.f));
+  float r = fmaf(f, 0.05517164617776871f, 0.2426111251115799f);
+  r = fmaf(r, f, 0.6932609677314758f);
+  r = fmaf(r, f, 0.9999280571937561f);
+  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }

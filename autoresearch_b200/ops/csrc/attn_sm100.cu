@@ -200,9 +200,16 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           sc[j] = vis ? sc[j] : -INFINITY;
         }
       }
-      float mx = sc[0];
+      // eight independent chains: one chain of 127 dependent max operations cost 400 clk per tile
+#ifndef ARB_FWD_MAX_CHAINS
+#define ARB_FWD_MAX_CHAINS 8
+#endif
+      float mxa[8];
 #pragma unroll
-      for (int j = 1; j < 128; ++j) mx = fmaxf(mx, sc[j]);
+      for (int j = 0; j < 8; ++j) mxa[j] = sc[j];
+#pragma unroll
+      for (int j = 8; j < 128; ++j) mxa[j % ARB_FWD_MAX_CHAINS] = fmaxf(mxa[j % ARB_FWD_MAX_CHAINS], sc[j]);
+      const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])), fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
       const float m_new = fmaxf(m_used, mx);
       bool resc = false;
       if (m_used == -INFINITY) m_used = m_new;            // nothing accumulated for this row yet
@@ -230,18 +237,24 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       // P buffer s was last read by the PV MMA of tile t-2
       if (t >= 2 && !mbar_wait(&p_empty[s], ((t - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
       float rs = 0.f;
+      float rsa[4] = {0.f, 0.f, 0.f, 0.f};
       if constexpr (TS) {
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {   // 64 keys -> 32 packed columns
           uint32_t pk[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const float e0 = fast_exp2(sc[hf * 64 + 2 * j] * c - mc), e1 = fast_exp2(sc[hf * 64 + 2 * j + 1] * c - mc);
-            rs += e0 + e1;
+            // the ex2 unit (4 lanes per clock and scheduler) is the bound of this loop: ARB_FWD_POLY_OF_8 of every
+            // eight exponentials are evaluated as a cubic on the FMA pipe instead
+            const float x0 = sc[hf * 64 + 2 * j] * c - mc, x1 = sc[hf * 64 + 2 * j + 1] * c - mc;
+            const float e0 = ((2 * j) & 7) < ARB_FWD_POLY_OF_8 ? poly_exp2(x0) : fast_exp2(x0);
+            const float e1 = ((2 * j + 1) & 7) < ARB_FWD_POLY_OF_8 ? poly_exp2(x1) : fast_exp2(x1);
+            rsa[j & 3] += e0 + e1;
             pk[j] = pack_bf16(e0, e1);
           }
           tmem_st32(TM_P + lane_addr + uint32_t(s * 64 + hf * 32), pk);
         }
+        rs = (rsa[0] + rsa[1]) + (rsa[2] + rsa[3]);
         tmem_wait_st();
         tc_fence_before();
       } else {
