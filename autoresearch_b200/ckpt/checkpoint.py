@@ -40,10 +40,16 @@ def engine_name(name: str) -> str:
     return name
 
 
-def model_to_engine_tensors(model) -> Dict[str, torch.Tensor]:
+def model_to_engine_tensors(model, expert_gather=None, materialise: bool = True) -> Dict[str, torch.Tensor]:
     """Flat engine-named BF16 tensors of a (full or pipeline-stage) model."""
     cfg = model.cfg
     out: Dict[str, torch.Tensor] = {}
+    if not materialise:
+        # a rank that only takes part in the expert gathers of an expert-parallel save (collective calls)
+        for blk in model.blocks:
+            if blk.router is not None and expert_gather is not None:
+                expert_gather(blk.expert_fc); expert_gather(blk.expert_proj)
+        return out
     bf = lambda t: t.detach().to(torch.bfloat16).cpu().contiguous()
     if model.wte is not None:
         out["wte.weight"] = bf(model.wte)
@@ -66,9 +72,12 @@ def model_to_engine_tensors(model) -> Dict[str, torch.Tensor]:
             out[f"h.{i}.attn.ve_gate.weight"] = bf(blk.ve_gate)
         if blk.router is not None:
             out[f"h.{i}.moe.router.weight"] = bf(blk.router)
-            for e in range(blk.expert_fc.shape[0]):
-                out[f"h.{i}.moe.expert.{e}.fc.weight"] = bf(blk.expert_fc[e])
-                out[f"h.{i}.moe.expert.{e}.proj.weight"] = bf(blk.expert_proj[e])
+            fc, pr = blk.expert_fc, blk.expert_proj
+            if expert_gather is not None:      # expert parallelism: collect the other ranks' experts
+                fc, pr = expert_gather(fc), expert_gather(pr)
+            for e in range(fc.shape[0]):
+                out[f"h.{i}.moe.expert.{e}.fc.weight"] = bf(fc[e])
+                out[f"h.{i}.moe.expert.{e}.proj.weight"] = bf(pr[e])
     return out
 
 
@@ -78,11 +87,13 @@ def checkpoint_path(ckpt_dir: str, step: Optional[int] = None) -> str:
 
 
 def save_checkpoint(model, ckpt_dir: str, step: Optional[int] = None, optimizer=None,
-                    trainer_state: Optional[dict] = None, subdir: Optional[str] = None) -> str:
+                    trainer_state: Optional[dict] = None, subdir: Optional[str] = None, expert_gather=None) -> str:
+    """`expert_gather(t)`: with expert parallelism, returns the [E, ...] stack of all ranks' experts for this
+    rank's [E_local, ...] stack (a collective every rank of the group has to enter, see the trainer)."""
     d = Path(ckpt_dir) / subdir if subdir else Path(ckpt_dir)
     d.mkdir(parents=True, exist_ok=True)
     path = checkpoint_path(str(d), step)
-    save_file(model_to_engine_tensors(model), path)
+    save_file(model_to_engine_tensors(model, expert_gather=expert_gather), path)
     if optimizer is not None:
         save_file(optimizer.state_dict(), str(d / "optim_state.safetensors"))
     if trainer_state is not None:
@@ -158,20 +169,25 @@ def load_weights(model, path: str, strict: bool = True, seed: int = 42) -> Dict[
             E, ME, D = blk.expert_fc.shape
             if f"h.{i}.moe.router.weight" in sd:
                 put(blk.router, f"h.{i}.moe.router.weight")
-                for e in range(E):
-                    blk.expert_fc.data[e].copy_(sd[f"h.{i}.moe.expert.{e}.fc.weight"].to(blk.expert_fc.dtype))
-                    blk.expert_proj.data[e].copy_(sd[f"h.{i}.moe.expert.{e}.proj.weight"].to(blk.expert_proj.dtype))
+                base = int(getattr(model, "ep_rank", 0)) * E if int(getattr(model, "ep", 1)) > 1 else 0
+                for e in range(E):            # E = experts held by this rank; `base` = id of its first expert
+                    blk.expert_fc.data[e].copy_(sd[f"h.{i}.moe.expert.{base + e}.fc.weight"].to(blk.expert_fc.dtype))
+                    blk.expert_proj.data[e].copy_(sd[f"h.{i}.moe.expert.{base + e}.proj.weight"].to(blk.expert_proj.dtype))
                     stats["loaded"] += 2
             elif f"h.{i}.mlp.c_fc.weight" in sd:
                 fc = sd[f"h.{i}.mlp.c_fc.weight"].float()[:ME]
                 pr = sd[f"h.{i}.mlp.c_proj.weight"].float()[:, :ME]
                 s_fc = 0.01 * fc.norm().item() / math.sqrt(fc.numel())
                 s_pr = 0.01 * pr.norm().item() / math.sqrt(pr.numel())
-                for e in range(E):
-                    nf = 0 if e == 0 else torch.randn(fc.shape, generator=gen) * s_fc
-                    np_ = 0 if e == 0 else torch.randn(pr.shape, generator=gen) * s_pr
-                    blk.expert_fc.data[e].copy_((fc + nf).to(blk.expert_fc.dtype))
-                    blk.expert_proj.data[e].copy_((pr + np_).to(blk.expert_proj.dtype))
+                ep_on = int(getattr(model, "ep", 1)) > 1
+                base = int(getattr(model, "ep_rank", 0)) * E if ep_on else 0
+                n_total = model.cfg.moe.n_experts if ep_on else E
+                for g in range(n_total):      # every rank draws the noise of all experts, in order, and keeps its own
+                    nf = 0 if g == 0 else torch.randn(fc.shape, generator=gen) * s_fc
+                    np_ = 0 if g == 0 else torch.randn(pr.shape, generator=gen) * s_pr
+                    if base <= g < base + E:
+                        blk.expert_fc.data[g - base].copy_((fc + nf).to(blk.expert_fc.dtype))
+                        blk.expert_proj.data[g - base].copy_((pr + np_).to(blk.expert_proj.dtype))
                 blk.router.data.zero_()
                 stats["warm_started"] += 1
             elif strict:

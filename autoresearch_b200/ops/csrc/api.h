@@ -92,6 +92,10 @@ int arb_qkv_post_bwd(void* d_qkv, const void* qkv, const void* cos_t, const void
 int arb_embedding_fwd(const int* ids, const void* w, void* out, long long N, int D, int vocab, cudaStream_t s);
 // dW[ids[i], :] += g[i, :]  (fp32 accumulate with red.global)
 int arb_embedding_bwd(const int* ids, const void* g, float* dw, long long N, int D, int vocab, cudaStream_t s);
+// deterministic (sorted, atomic-free) form of arb_embedding_bwd; see elementwise.cu for the plan arrays
+int arb_embedding_bwd_sorted(const long long* perm, const int* item_id, const int* item_start, const int* seg_start,
+                             const int* seg_count, const void* g, float* dw, float* partial, int n_items_max, int D, int R,
+                             int vocab, cudaStream_t s);
 int arb_add_cols(void* dst, long long ld_dst, const void* src, long long rows, int cols, cudaStream_t s);
 int arb_cast_f32_to_bf16(const float* src, void* dst, long long n, float scale, cudaStream_t s);
 int arb_accum_bf16_into_f32(const void* src, float* dst, long long n, cudaStream_t s);

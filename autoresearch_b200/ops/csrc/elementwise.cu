@@ -311,6 +311,58 @@ __global__ void embedding_bwd_k(const int* __restrict__ ids, const __nv_bfloat16
   }
 }
 
+// Deterministic embedding backward: rows sorted by token id (stable), one work item per (id, chunk of at most
+// `R` rows).  An item sums its rows in sorted order in fp32; an id with a single item adds the sum to its table
+// row (it is the only writer), longer ids leave per-item partial sums that embedding_bwd_combine_k adds up in
+// item order.  No atomics: the result does not depend on scheduling (the reference's histogram kernel,
+// brain/kernels/embedding.cu, and the kernel above both rely on the order of atomic adds).
+__global__ void __launch_bounds__(128) embedding_bwd_sorted_k(const long long* __restrict__ perm, const int* __restrict__ item_id,
+                                                              const int* __restrict__ item_start, const int* __restrict__ seg_start,
+                                                              const int* __restrict__ seg_count, const __nv_bfloat16* __restrict__ g,
+                                                              float* __restrict__ dw, float* __restrict__ partial, int n_items_max,
+                                                              int D, int R, int vocab) {
+  const int item = blockIdx.x;
+  const int id = item_id[item];
+  if (id < 0 || id >= vocab) return;                 // padding items beyond the real count
+  const int cnt = seg_count[id];
+  const int sub = item - item_start[id];
+  const int r0 = sub * R, r1 = min(cnt, r0 + R);
+  if (r0 >= r1) return;
+  const long long base = seg_start[id];
+  for (int c = threadIdx.x; c < (D >> 3); c += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = r0; j < r1; ++j) {
+      float f[8];
+      ld8(g + perm[base + j] * D + c * 8, f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += f[k];
+    }
+    float* dst = (cnt <= R) ? dw + (long long)id * D + c * 8 : partial + (long long)item * D + c * 8;
+    float4 a = make_float4(acc[0], acc[1], acc[2], acc[3]), b = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (cnt <= R) {
+      const float4 x = *reinterpret_cast<float4*>(dst), y = *reinterpret_cast<float4*>(dst + 4);
+      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w; b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+    }
+    *reinterpret_cast<float4*>(dst) = a;
+    *reinterpret_cast<float4*>(dst + 4) = b;
+  }
+}
+__global__ void __launch_bounds__(128) embedding_bwd_combine_k(const int* __restrict__ item_start, const int* __restrict__ seg_count,
+                                                               const float* __restrict__ partial, float* __restrict__ dw, int D, int R) {
+  const int id = blockIdx.x;
+  const int cnt = seg_count[id];
+  if (cnt <= R) return;
+  const int n_it = (cnt + R - 1) / R, i0 = item_start[id];
+  for (int c = threadIdx.x; c < (D >> 2); c += blockDim.x) {
+    float4 acc = *reinterpret_cast<float4*>(dw + (long long)id * D + c * 4);
+    for (int i = 0; i < n_it; ++i) {
+      const float4 p = *reinterpret_cast<const float4*>(partial + (long long)(i0 + i) * D + c * 4);
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    *reinterpret_cast<float4*>(dw + (long long)id * D + c * 4) = acc;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // qkv post-processing, head_dim = 128.  One warp handles one (token, head) slot of q, k or v:
 // lane l owns elements [4l, 4l+4) of the head row; the rotate-half partner (element i+64) lives
@@ -600,6 +652,21 @@ int arb_embedding_fwd(const int* ids, const void* w, void* out, long long N, int
 int arb_embedding_bwd(const int* ids, const void* g, float* dw, long long N, int D, int vocab, cudaStream_t s) {
   if (N <= 0 || (D & 7) || misaligned(g) || misaligned(dw)) return -3;
   embedding_bwd_k<<<grid_for(N * (D / 8), 256), 256, 0, s>>>(ids, (const bf16*)g, dw, N, D, vocab);
+  return int(cudaGetLastError());
+}
+// Deterministic variant: perm[N] = row indices sorted by token id (stable); seg_start / seg_count [vocab] = first
+// sorted position and number of rows of every id; item_start[vocab] = first work item of every id (exclusive
+// prefix sum of ceil(count / R)); item_id[n_items_max] = id of every item, -1 for unused ones; partial =
+// n_items_max * D floats of scratch.
+int arb_embedding_bwd_sorted(const long long* perm, const int* item_id, const int* item_start, const int* seg_start,
+                             const int* seg_count, const void* g, float* dw, float* partial, int n_items_max, int D, int R,
+                             int vocab, cudaStream_t s) {
+  if (n_items_max <= 0 || (D & 7) || R <= 0 || vocab <= 0 || misaligned(g) || misaligned(dw) || misaligned(partial)) return -3;
+  embedding_bwd_sorted_k<<<n_items_max, 128, 0, s>>>(perm, item_id, item_start, seg_start, seg_count, (const bf16*)g, dw, partial,
+                                                     n_items_max, D, R, vocab);
+  int rc = int(cudaGetLastError());
+  if (rc) return rc;
+  embedding_bwd_combine_k<<<vocab, 128, 0, s>>>(item_start, seg_count, partial, dw, D, R);
   return int(cudaGetLastError());
 }
 int arb_add_cols(void* dst, long long ld_dst, const void* src, long long rows, int cols, cudaStream_t s) {

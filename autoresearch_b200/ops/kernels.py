@@ -55,6 +55,7 @@ def lib() -> C.CDLL:
         "arb_qkv_post_bwd": [vp] * 14 + [i64, i32, i32, i32, i32, vp],
         "arb_embedding_fwd": [vp, vp, vp, i64, i32, i32, vp],
         "arb_embedding_bwd": [vp, vp, vp, i64, i32, i32, vp],
+        "arb_embedding_bwd_sorted": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
         "arb_add_cols": [vp, i64, vp, i64, i32, vp],
         "arb_cast_f32_to_bf16": [vp, vp, i64, f32, vp],
         "arb_accum_bf16_into_f32": [vp, vp, i64, vp],
@@ -290,9 +291,51 @@ def embedding_fwd(ids, w):
     return out
 
 
+EMB_BWD_DETERMINISTIC = True   # sorted, atomic-free embedding gradient (False: fp32 atomics)
+EMB_BWD_ROWS_PER_ITEM = 64
+_emb_plan = {}
+
+
+def _embedding_plan(ids, vocab: int):
+    """Sort order and work-item tables of one batch of token ids; cached, since the word-embedding and every
+    value-embedding gradient of a micro-batch use the same ids.  Fixed-size tensors only (no host sync)."""
+    key = (ids.data_ptr(), ids._version, ids.numel(), vocab)
+    hit = _emb_plan.get("plan")
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    R = EMB_BWD_ROWS_PER_ITEM
+    N = ids.numel()
+    flat = ids.reshape(-1).long().clamp(0, vocab - 1)
+    perm = torch.sort(flat, stable=True).indices.contiguous()                     # int64 [N]
+    counts = torch.bincount(flat, minlength=vocab)[:vocab]
+    seg_start = (torch.cumsum(counts, 0) - counts).to(torch.int32)
+    n_it = (counts + R - 1) // R
+    it_end = torch.cumsum(n_it, 0)
+    item_start = (it_end - n_it).to(torch.int32)
+    n_max = N // R + vocab + 1                                                     # upper bound of the item count
+    item = torch.arange(n_max, device=ids.device)
+    item_id = torch.searchsorted(it_end, item, right=True)
+    item_id = torch.where(item < it_end[-1], item_id, torch.full_like(item_id, -1)).to(torch.int32)
+    plan = (perm, item_id.contiguous(), item_start.contiguous(), seg_start.contiguous(), counts.to(torch.int32).contiguous(), n_max)
+    _emb_plan["plan"] = (key, plan)
+    return plan
+
+
 def embedding_bwd(ids, g, dw_f32):
-    _check(lib().arb_embedding_bwd(ids.data_ptr(), g.data_ptr(), dw_f32.data_ptr(), ids.numel(), g.shape[-1],
-                                   dw_f32.shape[0], _stream()), "embedding_bwd")
+    """dw[id] += sum of the rows of g whose token is id."""
+    D, vocab = g.shape[-1], dw_f32.shape[0]
+    if not EMB_BWD_DETERMINISTIC:
+        _check(lib().arb_embedding_bwd(ids.data_ptr(), g.data_ptr(), dw_f32.data_ptr(), ids.numel(), D, vocab, _stream()),
+               "embedding_bwd")
+        return
+    perm, item_id, item_start, seg_start, counts, n_max = _embedding_plan(ids, vocab)
+    scratch = _emb_plan.get("scratch")
+    if scratch is None or scratch.numel() < n_max * D or scratch.device != g.device:
+        scratch = torch.empty(n_max * D, dtype=torch.float32, device=g.device)
+        _emb_plan["scratch"] = scratch
+    _check(lib().arb_embedding_bwd_sorted(perm.data_ptr(), item_id.data_ptr(), item_start.data_ptr(), seg_start.data_ptr(),
+                                          counts.data_ptr(), g.data_ptr(), dw_f32.data_ptr(), scratch.data_ptr(), n_max, D,
+                                          EMB_BWD_ROWS_PER_ITEM, vocab, _stream()), "embedding_bwd_sorted")
 
 
 def softcap_ce_(logits, targets, softcap, dlogits_scale):

@@ -355,8 +355,16 @@ class Trainer:
         name = "optim_state.safetensors" if self.world == 1 else f"optim_state.rank{self.rank}.safetensors"
         save_file(self.opt.state_dict(), str(d / name))
         path = None
+        gather = None
+        if self.ep > 1:
+            def gather(t):      # [E_local, ...] of every rank -> [E, ...]; ranks hold consecutive expert ids
+                out = torch.empty((t.shape[0] * self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+                dist.all_gather_into_tensor(out, t.detach().contiguous(), group=self.group)
+                return out
         if self.rank == 0:
-            path = ckpt.save_checkpoint(self.model, str(d), step=step, trainer_state=state)
+            path = ckpt.save_checkpoint(self.model, str(d), step=step, trainer_state=state, expert_gather=gather)
+        elif gather is not None:
+            ckpt.model_to_engine_tensors(self.model, expert_gather=gather, materialise=False)
         if self.world > 1:
             dist.barrier(group=self.group)
         return path

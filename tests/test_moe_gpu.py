@@ -71,8 +71,28 @@ t = TrainConfig(device_batch_size=4, total_batch_size=8 * cfg.seq_len, max_steps
 tr = Trainer(cfg, t, device=f"cuda:{local}", quiet=True)
 losses = [tr.mean_loss_across_ranks(tr.train_step()) for _ in range(6)]
 torch.cuda.synchronize(); K.check_err_flag()
+ck = {}
+if world > 1:
+    # checkpoint under expert parallelism: one file with the experts of every rank under their global ids
+    tr.tcfg.checkpoint_dir = os.environ["ARB_CKPT"]
+    tr.save(step=None)
+    from autoresearch_b200.ckpt.safetensors_io import load_file
+    sd = load_file(os.path.join(os.environ["ARB_CKPT"], "model.safetensors"))
+    E, El = cfg.moe.n_experts, tr.model.blocks[0].expert_fc.shape[0]
+    rank = dist.get_rank()
+    mine = all(torch.equal(sd[f"h.0.moe.expert.{rank * El + e}.fc.weight"], tr.model.blocks[0].expert_fc[e].detach().cpu())
+               for e in range(El))
+    ok = torch.tensor([int(mine)], device="cuda"); dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    ck = {"experts_in_file": sum(1 for k in sd if k.startswith("h.0.moe.expert.") and k.endswith(".fc.weight")),
+          "every_rank_found_its_experts": bool(ok.item())}
+    # and back: a fresh expert-parallel trainer loads its slice of the file
+    t2 = dataclasses.replace(t, init_weights_path=os.path.join(os.environ["ARB_CKPT"], "model.safetensors"))
+    tr2 = Trainer(cfg, t2, device=f"cuda:{local}", quiet=True)
+    same = torch.equal(tr2.model.blocks[1].expert_proj.detach(), tr.model.blocks[1].expert_proj.detach())
+    ok2 = torch.tensor([int(same)], device="cuda"); dist.all_reduce(ok2, op=dist.ReduceOp.MIN)
+    ck["reload_matches"] = bool(ok2.item())
 if int(os.environ.get("RANK", "0")) == 0:
-    print("RESULT " + json.dumps({"losses": losses, "ep": tr.ep, "experts_local": tr.model.blocks[0].expert_fc.shape[0]}))
+    print("RESULT " + json.dumps({"losses": losses, "ep": tr.ep, "experts_local": tr.model.blocks[0].expert_fc.shape[0], "ckpt": ck}))
 if world > 1:
     dist.destroy_process_group()
 """
@@ -85,7 +105,8 @@ def test_expert_parallel_two_gpus_matches_single_gpu():
     os.makedirs(os.path.dirname(path), exist_ok=True)
     with open(path, "w") as f:
         f.write(WORKER)
-    env = dict(os.environ, ARB_ROOT=root, NCCL_NVLS_ENABLE="0", ARB_DISABLE_MULTIMEM="1")
+    ckdir = os.path.join(root, "gpurun_out", f"_ep_ckpt_{os.getpid()}")
+    env = dict(os.environ, ARB_ROOT=root, NCCL_NVLS_ENABLE="0", ARB_DISABLE_MULTIMEM="1", ARB_CKPT=ckdir)
 
     def run(n, port):
         cmd = ([sys.executable, path] if n == 1 else
@@ -97,7 +118,10 @@ def test_expert_parallel_two_gpus_matches_single_gpu():
 
     one, two = run(1, 0), run(2, 29631)
     os.remove(path)
+    import shutil
+    shutil.rmtree(ckdir, ignore_errors=True)
     assert one["ep"] == 1 and two["ep"] == 2 and two["experts_local"] == 2
+    assert two["ckpt"] == {"experts_in_file": 4, "every_rank_found_its_experts": True, "reload_matches": True}, two["ckpt"]
     for a, b in zip(one["losses"], two["losses"]):
         assert abs(a - b) < 0.05 * abs(a) + 0.02, (one, two)
 
