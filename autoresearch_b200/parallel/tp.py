@@ -265,6 +265,42 @@ def shard_full_model_into(full: GPT, model: GPT, tp_rank: int, tp: int) -> None:
                 mb.ve_gate.copy_(fb.ve_gate[tp_rank * H:(tp_rank + 1) * H])
 
 
+def gather_full_model(model: GPT, tp_group, tp_rank: int, tp: int) -> Optional[GPT]:
+    """Inverse of shard_full_model_into: every rank of the TP group sends its slices (collective), rank 0 of the
+    group returns a full fp32 CPU model, the others None.  Used to write the standard single-file checkpoint."""
+    cfg = model.cfg
+
+    def gather(t: torch.Tensor) -> List[torch.Tensor]:
+        parts = [torch.empty_like(t) for _ in range(tp)]
+        dist.all_gather(parts, t.detach().contiguous(), group=tp_group)
+        return [p.float().cpu() for p in parts]
+
+    full = GPT(cfg, get_backend("oracle", cfg), dtype=torch.float32, device="cpu") if tp_rank == 0 else None
+    with torch.no_grad():
+        if full is not None:
+            for name in ("wte", "lm_head", "resid_lambdas", "x0_lambdas"):
+                getattr(full, name).copy_(getattr(model, name).detach().float().cpu())
+        for i, mb in enumerate(model.blocks):
+            fb = full.blocks[i] if full is not None else None
+            Dl = cfg.d_model // tp
+            qkv = gather(mb.wqkv)
+            wo = gather(mb.wo)
+            if fb is not None:
+                fb.wqkv.copy_(torch.cat([torch.cat([p[j * Dl:(j + 1) * Dl] for p in qkv], 0) for j in range(3)], 0))
+                fb.wo.copy_(torch.cat(wo, 1))
+            if mb.wfc is not None:
+                fc, dn = gather(mb.wfc), gather(mb.wdn)
+                if fb is not None:
+                    fb.wfc.copy_(torch.cat(fc, 0))
+                    fb.wdn.copy_(torch.cat(dn, 1))
+            if mb.ve is not None:
+                ve, gate = gather(mb.ve), gather(mb.ve_gate)
+                if fb is not None:
+                    fb.ve.copy_(torch.cat(ve, 1))
+                    fb.ve_gate.copy_(torch.cat(gate, 0))
+    return full
+
+
 REPLICATED_KINDS = ("adamw_emb", "adamw_head", "adamw_lr", "adamw_l0", "adamw_router")
 
 
@@ -361,6 +397,19 @@ class TPTrainer:
         self.step += 1
         return loss_acc
 
+    def save(self, step: Optional[int] = None) -> Optional[str]:
+        """One standard checkpoint file (full, unsharded tensors), written by rank 0; the TP group of the first
+        DP replica gathers its shards (collective within that group)."""
+        from ..ckpt import checkpoint as ckpt
+        path = None
+        if self.dp_idx == 0:
+            full = gather_full_model(self.model, self.tp_group, self.tp_rank, self.tp)
+            if full is not None:
+                path = ckpt.save_checkpoint(full, self.tcfg.checkpoint_dir, step=step,
+                                            trainer_state=dict(step=self.step, wsd=self.wsd.state_dict(), tp=self.tp, dp=self.dp))
+        dist.barrier()
+        return path
+
     def global_loss(self, loss: torch.Tensor) -> float:
         """Each rank holds the loss of its token shard (already divided by the full micro-batch
         token count): sum over the TP group, mean over DP replicas."""
@@ -392,4 +441,8 @@ class TPTrainer:
                     left = (t.max_steps - self.step) if t.max_steps else -1
                     print(f"step {step:>5} | loss {ema / (1 - 0.9 ** n):.4f} | lr {lrm:.3f} | dt {dt:.3f}s | "
                           f"tok/s {int(tokens / dt)} | mfu 0.0% | vram 0MB | steps_left {left}", flush=True)
+        if t.checkpoint_dir and not t.synthetic_data:
+            p = self.save()
+            if self.rank == 0 and not self.quiet:
+                print(f"[checkpoint] saved {p}", flush=True)
         dist.barrier()

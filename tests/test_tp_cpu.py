@@ -18,9 +18,26 @@ t = TrainConfig(device_batch_size=2, total_batch_size=4 * 128, max_steps=10, coo
                 synthetic_kind="zipf", impl="oracle", cooldown_trigger_file="")
 t.init_scheme = "normal"
 tr = TPTrainer(cfg, t, tp=2, device="cpu", quiet=True)
-ls = [tr.global_loss(tr.train_step()) for _ in range(4)]
+# the sharded initial weights gather back into exactly the seed-initialised full model, and save() writes it
+from autoresearch_b200.parallel.tp import gather_full_model
+from autoresearch_b200.models.gpt import GPT
+from autoresearch_b200.models.init import init_weights
+from autoresearch_b200.ops.backend import get_backend
+full = gather_full_model(tr.model, tr.tp_group, tr.tp_rank, 2)
+same = None
 if dist.get_rank() == 0:
-    print("RESULT " + json.dumps({"losses": ls, "wqkv": list(tr.model.blocks[0].wqkv.shape), "bytes": tr.backend.tp.bytes}))
+    ref = GPT(cfg, get_backend("oracle", cfg), dtype=torch.float32, device="cpu")
+    init_weights(ref, seed=t.seed, scheme="normal")
+    same = all(torch.equal(a, b) for a, b in zip(full.state_dict().values(), ref.state_dict().values()))
+ls = [tr.global_loss(tr.train_step()) for _ in range(4)]
+tr.tcfg.checkpoint_dir = os.environ["ARB_CKPT"]
+path = tr.save()
+if dist.get_rank() == 0:
+    from autoresearch_b200.ckpt.safetensors_io import load_file
+    sd = load_file(path)
+    print("RESULT " + json.dumps({"losses": ls, "wqkv": list(tr.model.blocks[0].wqkv.shape), "bytes": tr.backend.tp.bytes,
+                                  "gather_exact": same, "ckpt_q_shape": list(sd["h.0.attn.c_q.weight"].shape),
+                                  "ckpt_tensors": len(sd)}))
 dist.destroy_process_group()
 """
 
@@ -66,10 +83,13 @@ def test_tp2_matches_single_process(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29657", str(script)],
-                       env=dict(os.environ, ARB_ROOT=root), capture_output=True, text=True, timeout=300)
+                       env=dict(os.environ, ARB_ROOT=root, ARB_CKPT=str(tmp_path / "ck")), capture_output=True, text=True,
+                       timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
     assert res["wqkv"] == [3 * cfg.d_model // 2, cfg.d_model] and res["bytes"] > 0
+    assert res["gather_exact"] is True                       # shards gather back into the full model
+    assert res["ckpt_q_shape"] == [cfg.d_model, cfg.d_model] and res["ckpt_tensors"] > 10   # unsharded checkpoint
     # the forward pass is exact; after an update the runs differ slightly because Muon
     # orthogonalises each rank's shard of a matrix instead of the whole matrix
     assert abs(ref[0] - res["losses"][0]) < 1e-4
