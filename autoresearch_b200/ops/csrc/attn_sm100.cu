@@ -193,12 +193,11 @@ attn_fwd_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       // masks are needed only on tiles that touch the diagonal, the window edge or the tail
       const bool need_mask = (n0 + 127 > m0) || (p.window < p.T && n0 < m0 + 127 - p.window) || (n0 + 127 >= p.T);
       if (need_mask) {
+        // the visible keys of a row are one interval [lo, hi] of column indices: one unsigned compare per element
+        const int lo = (row < p.T) ? row - p.window - n0 : 128;     // rows past the end see nothing
+        const unsigned span = (row < p.T) ? unsigned(p.window) : 0u;  // hi - lo = min(row, T-1) - row + window
 #pragma unroll
-        for (int j = 0; j < 128; ++j) {
-          const int key = n0 + j;
-          const bool vis = (key <= row) && (key >= row - p.window) && (key < p.T);
-          sc[j] = vis ? sc[j] : -INFINITY;
-        }
+        for (int j = 0; j < 128; ++j) sc[j] = (unsigned(j - lo) <= span) ? sc[j] : -INFINITY;
       }
       // eight independent chains: one chain of 127 dependent max operations cost 400 clk per tile
 #ifndef ARB_FWD_MAX_CHAINS

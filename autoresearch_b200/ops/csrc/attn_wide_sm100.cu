@@ -242,12 +242,12 @@ attn_bwd_dq_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                                (m0 + 127 >= p.T);
         exp2_64<true>(s0, s1, c, lse2, nullptr, pr);
         if (need_mask) {
+          // the visible keys of a row are one interval [lo, hi] of column indices: one unsigned compare per element
+          const int lo = row - p.window - n0;
+          const unsigned span = (row < p.T) ? unsigned(min(row, p.T - 1) - n0 - lo) : 0u;
+          const int lo_eff = (row < p.T) ? lo : 64;          // rows past the end see nothing
 #pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            const int key = n0 + j;
-            const bool vis = (key <= row) && (key >= row - p.window) && (key < p.T) && (row < p.T);
-            pr[j] = vis ? pr[j] : 0.f;
-          }
+          for (int j = 0; j < 64; ++j) pr[j] = (unsigned(j - lo_eff) <= span) ? pr[j] : 0.f;
         }
       }
       // ---- phase B ----
@@ -472,12 +472,11 @@ attn_bwd_dkv_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                                (n0 + 127 >= p.T);
         exp2_64<false>(s0, s1, c, 0.f, cl, pr);
         if (need_mask) {
+          // the queries that see a key are one interval of column indices: key <= q <= min(key + window, T - 1)
+          const int lo = (key < p.T) ? key - q0 : 64;
+          const unsigned span = (key < p.T) ? unsigned(min((long long)key + p.window, (long long)p.T - 1) - key) : 0u;
 #pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            const int qi = q0 + j;
-            const bool vis = (key <= qi) && (key >= qi - p.window) && (qi < p.T) && (key < p.T);
-            pr[j] = vis ? pr[j] : 0.f;
-          }
+          for (int j = 0; j < 64; ++j) pr[j] = (unsigned(j - lo) <= span) ? pr[j] : 0.f;
         }
         uint32_t pk[32];
 #pragma unroll
