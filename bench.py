@@ -18,7 +18,7 @@ import sys
 import time
 
 BASELINE_TOK_S = 52643.0  # reference, 1x H100 SXM, results/480m_30pct_cooldown/train.log
-PUBLISHED = {"phase2": 52643.0, "phase1": 349500.0}   # reference tokens/s on 1x H100 SXM
+PUBLISHED = {"phase2": 52643.0, "phase1": 349500.0}   # the reference's published tokens/s on 1x H100 SXM
 
 
 def main() -> int:

@@ -41,8 +41,8 @@ if world > 1:
 def _run(nproc, comm, port):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, ARB_ROOT=root, ARB_COMM=comm, NCCL_NVLS_ENABLE="0")
-    path = os.path.join(root, "gpurun_out", f"_dp_worker_{os.getpid()}.py")
-    os.makedirs(os.path.dirname(path), exist_ok=True)
+    import tempfile
+    path = os.path.join(tempfile.mkdtemp(prefix="arb_dp_"), "worker.py")
     with open(path, "w") as f:
         f.write(WORKER)
     if nproc == 1:

@@ -101,11 +101,11 @@ if world > 1:
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_expert_parallel_two_gpus_matches_single_gpu():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    path = os.path.join(root, "gpurun_out", f"_ep_worker_{os.getpid()}.py")
-    os.makedirs(os.path.dirname(path), exist_ok=True)
+    import tempfile
+    path = os.path.join(tempfile.mkdtemp(prefix="arb_ep_"), "worker.py")
     with open(path, "w") as f:
         f.write(WORKER)
-    ckdir = os.path.join(root, "gpurun_out", f"_ep_ckpt_{os.getpid()}")
+    ckdir = tempfile.mkdtemp(prefix="arb_ep_ckpt_")
     env = dict(os.environ, ARB_ROOT=root, NCCL_NVLS_ENABLE="0", ARB_DISABLE_MULTIMEM="1", ARB_CKPT=ckdir)
 
     def run(n, port):

@@ -44,8 +44,8 @@ if world > 1:
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tp2_fused_and_library_follow_single_gpu():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    path = os.path.join(root, "gpurun_out", f"_tp_worker_{os.getpid()}.py")
-    os.makedirs(os.path.dirname(path), exist_ok=True)
+    import tempfile
+    path = os.path.join(tempfile.mkdtemp(prefix="arb_tp_"), "worker.py")
     with open(path, "w") as f:
         f.write(WORKER)
 
