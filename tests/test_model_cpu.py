@@ -269,3 +269,38 @@ def test_data_parallel_gloo_matches_single_process(tmp_path):
     assert res["same"] and res["owners"] == [0, 1]
     for a, b in zip(ref, res["losses"]):
         assert abs(a - b) < 1e-3, (ref, res)
+
+
+def test_fused_gather_plan_covers_every_remote_parameter():
+    """The parameter all-gather plan of the peer-memory path: a dense weight of another rank is either pulled by
+    its first GEMM or lies inside a range that is copied at once; ranges are 16-byte aligned and stay inside the
+    owner's shard."""
+    from types import SimpleNamespace
+    from autoresearch_b200.config import model_preset
+    from autoresearch_b200.models.gpt import GPT
+    from autoresearch_b200.parallel.fused_dp import FusedComm
+    from autoresearch_b200.parallel.layout import ParamLayout
+    cfg = model_preset("tiny")
+    model = GPT(cfg, dtype=torch.bfloat16)
+    lay = ParamLayout(model.named_matrix_groups(), world=3, rank=1)
+    me = SimpleNamespace(world=3, rank=1, fuse_into_gemm=True, GEMM_OPERANDS=FusedComm.GEMM_OPERANDS)
+    gemm_atoms, ranges = FusedComm._plan_gather(me, lay)
+    es = 2
+    assert gemm_atoms and ranges
+    pulled = {a.name for a, _ in gemm_atoms}
+    assert all(n.endswith(FusedComm.GEMM_OPERANDS) for n in pulled)
+    for b0, b1, r in ranges:
+        lo, hi = lay.shard_range(r)
+        assert r != 1 and b0 % 16 == 0 and b1 % 16 == 0 and lo * es <= b0 < b1 <= hi * es
+    for a in lay.atoms:
+        if a.owner == 1:
+            assert a.name not in pulled
+            continue
+        if a.name in pulled:
+            continue
+        a0, a1 = a.offset * es, (a.offset + a.numel) * es
+        assert any(b0 <= a0 and a1 <= b1 and r == a.owner for b0, b1, r in ranges), a.name
+    # without the GEMM fusion everything travels in ranges
+    me.fuse_into_gemm = False
+    g2, r2 = FusedComm._plan_gather(me, lay)
+    assert not g2 and sum(b1 - b0 for b0, b1, _ in r2) >= sum(a.numel * es for a in lay.atoms if a.owner != 1)
