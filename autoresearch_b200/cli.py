@@ -19,7 +19,7 @@ import os
 import sys
 from typing import List, Optional
 
-from .config import PRESETS, ParallelConfig, ScheduleConfig, TrainConfig, model_preset
+from .config import PRESETS, ScheduleConfig, TrainConfig, model_preset
 
 
 def parse_args(argv: List[str], env=None):

@@ -9,10 +9,9 @@ names, defaults and precedence of the recipe tier are kept.
 from __future__ import annotations
 
 import dataclasses
-import math
 import os
 from dataclasses import dataclass, field
-from typing import Optional, Sequence, Tuple
+from typing import Optional, Tuple
 
 
 @dataclass

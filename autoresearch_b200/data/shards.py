@@ -10,7 +10,6 @@ The stdin stream is rows of SEQ+1 little-endian u16 without framing
 from __future__ import annotations
 
 import ctypes as C
-import os
 from pathlib import Path
 from typing import List, Optional
 

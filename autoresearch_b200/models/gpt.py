@@ -13,8 +13,7 @@ slices of `resid_lambdas` / `x0_lambdas` of its own layers (brain/src/train.rs:1
 """
 from __future__ import annotations
 
-import math
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn

@@ -15,7 +15,6 @@ from __future__ import annotations
 import ctypes as C
 
 import torch
-import torch.nn.functional as F
 
 from ..ops import kernels as K
 from ..ops import reference as R

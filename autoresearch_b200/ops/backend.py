@@ -13,8 +13,6 @@ brain/src/forward.rs and brain/src/backward.rs).
 """
 from __future__ import annotations
 
-import math
-from typing import Optional
 
 import torch
 import torch.nn.functional as F

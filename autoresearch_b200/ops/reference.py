@@ -10,7 +10,6 @@ original/train.py:42-290.
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
 
 import torch
 import torch.nn.functional as F

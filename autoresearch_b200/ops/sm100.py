@@ -23,7 +23,6 @@ from typing import Optional
 import torch
 
 from . import kernels as K
-from . import reference as R
 from .backend import OracleBackend
 
 

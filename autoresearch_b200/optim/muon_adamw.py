@@ -16,12 +16,12 @@ brain/src/optim.rs:253-264; fp32 is a strict refinement).
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional
+from typing import Dict
 
 import torch
 
 from ..config import ScheduleConfig
-from ..parallel.layout import Group, ParamLayout
+from ..parallel.layout import ParamLayout
 from . import schedule as S
 
 POLAR_EXPRESS = (

@@ -17,7 +17,7 @@ rank = dp_index * n_stages + stage.
 from __future__ import annotations
 
 import time
-from typing import List, Optional, Tuple
+from typing import List, Tuple
 
 import torch
 import torch.distributed as dist

@@ -13,7 +13,6 @@ import argparse
 import json
 from pathlib import Path
 
-import numpy as np
 import torch
 
 from ..ckpt.checkpoint import load_weights, model_to_engine_tensors

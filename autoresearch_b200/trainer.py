@@ -13,7 +13,6 @@ from __future__ import annotations
 import json
 import math
 import os
-import sys
 import time
 from pathlib import Path
 from typing import Optional

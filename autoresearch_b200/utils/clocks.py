@@ -7,7 +7,6 @@ from __future__ import annotations
 
 import statistics
 import threading
-import time
 from typing import List, Optional
 
 _REASONS = {
