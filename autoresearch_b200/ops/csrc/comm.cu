@@ -74,16 +74,26 @@ __global__ void __launch_bounds__(256) reduce_scatter_mc_k(const void* mc, long 
   }
 }
 
+// dst[i] = src[i] for i = first, first + stride, ... < n (16-byte units), four loads in flight per thread
+__device__ __forceinline__ void copy16_unrolled(uint4* __restrict__ dst, const uint4* __restrict__ src, long long n, long long first,
+                                                long long stride) {
+  long long i = first;
+  for (; i + 3 * stride < n; i += 4 * stride) {
+    const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+    dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+  }
+  for (; i < n; i += stride) dst[i] = src[i];
+}
+
 // dst_local[p-th shard] = peer_p[p-th shard] for every p != rank (16-byte units)
 __global__ void __launch_bounds__(256) all_gather_pull_k(PeerPtrs peers, int world, int rank, uint4* __restrict__ local,
                                                          long long shard16) {
-  const long long total = shard16 * (world - 1);
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int q = int(i / shard16);
-    const long long j = i - (long long)q * shard16;
+  // peer by peer (every rank starts with a different one), four independent 16-byte loads in flight per thread
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int q = 0; q < world - 1; ++q) {
     const int pr = (rank + 1 + q) % world;
-    const long long idx = (long long)pr * shard16 + j;
-    local[idx] = reinterpret_cast<const uint4*>(peers.p[pr])[idx];
+    copy16_unrolled(local + (long long)pr * shard16, reinterpret_cast<const uint4*>(peers.p[pr]) + (long long)pr * shard16, shard16,
+                    (long long)blockIdx.x * blockDim.x + threadIdx.x, stride);
   }
 }
 
@@ -96,12 +106,10 @@ struct PullRanges {
   int n;
 };
 __global__ void pull_ranges_k(const __grid_constant__ PullRanges r) {
-  const long long total = r.end16[r.n - 1];
-  int k = 0;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    while (i >= r.end16[k]) ++k;                       // indices only grow inside a thread
-    const long long j = i - (k ? r.end16[k - 1] : 0);
-    r.dst[k][j] = r.src[k][j];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int k = 0; k < r.n; ++k) {
+    const long long n = r.end16[k] - (k ? r.end16[k - 1] : 0);
+    copy16_unrolled(r.dst[k], r.src[k], n, (long long)blockIdx.x * blockDim.x + threadIdx.x, stride);
   }
 }
 
