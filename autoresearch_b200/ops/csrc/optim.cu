@@ -157,6 +157,40 @@ __device__ __forceinline__ void load_grad8(const GradPeers& g, long long idx, fl
   for (int j = 0; j < 8; ++j) o[j] *= g.scale;
 }
 
+// Two chunks at once: their peer (or multimem) loads are issued back to back, so that a thread has several NVLink
+// loads in flight.  With one chunk per iteration the fused kernels reached 160 GB/s on two GPUs, where every
+// thread has a single peer to read from.
+__device__ __forceinline__ void load_grad8x2(const GradPeers& g, long long i0, long long i1, float (&o0)[8], float (&o1)[8]) {
+  if (g.mc) {
+    uint32_t r[8];
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "l"(g.mc + i0));
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "l"(g.mc + i1));
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = unpack_bf16(r[k]), b = unpack_bf16(r[4 + k]);
+      o0[2 * k] = a.x; o0[2 * k + 1] = a.y; o1[2 * k] = b.x; o1[2 * k + 1] = b.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o0[j] = 0.f; o1[j] = 0.f; }
+#pragma unroll 2
+    for (int q = 0; q < g.world; ++q) {
+      const int pr = (g.rank + q) % g.world;
+      const uint4 u = *reinterpret_cast<const uint4*>(g.p[pr] + i0), w = *reinterpret_cast<const uint4*>(g.p[pr] + i1);
+      const uint32_t uu[4] = {u.x, u.y, u.z, u.w}, ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = unpack_bf16(uu[k]), b = unpack_bf16(ww[k]);
+        o0[2 * k] += a.x; o0[2 * k + 1] += a.y; o1[2 * k] += b.x; o1[2 * k + 1] += b.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { o0[j] *= g.scale; o1[j] *= g.scale; }
+}
+
 // grid (blocks_per_mat, n_mat); elements of matrix `mat` sit at bucket offset `offset + mat*per_mat`
 __global__ void __launch_bounds__(256) muon_nesterov_rs_k(float* __restrict__ buf, GradPeers gp, long long offset,
                                                           __nv_bfloat16* __restrict__ u, float* __restrict__ sumsq,
@@ -165,9 +199,7 @@ __global__ void __launch_bounds__(256) muon_nesterov_rs_k(float* __restrict__ bu
   const int mat = blockIdx.y;
   const long long base = (long long)mat * per_mat;
   float acc = 0.f;
-  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < per_mat; i += (long long)gridDim.x * blockDim.x * 8) {
-    float g[8];
-    load_grad8(gp, offset + base + i, g);
+  auto update8 = [&](long long i, const float (&g)[8]) {
     float4 b0 = *reinterpret_cast<const float4*>(buf + base + i), b1 = *reinterpret_cast<const float4*>(buf + base + i + 4);
     float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
     float uu[8];
@@ -182,6 +214,19 @@ __global__ void __launch_bounds__(256) muon_nesterov_rs_k(float* __restrict__ bu
     uint4 o;
     o.x = pack_bf16(uu[0], uu[1]); o.y = pack_bf16(uu[2], uu[3]); o.z = pack_bf16(uu[4], uu[5]); o.w = pack_bf16(uu[6], uu[7]);
     *reinterpret_cast<uint4*>(u + base + i) = o;
+  };
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  for (; i + stride < per_mat; i += 2 * stride) {
+    float g0[8], g1[8];
+    load_grad8x2(gp, offset + base + i, offset + base + i + stride, g0, g1);
+    update8(i, g0);
+    update8(i + stride, g1);
+  }
+  if (i < per_mat) {
+    float g[8];
+    load_grad8(gp, offset + base + i, g);
+    update8(i, g);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -194,28 +239,50 @@ __global__ void __launch_bounds__(256) muon_nesterov_rs_k(float* __restrict__ bu
   }
 }
 
+__device__ __forceinline__ void adamw8(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                                       __nv_bfloat16* __restrict__ shadow, long long i, const float (&g)[8], float lr, float b1,
+                                       float b2, float eps, float wd, float bc1, float bc2) {
+  float4 pa = *reinterpret_cast<float4*>(p + i), pb = *reinterpret_cast<float4*>(p + i + 4);
+  float4 ma = *reinterpret_cast<float4*>(m + i), mb = *reinterpret_cast<float4*>(m + i + 4);
+  float4 va = *reinterpret_cast<float4*>(v + i), vb = *reinterpret_cast<float4*>(v + i + 4);
+  float pp[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+  float mm[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+  float vv[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    pp[j] -= lr * wd * pp[j];
+    mm[j] = b1 * mm[j] + (1.f - b1) * g[j];
+    vv[j] = b2 * vv[j] + (1.f - b2) * g[j] * g[j];
+    pp[j] -= lr * (mm[j] / bc1) / (sqrtf(vv[j] / bc2) + eps);
+  }
+  *reinterpret_cast<float4*>(p + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+  *reinterpret_cast<float4*>(p + i + 4) = make_float4(pp[4], pp[5], pp[6], pp[7]);
+  *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+  *reinterpret_cast<float4*>(m + i + 4) = make_float4(mm[4], mm[5], mm[6], mm[7]);
+  *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+  *reinterpret_cast<float4*>(v + i + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+  if (shadow) {
+    uint4 u;
+    u.x = pack_bf16(pp[0], pp[1]); u.y = pack_bf16(pp[2], pp[3]); u.z = pack_bf16(pp[4], pp[5]); u.w = pack_bf16(pp[6], pp[7]);
+    *reinterpret_cast<uint4*>(shadow + i) = u;
+  }
+}
+
 __global__ void __launch_bounds__(256) adamw_rs_k(float* __restrict__ p, GradPeers gp, long long offset, float* __restrict__ m,
                                                   float* __restrict__ v, __nv_bfloat16* __restrict__ shadow, long long n, float lr,
                                                   float b1, float b2, float eps, float wd, float bc1, float bc2) {
-  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += (long long)gridDim.x * blockDim.x * 8) {
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  for (; i + stride < n; i += 2 * stride) {
+    float g0[8], g1[8];
+    load_grad8x2(gp, offset + i, offset + i + stride, g0, g1);
+    adamw8(p, m, v, shadow, i, g0, lr, b1, b2, eps, wd, bc1, bc2);
+    adamw8(p, m, v, shadow, i + stride, g1, lr, b1, b2, eps, wd, bc1, bc2);
+  }
+  if (i < n) {
     float g[8];
     load_grad8(gp, offset + i, g);
-    float o[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float pi = p[i + j], mi = m[i + j], vi = v[i + j];
-      pi -= lr * wd * pi;
-      mi = b1 * mi + (1.f - b1) * g[j];
-      vi = b2 * vi + (1.f - b2) * g[j] * g[j];
-      pi -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
-      p[i + j] = pi; m[i + j] = mi; v[i + j] = vi;
-      o[j] = pi;
-    }
-    if (shadow) {
-      uint4 u;
-      u.x = pack_bf16(o[0], o[1]); u.y = pack_bf16(o[2], o[3]); u.z = pack_bf16(o[4], o[5]); u.w = pack_bf16(o[6], o[7]);
-      *reinterpret_cast<uint4*>(shadow + i) = u;
-    }
+    adamw8(p, m, v, shadow, i, g, lr, b1, b2, eps, wd, bc1, bc2);
   }
 }
 
