@@ -782,24 +782,32 @@ attn_bwd_dkv_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
-// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per (token, head)
+// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per token, a half-warp per head (16-byte loads, two heads
+// per iteration), the token arithmetic done once per warp
 __global__ void __launch_bounds__(256) attn_delta_k(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                                     float* __restrict__ delta, int B, int T, int H, long long ldo, long long lddo) {
-  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const long long bt = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (wid >= (long long)B * T * H) return;
-  const int h = int(wid % H);
-  const long long bt = wid / H;
-  const uint2 a = *reinterpret_cast<const uint2*>(o + bt * ldo + h * HD + lane * 4);
-  const uint2 g = *reinterpret_cast<const uint2*>(d_o + bt * lddo + h * HD + lane * 4);
-  float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), g0 = unpack_bf16(g.x), g1 = unpack_bf16(g.y);
-  float acc = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+  if (bt >= (long long)B * T) return;
+  const int t = int(bt % T);
+  const int b = int(bt / T);
+  const int sub = lane >> 4, l16 = lane & 15;
+  for (int h0 = 0; h0 < H; h0 += 2) {
+    const int h = h0 + sub;
+    float acc = 0.f;
+    if (h < H) {
+      const uint4 a = *reinterpret_cast<const uint4*>(o + bt * ldo + h * HD + l16 * 8);
+      const uint4 g = *reinterpret_cast<const uint4*>(d_o + bt * lddo + h * HD + l16 * 8);
+      const uint32_t aa[4] = {a.x, a.y, a.z, a.w}, gg[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) {
-    const int t = int(bt % T);
-    const int b = int(bt / T);
-    delta[((long long)b * H + h) * T + t] = acc;
+      for (int k = 0; k < 4; ++k) {
+        const float2 x = unpack_bf16(aa[k]), y = unpack_bf16(gg[k]);
+        acc += x.x * y.x + x.y * y.y;
+      }
+    }
+#pragma unroll
+    for (int s = 8; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (l16 == 0 && h < H) delta[((long long)b * H + h) * T + t] = acc;
   }
 }
 
@@ -867,7 +875,7 @@ extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const v
   if (bad_ptr(q) || bad_ptr(k) || bad_ptr(v) || bad_ptr(o) || bad_ptr(d_o) || bad_ptr(dq) || bad_ptr(dk) || bad_ptr(dv)) return -4;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8) || (lddo % 8) || (lddq % 8) || (lddk % 8) || (lddv % 8)) return -4;
   int r;
-  attn_delta_k<<<unsigned(((long long)B * T * H + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, T, H, ldo, lddo);
+  attn_delta_k<<<unsigned(((long long)B * T + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, T, H, ldo, lddo);
   if ((r = int(cudaGetLastError()))) return r;
   AttnArgs a{};
   a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
