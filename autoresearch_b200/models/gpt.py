@@ -18,6 +18,7 @@ from typing import Optional, Tuple
 import torch
 import torch.nn as nn
 
+from ..utils.timing import nvtx_range
 from ..config import ModelConfig
 from ..ops import reference as R
 
@@ -104,15 +105,16 @@ class GPT(nn.Module):
         aux_total = None
         for bi, blk in enumerate(self.blocks):
             l = blk.layer
-            x, xn = be.resid_scale_norm(x, x0, self.resid_lambdas, self.x0_lambdas, bi)
-            a = be.attention_block(xn, blk, ids_flat, B, T, cfg, self.rope_cos, self.rope_sin,
-                                   cfg.window(l))
-            x, xn = be.proj_add_norm(a, blk.wo, x)
-            if blk.router is not None:
-                x, aux = be.moe_mlp_add(xn, x, blk, cfg.moe)
-                aux_total = aux if aux_total is None else aux_total + aux
-            else:
-                x = be.mlp_add(xn, blk.wfc, blk.wdn, x)
+            with nvtx_range(f"layer {l}"):
+                x, xn = be.resid_scale_norm(x, x0, self.resid_lambdas, self.x0_lambdas, bi)
+                a = be.attention_block(xn, blk, ids_flat, B, T, cfg, self.rope_cos, self.rope_sin,
+                                       cfg.window(l))
+                x, xn = be.proj_add_norm(a, blk.wo, x)
+                if blk.router is not None:
+                    x, aux = be.moe_mlp_add(xn, x, blk, cfg.moe)
+                    aux_total = aux if aux_total is None else aux_total + aux
+                else:
+                    x = be.mlp_add(xn, blk.wfc, blk.wdn, x)
         self.aux_loss = aux_total
         return x
 

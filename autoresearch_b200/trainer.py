@@ -32,7 +32,7 @@ from .optim.muon_adamw import MuonAdamW
 from .optim.schedule import WSDState, lr_multiplier, warmup_multiplier
 from .parallel.dp import LibraryComm, LocalComm
 from .parallel.layout import ParamLayout
-from .utils.timing import PhaseTimer, measured_peak_flops, vram_mb
+from .utils.timing import PhaseTimer, measured_peak_flops, nvtx_range, vram_mb
 
 
 def _log(msg: str, rank: int = 0):
@@ -211,8 +211,10 @@ class Trainer:
             if batch is None:
                 return None
             ids, tgt = batch
-            scaled, per_tok = self.model(ids, tgt, grad_scale=grad_scale)
-            scaled.backward()
+            with nvtx_range(f"forward micro {micro}"):
+                scaled, per_tok = self.model(ids, tgt, grad_scale=grad_scale)
+            with nvtx_range(f"backward micro {micro}"):
+                scaled.backward()
             self.layout.accumulate_autograd_grads()
             if self.expert_layout is not None:
                 self.expert_layout.accumulate_autograd_grads()
@@ -224,14 +226,17 @@ class Trainer:
             self.timer.mark("end")
             self.step += 1
             return self._loss_acc
-        self.comm.reduce_scatter_grads(self.layout)
+        with nvtx_range("gradient exchange"):
+            self.comm.reduce_scatter_grads(self.layout)
         progress = self.wsd.progress(self.step)
         wm = warmup_multiplier(self.step + 1, self.wsd.warmup_steps)
         gs = self.comm.grad_source(self.layout) if hasattr(self.comm, "grad_source") else None
-        self.opt.step(self.step + 1, progress, wm, grad_source=gs)
-        if self.expert_opt is not None:
-            self.expert_opt.step(self.step + 1, progress, wm)
-        self.comm.all_gather_params(self.layout)
+        with nvtx_range("optimizer"):
+            self.opt.step(self.step + 1, progress, wm, grad_source=gs)
+            if self.expert_opt is not None:
+                self.expert_opt.step(self.step + 1, progress, wm)
+        with nvtx_range("parameter exchange"):
+            self.comm.all_gather_params(self.layout)
         self.timer.mark("opt_end")
         self.timer.mark("end")
         self.step += 1

@@ -54,3 +54,25 @@ def vram_mb() -> float:
         free, total = torch.cuda.mem_get_info()
         return (total - free) / (1024.0 * 1024.0)
     return 0.0
+
+
+# ---- NVTX ranges (opt-in: ARB_NVTX=1) ----------------------------------------------------------------
+# Phase and layer ranges for timeline tools (role of the phase events of brain/src/train.rs:867-870, which this
+# package keeps as PhaseTimer; the reference has no NVTX).  Off by default: a range push/pop costs host time in the
+# launch path.
+import contextlib as _contextlib
+import os as _os
+
+NVTX = _os.environ.get("ARB_NVTX", "0") == "1"
+
+
+@_contextlib.contextmanager
+def nvtx_range(name: str):
+    if NVTX and torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield

@@ -188,3 +188,61 @@ def test_embedding_backward_sorted_is_exact_and_deterministic():
     finally:
         K.EMB_BWD_DETERMINISTIC = True
     assert (dw2 - outs[0]).abs().max().item() < 2e-3
+
+
+def test_bounded_device_wait_expires_into_the_error_word_and_the_context_stays_usable():
+    """A peer barrier whose partner never arrives (a flag that nothing sets): the kernel gives up after its wait
+    limit, returns normally and leaves ERR_COMM_TIMEOUT in the status word; the next kernels run as usual."""
+    import ctypes as C
+    import time
+    from autoresearch_b200.ops import kernels as K
+    K.check_err_flag()
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")
+    absent_peer = torch.zeros(64, dtype=torch.int32, device="cuda")       # stands in for a rank that never shows up
+    ptrs = (C.c_void_p * 2)(mine.data_ptr(), absent_peer.data_ptr())
+    t0 = time.time()
+    rc = K.lib().arb_peer_barrier(ptrs, 2, 0, 1, K.err_flag().data_ptr(), K._stream())
+    assert rc == 0
+    torch.cuda.synchronize()                                              # returns: the wait is bounded (2 s of device time)
+    assert 1.0 < time.time() - t0 < 20.0
+    assert int(absent_peer[0].item()) == 1                                # this rank did announce itself
+    with pytest.raises(K.KernelError, match="peer barrier wait timed out"):
+        K.check_err_flag()
+    K.check_err_flag()                                                    # the word was cleared by the read above
+    x = _bf(64, 512)
+    _close(K.rmsnorm_fwd(x, EPS), torch.nn.functional.rms_norm(x.float(), (512,), eps=EPS))
+    torch.cuda.synchronize()
+    K.check_err_flag()
+
+
+def test_kernels_are_bitwise_reproducible_and_stay_inside_their_outputs():
+    """Run twice -> identical bits (no atomics on these paths), and canary rows around the outputs stay untouched."""
+    from autoresearch_b200.ops import kernels as K, sm100
+    torch.manual_seed(21)
+    # GEMM into the middle of a larger buffer
+    a, w = _bf(300, 256), _bf(200, 256)
+    buf = torch.full((300 + 16, 200), 7.0, device="cuda", dtype=torch.bfloat16)
+    outs = []
+    for _ in range(2):
+        buf.fill_(7.0)
+        K.gemm(a, w, out=buf[8:308])
+        outs.append(buf.clone())
+    assert torch.equal(outs[0], outs[1])
+    assert torch.all(outs[0][:8] == 7.0) and torch.all(outs[0][308:] == 7.0)
+    # attention forward + backward (deterministic two-kernel backward)
+    B, T, H = 1, 640, 2
+    qkv = _bf(B * T, 3 * H * 128).requires_grad_(True)
+    g = _bf(B * T, H * 128)
+    res = []
+    for _ in range(2):
+        out = sm100.AttentionFn.apply(qkv, B, T, H, 200)
+        out.backward(g)
+        res.append((out.detach().clone(), qkv.grad.clone()))
+        qkv.grad = None
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    # fused norm kernels next to canaries
+    x = _bf(37, 1024)
+    y1, y2 = K.rmsnorm_fwd(x, EPS), K.rmsnorm_fwd(x, EPS)
+    assert torch.equal(y1, y2)
+    torch.cuda.synchronize()
+    K.check_err_flag()
