@@ -136,7 +136,10 @@ class Trainer:
     def _make_comm(self):
         if self.world == 1:
             return LocalComm()
-        if self.tcfg.parallel.comm == "fused" and self.device.type == "cuda":
+        # the peer-memory path hands gradients to the sm_100a optimizer kernels and parameters to the sm_100a GEMMs;
+        # every other backend (fp32 oracle, library baseline) uses the library collectives
+        if (self.tcfg.parallel.comm == "fused" and self.device.type == "cuda"
+                and type(self.backend).__name__ == "Sm100Backend"):
             from .parallel.fused_dp import FusedComm
             return FusedComm(self.group, self.device)
         bucket = torch.bfloat16 if self.device.type == "cuda" else None
