@@ -22,12 +22,60 @@ import torch
 from ..ops import build as B
 
 
+def fwd2(a):
+    """Cycles per key tile (both query tiles) of the MMA-issuing thread and of one warp of each softmax group."""
+    T, H = a.T, a.H
+    W = a.window if a.window is not None else T
+    with tempfile.TemporaryDirectory(prefix="arb_prof_") as td:
+        so = Path(td) / "attn_prof.so"
+        flags = [f for f in B.NVCC_FLAGS if f not in ("-Xptxas", "-v")]
+        subprocess.run([B.nvcc_path()] + flags + ["-DARB_ATTN_PROF", "-shared", str(B.CSRC / "attn_fwd2_sm100.cu"), "-o", str(so),
+                        "-lcuda"], check=True)
+        lib = C.CDLL(str(so))
+        Dl = H * 128
+        torch.manual_seed(0)
+        qkv = torch.randn(T, 3 * Dl, device="cuda").to(torch.bfloat16)
+        o = torch.empty(T, Dl, device="cuda", dtype=torch.bfloat16)
+        lse = torch.empty(1, H, T, device="cuda")
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        prof = torch.zeros(64, dtype=torch.int64, device="cuda")
+        vp, ll, ci = C.c_void_p, C.c_longlong, C.c_int
+        f = lib.arb_attn_prof_fwd2
+        f.restype = ci
+        f.argtypes = [vp] * 5 + [ci, ci, ci, ll, ll, ci, C.c_float, vp, vp]
+        b = qkv.data_ptr()
+        for _ in range(2):
+            prof.zero_()
+            e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+            e1.record()
+            rc = f(b, b + 2 * Dl, b + 4 * Dl, o.data_ptr(), lse.data_ptr(), 1, T, H, 3 * Dl, Dl, W, 1 / math.sqrt(128),
+                   err.data_ptr(), prof.data_ptr())
+            e2.record()
+            torch.cuda.synchronize()
+            assert rc == 0 and err.item() == 0, (rc, err.item())
+        print(f"B=1 T={T} H={H} window={W}: forward (two query tiles per CTA) {e1.elapsed_time(e2):.3f} ms (with the profiling marks)")
+        p = prof.cpu()
+        nt = (T + 127) // 128 if W >= T else (W // 128 + 2)
+        print(f"cycles per key tile, heaviest CTA ({nt} key tiles, two query tiles each)")
+        for role, label, names in (
+                (0, "issuer", ["total", "wait V(t)", "wait P0(t)", "issue PV0(t)", "wait K(t+1)", "issue S0(t+1)", "wait P1(t)",
+                               "issue PV1(t), S1(t+1)"]),
+                (2, "softmax g0", ["total", "wait S", "row max", "rescale", "exp + store P", "store wait, arrive", "", ""]),
+                (3, "softmax g1", ["total", "wait S", "row max", "rescale", "exp + store P", "store wait, arrive", "", ""])):
+            row = p[role * 8: role * 8 + 8].tolist()
+            print("   %-11s" % label, "  ".join(f"{n}={v / nt:.0f}" for n, v in zip(names, row) if n))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--T", type=int, default=32768)
     ap.add_argument("--H", type=int, default=8)
     ap.add_argument("--window", type=int, default=None)
+    ap.add_argument("--kernel", choices=("bwd", "fwd2"), default="bwd",
+                    help="bwd: the wide backward kernels; fwd2: the forward with two query tiles per CTA")
     a = ap.parse_args()
+    if a.kernel == "fwd2":
+        return fwd2(a)
     T, H, Bsz = a.T, a.H, 1
     W = a.window if a.window is not None else T
     with tempfile.TemporaryDirectory(prefix="arb_prof_") as td:

@@ -91,4 +91,9 @@ int attn_wide_bwd_launch(const void* q, const void* k, const void* v, const void
                          long long ldq, long long ldk, long long ldv, long long lddo, long long lddq, long long lddk,
                          long long lddv, AttnArgs a, cudaStream_t stream);
 
+
+// attn_fwd2_sm100.cu
+int attn_fwd2_launch(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv, AttnArgs a,
+                     cudaStream_t stream);
+
 }  // namespace arb

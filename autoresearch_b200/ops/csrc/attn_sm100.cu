@@ -815,10 +815,11 @@ __global__ void __launch_bounds__(256) attn_delta_k(const __nv_bfloat16* __restr
 
 using namespace arb;
 
-// 2 (default): wide backward; 1: 64-wide sub-tiles with TMEM operands; 0: with shared-memory operands
+// 3: as 2 with the two-query-tile forward for every shape; 2 (default): wide backward, two-query-tile forward for
+// short windows only; 1: 64-wide sub-tiles with TMEM operands; 0: with shared-memory operands
 static int g_attn_mode = 2;
 static int g_attn_ts = 1;
-extern "C" void arb_attn_set_mode(int mode) { g_attn_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode); g_attn_ts = g_attn_mode ? 1 : 0; }
+extern "C" void arb_attn_set_mode(int mode) { g_attn_mode = mode < 0 ? 0 : (mode > 3 ? 3 : mode); g_attn_ts = g_attn_mode ? 1 : 0; }
 
 template <bool TS>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a, dim3 grid,
@@ -862,6 +863,11 @@ extern "C" int arb_attn_fwd(const void* q, const void* k, const void* v, void* o
   AttnArgs a{};
   a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
   a.o = o; a.ldo = ldo; a.lse = lse; a.err = err_flag;
+  // Two query tiles per CTA: measured faster only for short windows on large grids (B=4, H=8, T=32768: window 128
+  // 0.434 -> 0.378 ms, 256 0.513 -> 0.474 ms, 512 equal, 1024 and above slower; full causal 9.55 -> 13.05 ms).
+  const long long pair_ctas = (long long)((T + 255) / 256) * H * B;
+  if (g_attn_mode == 3 || (g_attn_mode == 2 && a.window <= 256 && pair_ctas >= 2048))
+    return attn_fwd2_launch(q, k, v, ldq, ldk, ldv, a, stream);
   dim3 grid((T + 127) / 128, H, B);
   return g_attn_ts ? launch_fwd<true>(tq, tk, tv, a, grid, stream) : launch_fwd<false>(tq, tk, tv, a, grid, stream);
 }
@@ -880,7 +886,7 @@ extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const v
   AttnArgs a{};
   a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
   a.lse = const_cast<float*>(lse); a.delta = delta; a.err = err_flag;
-  if (g_attn_mode == 2)
+  if (g_attn_mode >= 2)
     return attn_wide_bwd_launch(q, k, v, d_o, dq, dk, dv, ldq, ldk, ldv, lddo, lddq, lddk, lddv, a, stream);
   {
     CUtensorMap tq, tk, tv, tdo;

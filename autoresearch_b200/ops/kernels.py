@@ -221,8 +221,9 @@ def flush_pending_pulls() -> None:
 
 
 def attn_set_mode(mode: int) -> None:
-    """2 (default) = backward on 128 x 128 tiles with the two-phase softmax; 1 = 64-wide sub-tiles with
-    P / dS operands in TMEM; 0 = 64-wide sub-tiles with P / dS in shared memory (forward too)."""
+    """3 = as 2, with the forward on two query tiles per CTA in ping-pong; 2 = backward on 128 x 128 tiles with
+    the two-phase softmax; 1 = 64-wide sub-tiles with P / dS operands in TMEM; 0 = 64-wide sub-tiles with P / dS
+    in shared memory (forward too)."""
     f = lib().arb_attn_set_mode
     f.restype, f.argtypes = None, [C.c_int]
     f(int(mode))
