@@ -8,7 +8,10 @@
 // ends, for the record: (1) two issuing threads: the tensor pipe interleaves their instructions and the
 // tile the softmax warps wait for finishes later than when one thread queues the work in the order it is
 // needed; (2) evaluating part of the exponentials with a polynomial on the FMA pipe: the extra
-// instructions take issue slots from the issuing thread, which shares a scheduler with two softmax warps.
+// instructions take issue slots from the issuing thread, which shares a scheduler with two softmax warps;
+// (3) in the dQ kernel, double-buffered scores with dS written over the score tile (one barrier check fewer per
+// tile) and, separately, Q and dO held in TMEM as the A operands of S and dP (half the shared-memory operand
+// reads): both correct, neither faster, so neither the barrier checks nor shared-memory bandwidth is the bound.
 //
 // The softmax of a tile is split in two phases so that the score buffer is released early:
 //   phase A  needs only S: p = exp2(S*c - lse) is kept in fp32 registers (64 per thread);
