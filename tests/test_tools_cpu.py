@@ -71,3 +71,30 @@ def test_launch_lifecycle_and_plot(tmp_path):
     plot_live.main([str(out / "train.log"), "--out", str(tmp_path / "c.svg")])
     svg = (tmp_path / "c.svg").read_text()
     assert svg.startswith("<svg") and "polyline" in svg
+
+
+def test_report_page_from_bench_lines(tmp_path):
+    """The static benchmark page: one bar per result line, grouped by metric; 'unavailable' lines become notes."""
+    import json
+    from autoresearch_b200.tools import report
+    lines = [
+        {"metric": "train tokens/sec", "value": 222063.0, "unit": "tokens/s", "n_gpus": 1, "steps": 3, "ms_per_step": 2361.0,
+         "dtype": "bf16", "vs_baseline": 4.22, "impl": "sm100", "data": "synthetic",
+         "config": {"model": "phase2 <428M>", "parallelism": "dp1"}, "clocks": {"sm_mhz": 1567, "reasons": ["sw_power_cap"]},
+         "e2e": {"value": 221900.0}},
+        {"metric": "train tokens/sec", "value": 1743016.0, "unit": "tokens/s", "n_gpus": 8, "steps": 3, "ms_per_step": 300.8,
+         "dtype": "bf16", "vs_baseline": None, "impl": "sm100", "data": "synthetic", "config": {"model": "phase2", "parallelism": "dp8"}},
+        {"impl": "reference", "unavailable": "needs a Hopper-only attention library"},
+    ]
+    src = tmp_path / "r.jsonl"
+    src.write_text("noise before\n" + "\n".join(json.dumps(l) for l in lines) + "\nnot json {\n")
+    out = tmp_path / "report.html"
+    report.main([str(src), "--out", str(out)])
+    page = out.read_text()
+    assert page.count("<rect") == 2 and "1,743,016 tokens/s" in page and "4.22x published reference" in page
+    assert "phase2 &lt;428M&gt;" in page                      # labels are escaped
+    assert "needs a Hopper-only attention library" in page and "sw_power_cap" in page
+    # the longest bar belongs to the largest value
+    import re
+    widths = [float(w) for w in re.findall(r'<rect x="390" y="\d+" width="([0-9.]+)"', page)]
+    assert widths[1] == 420.0 and widths[0] < 60
