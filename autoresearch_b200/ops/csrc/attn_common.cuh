@@ -66,6 +66,48 @@ __device__ __forceinline__ float poly_exp2(float x) {
   return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
 }
 
+// row maximum of 64 scores, columns [col0, col0 + 64) of a tile whose visible columns are [mlo, mlo + span]
+template <bool MASK>
+__device__ __forceinline__ void max64(const uint32_t (&a)[32], const uint32_t (&b)[32], int col0, int mlo, unsigned span,
+                                      float (&mxa)[4]) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x = __uint_as_float(a[j]), y = __uint_as_float(b[j]);
+    if constexpr (MASK) {
+      x = (unsigned(col0 + j - mlo) <= span) ? x : -INFINITY;
+      y = (unsigned(col0 + 32 + j - mlo) <= span) ? y : -INFINITY;
+    }
+    mxa[j & 3] = fmaxf(mxa[j & 3], fmaxf(x, y));
+  }
+}
+
+// Exponentials of the 64 scores of columns [col0, col0 + 64) of one row (two 32-column loads), written to
+// `tm_dst` as 32 columns of bf16 pairs; row sums into four chains.
+template <bool MASK>
+__device__ __forceinline__ void exp64_store(const uint32_t (&s0)[32], const uint32_t (&s1)[32], uint32_t tm_dst, float c,
+                                            float mc, int col0, int mlo, unsigned span, float (&rsa)[4]) {
+  uint32_t pk[32];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    float e[4];
+    e[0] = fast_exp2(__uint_as_float(s0[2 * j]) * c - mc);
+    e[1] = fast_exp2(__uint_as_float(s0[2 * j + 1]) * c - mc);
+    e[2] = fast_exp2(__uint_as_float(s1[2 * j]) * c - mc);
+    e[3] = fast_exp2(__uint_as_float(s1[2 * j + 1]) * c - mc);
+    if constexpr (MASK) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int col = col0 + (u >> 1) * 32 + 2 * j + (u & 1);
+        e[u] = (unsigned(col - mlo) <= span) ? e[u] : 0.f;
+      }
+    }
+    rsa[j & 3] += (e[0] + e[1]) + (e[2] + e[3]);
+    pk[j] = pack_bf16(e[0], e[1]);
+    pk[16 + j] = pack_bf16(e[2], e[3]);
+  }
+  tmem_st32(tm_dst, pk);
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }

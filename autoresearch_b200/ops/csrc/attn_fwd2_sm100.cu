@@ -17,13 +17,13 @@
 // of its own.  The scores are read from TMEM twice (row maximum, then exponentials) instead of being
 // held in 128 registers.
 //
-// Measured (B=4, H=8, T=32768, B200 under its power cap): faster than the one-tile kernel only for windows of up to
-// 256 keys (0.513 -> 0.474 ms); equal at 512; slower for long ranges (full causal 13.05 ms against 9.55 ms).  The
-// role counters (bench/attn_roles.py --kernel fwd2) show why: per key tile and CTA the 32 MMAs take 3350 clk to
-// issue (105 each instead of 66 with four softmax warps), a row-maximum pass takes 1000-1400 clk and the
-// exponentials 1600-2000 clk, because eight softmax warps, their TMEM loads and the tensor pipe's accumulator
-// traffic slow each other down; the two groups then drift into phase instead of alternating.  The dispatcher
-// therefore selects this kernel for short windows on large grids only.
+// Measured (B=4, H=8, T=32768, B200 under its power cap): 3-5 % faster than the one-tile kernel (full causal 9.79 ->
+// 9.42 ms, window 4096 2.61 -> 2.50 ms, window 256 0.51 -> 0.47 ms); slower on grids of few waves, so the dispatcher
+// uses it on large grids only.  Two findings from the role counters (bench/attn_roles.py --kernel fwd2): (1) a mask
+// test inside the unrolled loops, even on tiles that need none, doubled both softmax passes (full causal 13.05 ms
+// with it), so the masked variants are selected per tile outside the loops; (2) with that fixed the MMA-issuing
+// thread is the bound: the 32 MMAs of a key tile take about 3000 clk to issue (94 each, 66 in isolation), and each
+// softmax group waits for scores half of the time.
 //
 // Mask semantics: key j is visible to query i iff i - window <= j <= i
 // (brain/src/forward.rs:1134-1138); the reference calls a Hopper-only FlashAttention-3 build here
@@ -216,21 +216,16 @@ attn_fwd2_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const unsigned span = (row < p.T) ? unsigned(p.window) : 0u;
       // ---- pass 1: row maximum ----
       float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // the masked variants are selected per tile, outside the unrolled loops: a compare / select per element in the
+      // common path doubled the time of both passes
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t s0[32], s1[32];
         tmem_ld32(TM_S + lane_addr + uint32_t(hf * 64), s0);
         tmem_ld32(TM_S + lane_addr + uint32_t(hf * 64 + 32), s1);
         tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float a = __uint_as_float(s0[j]), bb = __uint_as_float(s1[j]);
-          if (need_mask) {
-            a = (unsigned(hf * 64 + j - mlo) <= span) ? a : -INFINITY;
-            bb = (unsigned(hf * 64 + 32 + j - mlo) <= span) ? bb : -INFINITY;
-          }
-          mxa[j & 3] = fmaxf(mxa[j & 3], fmaxf(a, bb));
-        }
+        if (need_mask) max64<true>(s0, s1, hf * 64, mlo, span, mxa);
+        else max64<false>(s0, s1, hf * 64, mlo, span, mxa);
       }
       const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
       const float m_new = fmaxf(m_used, mx);
@@ -259,26 +254,13 @@ attn_fwd2_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       float rsa[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        uint32_t s0[32], s1[32], pk[32];
+        uint32_t s0[32], s1[32];
         tmem_ld32(TM_S + lane_addr + uint32_t(hf * 64), s0);
         tmem_ld32(TM_S + lane_addr + uint32_t(hf * 64 + 32), s1);
         tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float x[4] = {__uint_as_float(s0[2 * j]), __uint_as_float(s0[2 * j + 1]), __uint_as_float(s1[2 * j]),
-                        __uint_as_float(s1[2 * j + 1])};
-          float e[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int col = hf * 64 + (u >> 1) * 32 + 2 * j + (u & 1);
-            e[u] = fast_exp2(x[u] * c - mc);
-            if (need_mask) e[u] = (unsigned(col - mlo) <= span) ? e[u] : 0.f;
-          }
-          rsa[j & 3] += (e[0] + e[1]) + (e[2] + e[3]);
-          pk[j] = pack_bf16(e[0], e[1]);
-          pk[16 + j] = pack_bf16(e[2], e[3]);
-        }
-        tmem_st32(TM_S + lane_addr + uint32_t(hf * 32), pk);   // columns [32 hf, 32 hf + 32) <= scores already read
+        // columns [32 hf, 32 hf + 32) <= scores already read
+        if (need_mask) exp64_store<true>(s0, s1, TM_S + lane_addr + uint32_t(hf * 32), c, mc, hf * 64, mlo, span, rsa);
+        else exp64_store<false>(s0, s1, TM_S + lane_addr + uint32_t(hf * 32), c, mc, hf * 64, mlo, span, rsa);
       }
       l += (rsa[0] + rsa[1]) + (rsa[2] + rsa[3]);
       PROF_TOC(4);

@@ -815,8 +815,8 @@ __global__ void __launch_bounds__(256) attn_delta_k(const __nv_bfloat16* __restr
 
 using namespace arb;
 
-// 3: as 2 with the two-query-tile forward for every shape; 2 (default): wide backward, two-query-tile forward for
-// short windows only; 1: 64-wide sub-tiles with TMEM operands; 0: with shared-memory operands
+// 3: as 2 with the two-query-tile forward for every shape; 2 (default): wide backward, two-query-tile forward on
+// large grids only; 1: 64-wide sub-tiles with TMEM operands; 0: with shared-memory operands
 static int g_attn_mode = 2;
 static int g_attn_ts = 1;
 extern "C" void arb_attn_set_mode(int mode) { g_attn_mode = mode < 0 ? 0 : (mode > 3 ? 3 : mode); g_attn_ts = g_attn_mode ? 1 : 0; }
@@ -863,10 +863,11 @@ extern "C" int arb_attn_fwd(const void* q, const void* k, const void* v, void* o
   AttnArgs a{};
   a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
   a.o = o; a.ldo = ldo; a.lse = lse; a.err = err_flag;
-  // Two query tiles per CTA: measured faster only for short windows on large grids (B=4, H=8, T=32768: window 128
-  // 0.434 -> 0.378 ms, 256 0.513 -> 0.474 ms, 512 equal, 1024 and above slower; full causal 9.55 -> 13.05 ms).
+  // Two query tiles per CTA: 3-5 % faster than one tile on grids of several waves (B=4, H=8, T=32768: full causal
+  // 9.79 -> 9.42 ms, window 4096 2.61 -> 2.50 ms, window 1024 0.96 -> 0.92 ms, window 256 0.51 -> 0.47 ms), slower on small
+  // grids, where halving the CTA count costs more than the shared K / V loads save.
   const long long pair_ctas = (long long)((T + 255) / 256) * H * B;
-  if (g_attn_mode == 3 || (g_attn_mode == 2 && a.window <= 256 && pair_ctas >= 2048))
+  if (g_attn_mode == 3 || (g_attn_mode == 2 && pair_ctas >= 2048))
     return attn_fwd2_launch(q, k, v, ldq, ldk, ldv, a, stream);
   dim3 grid((T + 127) / 128, H, B);
   return g_attn_ts ? launch_fwd<true>(tq, tk, tv, a, grid, stream) : launch_fwd<false>(tq, tk, tv, a, grid, stream);
