@@ -50,6 +50,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+#ifndef ARB_FWD2_POLY
+#define ARB_FWD2_POLY 0
+#endif
 #ifndef ARB_FWD_POLY_OF_8
 #define ARB_FWD_POLY_OF_8 0
 #endif
@@ -90,10 +93,11 @@ __device__ __forceinline__ void exp64_store(const uint32_t (&s0)[32], const uint
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     float e[4];
+    // ARB_FWD2_POLY of every four exponentials go to the FMA pipe as a cubic instead of the ex2 unit
     e[0] = fast_exp2(__uint_as_float(s0[2 * j]) * c - mc);
-    e[1] = fast_exp2(__uint_as_float(s0[2 * j + 1]) * c - mc);
+    e[1] = (ARB_FWD2_POLY >= 2) ? poly_exp2(__uint_as_float(s0[2 * j + 1]) * c - mc) : fast_exp2(__uint_as_float(s0[2 * j + 1]) * c - mc);
     e[2] = fast_exp2(__uint_as_float(s1[2 * j]) * c - mc);
-    e[3] = fast_exp2(__uint_as_float(s1[2 * j + 1]) * c - mc);
+    e[3] = (ARB_FWD2_POLY >= 1) ? poly_exp2(__uint_as_float(s1[2 * j + 1]) * c - mc) : fast_exp2(__uint_as_float(s1[2 * j + 1]) * c - mc);
     if constexpr (MASK) {
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
