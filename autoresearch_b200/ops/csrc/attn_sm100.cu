@@ -865,9 +865,10 @@ extern "C" int arb_attn_fwd(const void* q, const void* k, const void* v, void* o
   a.o = o; a.ldo = ldo; a.lse = lse; a.err = err_flag;
   // Two query tiles per CTA: 3-5 % faster than one tile on grids of several waves (B=4, H=8, T=32768: full causal
   // 9.79 -> 9.42 ms, window 4096 2.61 -> 2.50 ms, window 1024 0.96 -> 0.92 ms, window 256 0.51 -> 0.47 ms), slower on small
-  // grids, where halving the CTA count costs more than the shared K / V loads save.
+  // grids, where halving the CTA count costs more than the shared K / V loads save, and no gain on short sequences
+  // (B=64, H=4, T=2048: full equal, window 1024 0.369 -> 0.392 ms; B=8, H=16, T=8192: full 2.49 -> 2.39 ms).
   const long long pair_ctas = (long long)((T + 255) / 256) * H * B;
-  if (g_attn_mode == 3 || (g_attn_mode == 2 && pair_ctas >= 2048))
+  if (g_attn_mode == 3 || (g_attn_mode == 2 && pair_ctas >= 2048 && T >= 4096))
     return attn_fwd2_launch(q, k, v, ldq, ldk, ldv, a, stream);
   dim3 grid((T + 127) / 128, H, B);
   return g_attn_ts ? launch_fwd<true>(tq, tk, tv, a, grid, stream) : launch_fwd<false>(tq, tk, tv, a, grid, stream);
