@@ -30,7 +30,8 @@ def main() -> int:
     ap.add_argument("--model", default="phase2")
     ap.add_argument("--attn", default=None, choices=[None, "own", "library"])
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--micro-batch", type=int, default=4)
+    ap.add_argument("--micro-batch", type=int, default=None,
+                    help="sequences per GPU and micro-step; default 4 (64 for phase1, the reference's batch for that model)")
     ap.add_argument("--total-batch", type=int, default=524288)
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (world = tp x dp); dense models")
@@ -72,8 +73,10 @@ def main() -> int:
     mcfg = model_preset(args.model, **over)
     sched = ScheduleConfig(peak_lr=0.02, weight_decay=0.3, final_lr_frac=0.02,
                            embedding_lr=0.45, unembedding_lr=0.0025, scalar_lr=0.25)
-    if args.impl == "baseline" and args.micro_batch == 4:
-        args.micro_batch = 2   # the library arm keeps every autograd intermediate: 4 x 32768 tokens do not fit
+    if args.micro_batch is None:
+        args.micro_batch = 64 if args.model == "phase1" else 4
+        if args.impl == "baseline" and args.model != "phase1":
+            args.micro_batch = 2   # the library arm keeps every autograd intermediate: 4 x 32768 tokens do not fit
     tcfg = TrainConfig(device_batch_size=args.micro_batch, total_batch_size=args.total_batch,
                        max_steps=1000, cooldown_steps=300, synthetic_data=True, synthetic_kind="zipf",
                        impl=args.impl, schedule_cfg=sched, cooldown_trigger_file="",
