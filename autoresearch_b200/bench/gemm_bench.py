@@ -69,15 +69,11 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-ref", action="store_true")
-    ap.add_argument("--flags", type=int, default=0)
     a = ap.parse_args()
     if a.table:
         print(table(a.iters, a.warmup))
         return
     K.gemm_set_mode(a.mode)
-    if a.flags:
-        import ctypes
-        K.lib().arb_gemm_set_flags(ctypes.c_int(a.flags))
     M, N, Kd = a.M, a.N, a.K
     g = torch.Generator(device="cuda").manual_seed(0)
     r = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)

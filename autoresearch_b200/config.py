@@ -258,6 +258,7 @@ class TrainConfig:
     metrics_jsonl: Optional[str] = None
     resume: bool = False
     heartbeat_timeout_s: float = 0.0  # > 0: watch peer liveness through the process group's store
+    peak_flops: Optional[float] = None  # MFU denominator per GPU; None = ARB_PEAK_TFLOPS or the nominal B200 peak
     parallel: ParallelConfig = field(default_factory=ParallelConfig)
 
     @staticmethod

@@ -122,6 +122,20 @@ class ShardLoader:
             have += len(r)
         return np.concatenate(parts)[:need] if len(parts) > 1 else parts[0][:need]
 
+    def state_dict(self):
+        """Position of the stream: epoch, index into the epoch's shard order, next row of that shard (the order
+        itself follows from seed + epoch)."""
+        return {"epoch": self.epoch, "si": self.si, "ri": self.ri if self.cur is not None else 0}
+
+    def load_state_dict(self, d) -> None:
+        self.epoch, self.si = int(d["epoch"]), int(d["si"])
+        if self.split == "train":
+            self.order = shuffle_order(len(self.files), self.seed + self.epoch)
+        if self.si >= len(self.files):
+            raise ValueError(f"data position names shard {self.si} of {len(self.files)}")
+        self._open()
+        self.ri = int(d["ri"])
+
     def next_batch(self, ids_out=None, tgt_out=None):
         """Round-robin over data-parallel ranks: rank r takes sequences r, r+world, ..."""
         rows = []
@@ -150,6 +164,7 @@ class StdinRowStream:
         self.h = self.lib.ar_rowstream_open(fd, seq_len + 1, batch_size, depth)
         if not self.h:
             raise ValueError("bad row stream parameters")
+        self._batches = 0
 
     def next_batch(self, ids_out=None, tgt_out=None, timeout_ms: int = -1):
         if ids_out is None:
@@ -157,6 +172,7 @@ class StdinRowStream:
             tgt_out = torch.empty(self.B, self.T, dtype=torch.int32)
         rc = self.lib.ar_rowstream_next(self.h, ids_out.data_ptr(), tgt_out.data_ptr(), timeout_ms)
         if rc == 1:
+            self._batches += 1
             return ids_out, tgt_out
         if rc == 0:
             return None
@@ -166,6 +182,18 @@ class StdinRowStream:
 
     def rows_read(self) -> int:
         return int(self.lib.ar_rowstream_rows_read(self.h))
+
+    def state_dict(self):
+        return {"batches": self._batches}
+
+    def load_state_dict(self, d) -> None:
+        """A pipe cannot seek: the batches already consumed are read and dropped, which restores the position
+        when the feeder replays the same stream (a seeded feeder does)."""
+        ids = torch.empty(self.B, self.T, dtype=torch.int32)
+        tgt = torch.empty(self.B, self.T, dtype=torch.int32)
+        for _ in range(int(d.get("batches", 0)) - self._batches):
+            if self.next_batch(ids, tgt) is None:
+                break
 
     def close(self):
         if self.h:

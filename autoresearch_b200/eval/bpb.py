@@ -32,8 +32,14 @@ def load_token_bytes(path, vocab: int, device="cpu") -> torch.Tensor:
 
 @torch.no_grad()
 def eval_bpb(model, loader, token_bytes: torch.Tensor, max_batches: Optional[int] = None,
-             device="cpu", group=None) -> float:
-    """`loader.next_batch()` returns (ids, targets) int32 [B, T] or None at the end."""
+             device="cpu", group=None, forward=None) -> float:
+    """`loader.next_batch()` returns (ids, targets) int32 [B, T] or None at the end.
+
+    `group`: the ranks whose sums are added (every rank scores different tokens).  They leave the loop together:
+    a validation split can end on one rank first, so each batch is preceded by an agreement (MIN over the group)
+    that every rank still has one.  `forward(ids, targets) -> (per_token_losses, targets_scored)` replaces the
+    plain model call where a rank scores only part of a batch (tensor-parallel token shards, the last pipeline
+    stage)."""
     B, T = loader.B, loader.T
     n = EVAL_TOKENS // (B * T)
     if max_batches is not None:
@@ -43,19 +49,30 @@ def eval_bpb(model, loader, token_bytes: torch.Tensor, max_batches: Optional[int
     nbytes = torch.zeros((), dtype=torch.float64, device=device)
     was_training = model.training
     model.eval()
+    dist = None
+    if group is not None:
+        import torch.distributed as dist
     for _ in range(n):
         batch = loader.next_batch()
-        if batch is None:
+        if dist is not None:
+            have = torch.tensor([0 if batch is None else 1], dtype=torch.int32, device=device)
+            dist.all_reduce(have, op=dist.ReduceOp.MIN, group=group)
+            if int(have.item()) == 0:
+                break
+        elif batch is None:
             break
         ids, tgt = (t.to(device, non_blocking=True) for t in batch)
-        _, per_tok = model(ids, tgt)
-        by = token_bytes[tgt.reshape(-1).long()]
+        if forward is not None:
+            per_tok, scored = forward(ids, tgt)
+        else:
+            _, per_tok = model(ids, tgt)
+            scored = tgt
+        by = token_bytes[scored.reshape(-1).long()]
         m = by > 0
         nats += (per_tok.double() * m).sum()
         nbytes += by.double().sum()
     model.train(was_training)
-    if group is not None:
-        import torch.distributed as dist
+    if dist is not None:
         pair = torch.stack([nats, nbytes])
         dist.all_reduce(pair, group=group)
         nats, nbytes = pair[0], pair[1]

@@ -40,8 +40,20 @@ int arb_gemm_bf16(const void* A, const void* B, void* C, const void* aux, int M,
 // Tile selection: 0 = automatic (2-CTA 256x256 tiles when M >= 512 and N >= 256, else 1-CTA
 // 128x256/128x128), 1 = always 1-CTA, 2 = always 2-CTA.  Process-wide; meant for tests / benchmarks.
 int arb_gemm_set_mode(int mode);
-// one-shot: the next arb_gemm_bf16 of the calling thread pulls `bytes` from `src` to `dst` in its prologue
-int arb_gemm_pull_next(const void* src, void* dst, long long bytes);
+// The same GEMM with up to two copies from another GPU's memory folded into the kernel (the data-parallel
+// all-gather of updated weights, see parallel/fused_dp.py).  Sizes are multiples of 16 bytes, pointers 16-byte
+// aligned; a null source switches the copy off.
+//   pull_src / pull_bytes   B itself is stale: every CTA first copies pull_src -> B (peer loads), the grid meets
+//                           at a bounded counter barrier, then the tiles are computed.  Needs the whole grid
+//                           resident (it is: one persistent CTA per SM).
+//   ahead_src / ahead_dst / ahead_bytes   the operand of a LATER GEMM on the same stream: a spare warp of every CTA
+//                           copies it while the tiles are computed; the kernel boundary orders the copy before its
+//                           consumer.
+int arb_gemm_bf16_ex(const void* A, const void* B, void* C, const void* aux, int M, int N, int K, int batch,
+                     long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                     long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha, float beta,
+                     float gamma, int* err_flag, cudaStream_t stream, const void* pull_src, long long pull_bytes,
+                     const void* ahead_src, void* ahead_dst, long long ahead_bytes);
 
 // ---- flash attention (attn_sm100.cu) ----------------------------------------------------------
 // q, k, v, o: [B, T, H, hd=128] bf16 with token stride `ld*` elements (head h at column

@@ -11,9 +11,10 @@
 // (brain/kernels/muon.cu:385-415), and fp32 gradient accumulation (split-K partial sums are
 // added with red.global so wide-K dW GEMMs fill all SMs).
 //
-// CTA = 192 threads: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5 epilogue
-// (warp w reads TMEM lanes 32*(w%4)..+31).  Tile 128 x BN x 64 (BN = 256 or 128), 128-byte
-// swizzled smem stages.
+// CTA = 224 threads: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5 epilogue
+// (warp w reads TMEM lanes 32*(w%4)..+31), warp 6 copies another operand from a peer GPU while the
+// tiles are computed (GemmArgs::ahead_src; idle otherwise).  Tile 128 x BN x 64 (BN = 256 or 128),
+// 128-byte swizzled smem stages.
 #include "api.h"
 #include "ptx.cuh"
 #include "tmap.h"
@@ -24,7 +25,7 @@ namespace arb {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 224;
 
 struct GemmArgs {
   int M, N, K, batch;
@@ -34,7 +35,6 @@ struct GemmArgs {
   long long ldc, stride_c;      // elements
   float alpha, beta, gamma;
   int* err;
-  int flags;   // experiment switches of the 2-CTA kernel: bit0 = multicast commits, bit1 = leader-only barrier arrive
   // Optional prologue: before any tile is loaded, all CTAs of this (fully resident, persistent) grid copy
   // pull_n16 16-byte units from pull_src (the owner rank's copy of the B operand, NVLink peer loads) to
   // pull_dst (the local operand) and meet at a counter barrier.  Fuses the data-parallel all-gather of an
@@ -44,18 +44,41 @@ struct GemmArgs {
   long long pull_n16;
   unsigned* pull_counter;
   unsigned pull_target;
+  // Optional side copy, overlapped with the tile loop: warp 6 of every CTA copies ahead_n16 16-byte units from
+  // ahead_src (a peer rank's copy of the operand of a LATER GEMM on this stream) to ahead_dst.  Nothing in this
+  // kernel reads ahead_dst; the kernel boundary orders the copy before its consumer, so no barrier is needed.
+  const uint4* ahead_src;
+  uint4* ahead_dst;
+  long long ahead_n16;
 };
+
+__device__ __forceinline__ uint4 ld_peer16(const uint4* a) {
+  uint4 v;
+  asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(a));
+  return v;
+}
+
+// Warp 6: grid-strided copy with eight peer loads in flight per thread.
+__device__ __forceinline__ void pull_ahead(const GemmArgs& p, int lane) {
+  if (p.ahead_n16 <= 0) return;
+  const long long stride = (long long)gridDim.x * 32;
+  long long i = (long long)blockIdx.x * 32 + lane;
+  for (; i + 7 * stride < p.ahead_n16; i += 8 * stride) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = ld_peer16(p.ahead_src + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) p.ahead_dst[i + u * stride] = v[u];
+  }
+  for (; i < p.ahead_n16; i += stride) p.ahead_dst[i] = ld_peer16(p.ahead_src + i);
+}
 
 // Runs in every thread of every CTA at kernel start.  The waits are bounded; on expiry the error word is set
 // and the kernel goes on (the result is then wrong, the host raises on the error word).
 __device__ __forceinline__ void pull_prologue(const GemmArgs& p) {
   if (p.pull_n16 <= 0) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  auto ld = [](const uint4* a) {
-    uint4 v;
-    asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(a));
-    return v;
-  };
+  auto ld = [](const uint4* a) { return ld_peer16(a); };
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   for (; i + 3 * stride < p.pull_n16; i += 4 * stride) {     // four peer loads in flight per thread
     const uint4 a = ld(p.pull_src + i), b = ld(p.pull_src + i + stride), c = ld(p.pull_src + i + 2 * stride),
@@ -272,6 +295,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (ok) tc_commit(&tfull_bar[acc]);
       }
     }
+  } else if (warp == 6) {
+    pull_ahead(p, lane);
   } else {
     // ---------------- epilogue (4 warps) ----------------
     const int q = warp & 3;
@@ -443,25 +468,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint64_t bd = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 0, 1024);
             tc_mma_ss_pair(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          if (p.flags & 1) {
-            tc_commit_pair_mc(&empty_bar[s], 3);
-          } else {
-            const uint32_t eb = smem_u32(&empty_bar[s]);
-            tc_commit_pair(eb);
-            tc_commit_pair(mapa_u32(eb, 1));
-          }
+          const uint32_t eb = smem_u32(&empty_bar[s]);
+          tc_commit_pair(eb);
+          tc_commit_pair(mapa_u32(eb, 1));
         }
         if (ok) {
-          if (p.flags & 1) {
-            tc_commit_pair_mc(&tfull_bar[acc], 3);
-          } else {
-            const uint32_t tb = smem_u32(&tfull_bar[acc]);
-            tc_commit_pair(tb);
-            tc_commit_pair(mapa_u32(tb, 1));
-          }
+          const uint32_t tb = smem_u32(&tfull_bar[acc]);
+          tc_commit_pair(tb);
+          tc_commit_pair(mapa_u32(tb, 1));
         }
       }
     }
+  } else if (warp == 6) {
+    pull_ahead(p, lane);
   } else {
     const int q = warp & 3;
     uint32_t tile_it = 0, slab_it = 0;
@@ -610,32 +629,28 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 // ------------------------------------------------------------------------------------------
 static int g_num_sms = 0;
-static int g_gemm_flags = 0;
-// one-shot request set by arb_gemm_pull_next and consumed by the next arb_gemm_bf16 of this thread
-struct PullRequest { const void* src; void* dst; long long bytes; };
-static thread_local PullRequest g_pull = {nullptr, nullptr, 0};
+// Counters of the prologue pull: a ring per device, one slot per pulling launch (round-robin), each slot with a
+// running target, so that pulling GEMMs in flight on different streams never share a counter.
 constexpr int PULL_MAX_DEV = 64;
+constexpr int PULL_SLOTS = 64;
 static unsigned* g_pull_counter[PULL_MAX_DEV] = {nullptr};
-static unsigned g_pull_total[PULL_MAX_DEV] = {0};
+static unsigned g_pull_total[PULL_MAX_DEV][PULL_SLOTS] = {{0}};
+static unsigned g_pull_next_slot[PULL_MAX_DEV] = {0};
 
-// Fills the pull fields for a launch of `grid_ctas` CTAs; 0 on success.
+// Fills the counter fields of a launch of `grid_ctas` CTAs whose prologue pull is set; 0 on success.
 static int arm_pull(GemmArgs& a, int grid_ctas) {
-  a.pull_src = nullptr; a.pull_dst = nullptr; a.pull_n16 = 0; a.pull_counter = nullptr; a.pull_target = 0;
-  if (!g_pull.src) return 0;
-  const PullRequest rq = g_pull;
-  g_pull = {nullptr, nullptr, 0};
+  a.pull_counter = nullptr; a.pull_target = 0;
+  if (a.pull_n16 <= 0) return 0;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PULL_MAX_DEV) return -7;
   if (!g_pull_counter[dev]) {
-    if (cudaMalloc(&g_pull_counter[dev], sizeof(unsigned)) != cudaSuccess) return -7;
-    if (cudaMemset(g_pull_counter[dev], 0, sizeof(unsigned)) != cudaSuccess) return -7;
+    if (cudaMalloc(&g_pull_counter[dev], PULL_SLOTS * sizeof(unsigned)) != cudaSuccess) return -7;
+    if (cudaMemset(g_pull_counter[dev], 0, PULL_SLOTS * sizeof(unsigned)) != cudaSuccess) return -7;
   }
-  g_pull_total[dev] += unsigned(grid_ctas);
-  a.pull_src = reinterpret_cast<const uint4*>(rq.src);
-  a.pull_dst = reinterpret_cast<uint4*>(rq.dst);
-  a.pull_n16 = rq.bytes / 16;
-  a.pull_counter = g_pull_counter[dev];
-  a.pull_target = g_pull_total[dev];
+  const unsigned slot = g_pull_next_slot[dev]++ % PULL_SLOTS;
+  g_pull_total[dev][slot] += unsigned(grid_ctas);
+  a.pull_counter = g_pull_counter[dev] + slot;
+  a.pull_target = g_pull_total[dev][slot];
   return 0;
 }
 static int g_gemm_mode = 0;   // 0 = automatic, 1 = always 1-CTA tiles, 2 = always 2-CTA tiles
@@ -740,23 +755,27 @@ extern "C" int arb_gemm_set_mode(int mode) {
   g_gemm_mode = mode;
   return 0;
 }
-// The next arb_gemm_bf16 call of this thread first copies `bytes` (a multiple of 16) from `src` (typically a
-// peer rank's copy of its B operand) to `dst` inside the GEMM kernel; see GemmArgs::pull_src.
-extern "C" int arb_gemm_pull_next(const void* src, void* dst, long long bytes) {
-  if (!src || !dst || bytes <= 0 || (bytes & 15) || ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return -3;
-  g_pull = {src, dst, bytes};
-  return 0;
-}
-extern "C" int arb_gemm_set_flags(int flags) {
-  g_gemm_flags = flags;
-  return 0;
+static bool bad_copy(const void* src, const void* dst, long long bytes) {
+  return !src || !dst || bytes <= 0 || (bytes & 15) ||
+         ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15);
 }
 
 extern "C" int arb_gemm_bf16(const void* A, const void* B, void* C, const void* aux, int M, int N, int K, int batch,
                              long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                              long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha,
                              float beta, float gamma, int* err_flag, cudaStream_t stream) {
+  return arb_gemm_bf16_ex(A, B, C, aux, M, N, K, batch, lda, ldb, ldc, stride_a, stride_b, stride_c, a_mn_major, b_mn_major,
+                          epi, splitk, alpha, beta, gamma, err_flag, stream, nullptr, 0, nullptr, nullptr, 0);
+}
+
+extern "C" int arb_gemm_bf16_ex(const void* A, const void* B, void* C, const void* aux, int M, int N, int K, int batch,
+                                long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                                long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha,
+                                float beta, float gamma, int* err_flag, cudaStream_t stream, const void* pull_src,
+                                long long pull_bytes, const void* ahead_src, void* ahead_dst, long long ahead_bytes) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -3;
+  if (pull_src && bad_copy(pull_src, B, pull_bytes)) return -3;
+  if (ahead_src && bad_copy(ahead_src, ahead_dst, ahead_bytes)) return -3;
   // TMA needs 16-byte aligned bases and row strides; vector epilogue needs ldc % 8 == 0.
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -4;
   if ((lda % 8) || (ldb % 8) || (stride_a % 8) || (stride_b % 8)) return -4;
@@ -798,7 +817,13 @@ extern "C" int arb_gemm_bf16(const void* A, const void* B, void* C, const void* 
   a.kb_per_split = (a.kb_total + splitk - 1) / splitk;
   a.splitk = (a.kb_total + a.kb_per_split - 1) / a.kb_per_split;
   a.C = C; a.aux = aux; a.ldc = ldc; a.stride_c = stride_c;
-  a.alpha = alpha; a.beta = beta; a.gamma = gamma; a.err = err_flag; a.flags = g_gemm_flags;
+  a.alpha = alpha; a.beta = beta; a.gamma = gamma; a.err = err_flag;
+  a.pull_src = reinterpret_cast<const uint4*>(pull_src);
+  a.pull_dst = reinterpret_cast<uint4*>(const_cast<void*>(B));
+  a.pull_n16 = pull_src ? pull_bytes / 16 : 0;
+  a.ahead_src = reinterpret_cast<const uint4*>(ahead_src);
+  a.ahead_dst = reinterpret_cast<uint4*>(ahead_dst);
+  a.ahead_n16 = ahead_src ? ahead_bytes / 16 : 0;
 
   CUtensorMap ta, tb;
   {

@@ -191,13 +191,6 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-// one arrive on the barrier at the same offset in every CTA of `cta_mask` (commit multicast; this
-// is a barrier signal, not a data load)
-__device__ __forceinline__ void tc_commit_pair_mc(uint64_t* bar, uint16_t cta_mask) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
-}
-
 // ---- descriptors -------------------------------------------------------------------------------
 // Shared-memory matrix descriptor for 128-byte swizzled tiles (layout type 2), version 1.
 //   K-major  : rows of 64 bf16 (128 B); 8-row groups `sbo` bytes apart; lbo unused.

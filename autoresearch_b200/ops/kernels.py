@@ -21,9 +21,16 @@ ERR_NAMES = {1: "GEMM barrier wait timed out", 2: "attention barrier wait timed 
              5: "dynamic shared memory base is not 1 KB aligned"}
 
 launch_count = 0  # number of kernel-launching calls made through this module
-# B operands whose up-to-date copy still sits on another rank: data_ptr -> (peer pointer, bytes).  The first
-# GEMM that consumes such an operand pulls it inside the kernel (parallel/fused_dp.py registers the entries).
+# B operands whose up-to-date copy still sits on another rank: data_ptr -> (peer pointer, bytes), registered by
+# parallel/fused_dp.py after every optimizer step.  GEMMs on the stream the entries were registered on work the
+# list off: a GEMM whose own B is still pending copies it in its prologue; every GEMM also lets a spare warp copy
+# the oldest other pending entry while its tiles are computed ("ahead" copy), so that from the second GEMM of a
+# step on the operand is already local when its consumer starts.  pull_use_order remembers in which order the
+# operands were consumed, and fused_dp registers them in that order.
 pending_pulls = {}
+pull_stream = None
+pull_use_order = {}
+PULL_AHEAD = True
 
 
 class KernelError(RuntimeError):
@@ -41,6 +48,8 @@ def lib() -> C.CDLL:
     sigs = {
         "arb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32,
                           f32, f32, f32, vp, vp],
+        "arb_gemm_bf16_ex": [vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32,
+                             f32, f32, f32, vp, vp, vp, i64, vp, vp, i64],
         "arb_attn_fwd": [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, f32, vp, vp],
         "arb_attn_bwd": [vp] * 11 + [i32, i32, i32] + [i64] * 8 + [i32, f32, vp, vp],
         "arb_rmsnorm_fwd": [vp, vp, i64, i32, f32, vp],
@@ -74,7 +83,6 @@ def lib() -> C.CDLL:
         "arb_all_gather_pull": [vp, i32, i32, vp, i64, vp],
         "arb_peer_barrier": [vp, i32, i32, i32, vp, vp],
         "arb_pull_ranges": [vp, vp, vp, i32, vp],
-        "arb_gemm_pull_next": [vp, vp, i64],
         "arb_moe_router_fwd": [vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
         "arb_moe_router_bwd": [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, vp],
         "arb_moe_slot_positions": [vp, i64, i32, vp, vp, vp, vp],
@@ -180,10 +188,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     if tuple(o2.shape) != (M, N) or out.dtype != (torch.float32 if f32_out else torch.bfloat16):
         raise ValueError("out has the wrong shape or dtype")
     so = out.stride(0) if batched else 0
+    pull = ahead = None
     if pending_pulls:
+        stream = _stream()
         pull = pending_pulls.pop(b.data_ptr(), None)
         if pull is not None:
-            _check(lib().arb_gemm_pull_next(pull[0], b.data_ptr(), pull[1]), "gemm_pull_next")
+            pull_use_order.setdefault(b.data_ptr(), len(pull_use_order))
+        if PULL_AHEAD and stream == pull_stream and pending_pulls:
+            dst = next(iter(pending_pulls))
+            ahead = (dst,) + pending_pulls.pop(dst)
+            pull_use_order.setdefault(dst, len(pull_use_order))
     auxp = 0
     if aux is not None:
         _bf16(aux, "aux")
@@ -191,11 +205,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         if ax2.stride(0) != o2.stride(0) or tuple(ax2.shape) != (M, N) or (batched and aux.stride(0) != so):
             raise ValueError("aux must have the layout of out")
         auxp = aux.data_ptr()
-    rc = lib().arb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), auxp, M, N, K, G,
-                             a2.stride(0), b2.stride(0), o2.stride(0), sa, sb, so,
-                             int(trans_a), int(not trans_b), epi, splitk, alpha, beta, gamma,
-                             err_flag(a.device).data_ptr(), _stream())
-    _check(rc, "arb_gemm_bf16")
+    try:
+        rc = lib().arb_gemm_bf16_ex(a.data_ptr(), b.data_ptr(), out.data_ptr(), auxp, M, N, K, G,
+                                    a2.stride(0), b2.stride(0), o2.stride(0), sa, sb, so,
+                                    int(trans_a), int(not trans_b), epi, splitk, alpha, beta, gamma,
+                                    err_flag(a.device).data_ptr(), _stream(),
+                                    pull[0] if pull else None, pull[1] if pull else 0,
+                                    ahead[1] if ahead else None, ahead[0] if ahead else None, ahead[2] if ahead else 0)
+        _check(rc, "arb_gemm_bf16")
+    except Exception:
+        # nothing was launched: the copies are still owed
+        if ahead is not None:
+            pending_pulls[ahead[0]] = ahead[1:]
+        if pull is not None:
+            pending_pulls[b.data_ptr()] = pull
+        raise
     return out
 
 

@@ -12,9 +12,11 @@ Per optimizer step, on the compute stream:
 4. the optimizer updates the owned matrices and writes bf16 parameters into the symmetric
    parameter buffer;
 5. a second barrier; the dense weight matrices (wqkv, wo, wfc, wdn: 99 % of the bytes) are NOT
-   copied here: each is registered as pending and the first GEMM that uses it as its B operand
-   pulls it from the owner's memory in its own prologue (``GemmArgs::pull_src``); one small kernel
-   pulls everything else (embeddings, head, scalars, gates, experts).
+   copied here: each is registered as pending and the GEMMs of the next forward pass copy them from
+   the owners' memory themselves: the first GEMM copies its own B operand in its prologue
+   (``GemmArgs::pull_src``), and a spare warp of every GEMM copies the operand of the NEXT GEMM while
+   the tiles are computed (``GemmArgs::ahead_src``), so the transfer hides under the math; one small
+   kernel pulls everything else (embeddings, head, scalars, gates, experts).
 
 The library arm (``LibraryComm``) does the same with ncclReduceScatter / ncclAllGather and is
 what this path is measured against.
@@ -168,8 +170,11 @@ class FusedComm:
         base = layout.flat_param.data_ptr()
         es = layout.flat_param.element_size()
         peers = self._param.peer_ptrs
-        for a, r in gemm_atoms:
+        # registered in the order in which the forward pass consumed them last time (unknown ones last), on this stream
+        order = K.pull_use_order
+        for a, r in sorted(gemm_atoms, key=lambda ar: order.get(base + ar[0].offset * es, 1 << 30)):
             K.pending_pulls[base + a.offset * es] = (peers[r] + a.offset * es, a.numel * es)
+        K.pull_stream = K._stream()
         if ranges:
             n = len(ranges)
             src = (C.c_void_p * n)(*[peers[r] + b0 for b0, _, r in ranges])

@@ -1,23 +1,30 @@
-"""Pipeline parallelism with a 1F1B schedule over point-to-point sends (NCCL on GPUs, gloo on
-CPU ranks).
+"""Pipeline parallelism, one process per stage, with a 1F1B schedule over point-to-point sends (NCCL on
+GPUs, gloo on CPU ranks).
 
-What is kept from the reference (brain/src/train.rs:1620-2029, brain/src/pipeline.rs:45-259):
-one rank per stage; layers split ``L // n`` with the remainder on the early stages; stage 0 owns
-the token embedding, the last stage owns the LM head and the loss; every stage keeps and
-updates only its own slice of ``resid_lambdas`` / ``x0_lambdas``; ``x`` and ``x0`` travel forward
-together; checkpoints go to ``stage_{i}/`` sub-directories.
+What is kept from the reference's multi-process driver (brain/src/train.rs:1620-2029): one rank per
+stage; layers split ``L // n`` with the remainder on the early stages; stage 0 owns the token
+embedding, the last stage owns the LM head and the loss; every stage keeps and updates only its own
+slice of ``resid_lambdas`` / ``x0_lambdas``; ``x`` and ``x0`` travel forward together; every rank
+writes its checkpoint to ``rank_{r}/`` (brain/src/train.rs:1998-2002).
 
 What is different: the reference runs one micro-batch through all stages strictly in sequence
-(bubble (n-1)/n) with blocking sends; here micro-batches are interleaved one-forward-one-backward
-and transfers are posted asynchronously so they overlap compute.  The gradient of ``x0`` is
-accumulated along the chain (each boundary carries d_x and d_x0 back) instead of every stage
-sending its partial sum to stage 0.  Pipeline stages can be combined with data parallelism:
-rank = dp_index * n_stages + stage.
+(bubble (n-1)/n) with blocking sends and logs wall-clock time only; here micro-batches are
+interleaved one-forward-one-backward, the receive of the NEXT pass is posted before the current
+pass is computed and sends are never waited for before the end of the step, so transfers run
+under compute.  Activations and gradients travel on two separate communicators (one per
+direction): on each of them a rank only ever sends to, or only ever receives from, a given
+neighbour, so an early-posted receive can never sit in front of the send its peer is waiting
+for.  The gradient of ``x0`` is accumulated along the chain (each boundary carries d_x and d_x0
+back) instead of every stage sending its partial sum to stage 0.  Pipeline stages can be combined
+with data parallelism (rank = dp_index * n_stages + stage), whose gradient exchange is the same
+fused peer-memory path as in the plain data-parallel trainer.  Loop, logging, timing, evaluation,
+checkpoint cadence and resume are the shared ones of ``TrainerBase``.
 """
 from __future__ import annotations
 
-import time
-from typing import List, Tuple
+import json
+from pathlib import Path
+from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -28,7 +35,8 @@ from ..models.gpt import GPT
 from ..models.init import init_weights
 from ..ops.backend import get_backend
 from ..optim.muon_adamw import MuonAdamW
-from ..optim.schedule import WSDState, lr_multiplier, warmup_multiplier
+from ..loop import TrainerBase
+from ..optim.schedule import WSDState, warmup_multiplier
 from .dp import LibraryComm, LocalComm
 from .layout import ParamLayout
 
@@ -59,7 +67,7 @@ def one_f_one_b(stage: int, n_stages: int, n_micro: int) -> List[Tuple[str, int]
     return sched
 
 
-class PipelineTrainer:
+class PipelineTrainer(TrainerBase):
     def __init__(self, mcfg: ModelConfig, tcfg: TrainConfig, pp: int, device: str = "cpu", quiet: bool = False):
         if not dist.is_initialized():
             raise RuntimeError("pipeline training needs an initialised process group (torchrun)")
@@ -70,20 +78,26 @@ class PipelineTrainer:
         self.dp = self.world // pp
         self.stage = self.rank % pp
         self.dp_idx = self.rank // pp
+        self.data_rank, self.data_world = self.dp_idx, self.dp
+        self.log_rank = self.world - 1            # the loss lives on the last stage (the reference logs there too)
         self.device = torch.device(device)
         self.quiet = quiet
         on_gpu = self.device.type == "cuda"
         impl = tcfg.impl
         if impl == "auto":
             impl = "sm100" if (on_gpu and torch.cuda.get_device_capability(self.device)[0] == 10) else "oracle"
+        self.impl = impl
         self.dtype = torch.bfloat16 if on_gpu and impl != "oracle" else torch.float32
         self.backend = get_backend(impl, mcfg)
-        # process groups: one DP group per stage (collective creation: every rank calls all)
+        # process groups (collective creation: every rank calls all): one DP group per stage, and one
+        # communicator per transfer direction
         self.dp_group = None
         for s in range(pp):
             g = dist.new_group([d * pp + s for d in range(self.dp)])
             if s == self.stage:
                 self.dp_group = g
+        self.fwd_group = dist.new_group()
+        self.bwd_group = dist.new_group()
         lo, hi = split_layers(mcfg.n_layer, pp)[self.stage]
         self.first, self.last = self.stage == 0, self.stage == pp - 1
         self.model = GPT(mcfg, self.backend, dtype=self.dtype, device=self.device, layer_range=(lo, hi),
@@ -91,26 +105,31 @@ class PipelineTrainer:
         self._init_stage_weights()
         self.micro_batch, self.accum = derive_accumulation(tcfg.total_batch_size, tcfg.device_batch_size,
                                                            mcfg.seq_len, self.dp)
-        self.comm = LocalComm() if self.dp == 1 else LibraryComm(self.dp_group,
-                                                                 torch.bfloat16 if on_gpu else None)
-        self.layout = ParamLayout(self.model.named_matrix_groups(), self.dp, self.dp_idx)
+        fused = tcfg.parallel.comm == "fused" and on_gpu and impl == "sm100"
+        if self.dp == 1:
+            self.comm = LocalComm()
+        elif fused:
+            from .fused_dp import FusedComm
+            self.comm = FusedComm(self.dp_group, self.device)
+        else:
+            self.comm = LibraryComm(self.dp_group, torch.bfloat16 if on_gpu else None)
+        self.layout = ParamLayout(self.model.named_matrix_groups(), self.dp, self.dp_idx,
+                                  allocator=getattr(self.comm, "allocator", None))
+        if hasattr(self.comm, "attach"):
+            self.comm.attach(self.layout)
         kernels = getattr(self.backend, "optim_kernels", None)
         self.opt = MuonAdamW(self.layout, tcfg.schedule_cfg, mcfg.d_model, kernels=kernels() if callable(kernels) else None)
         self.wsd = WSDState(tcfg.max_steps, tcfg.cooldown_steps, tcfg.schedule_cfg.warmdown_ratio,
                             int(round(tcfg.schedule_cfg.warmup_ratio * (tcfg.max_steps or 0))))
-        self.step = 0
-        from ..trainer import Trainer
-        self.loader = Trainer._make_loader(self._loader_shim(), "train")
         self.sched = one_f_one_b(self.stage, pp, self.accum)
         self.comm_bytes = 0
-
-    # the single-GPU trainer's loader factory only needs these attributes
-    def _loader_shim(self):
-        class S: pass
-        s = S()
-        s.tcfg, s.mcfg, s.micro_batch = self.tcfg, self.mcfg, self.micro_batch
-        s.rank, s.world = self.dp_idx, self.dp
-        return s
+        self._init_common()
+        # every micro-batch of a step is staged up front (a stage needs batch i again for its backward)
+        B, T = self.micro_batch, mcfg.seq_len
+        self._d = [(torch.empty(B, T, dtype=torch.int32, device=self.device),
+                    torch.empty(B, T, dtype=torch.int32, device=self.device)) for _ in range(self.accum)]
+        if tcfg.resume and tcfg.checkpoint_dir:
+            self._resume()
 
     def _init_stage_weights(self):
         """Initialise the full model once per rank with the shared seed and keep this stage's
@@ -120,7 +139,10 @@ class PipelineTrainer:
             ckpt.load_weights(self.model, t.load_checkpoint, strict=True)
             return
         full = GPT(self.mcfg, get_backend("oracle", self.mcfg), dtype=torch.float32, device="cpu")
-        init_weights(full, seed=t.seed, scheme=getattr(t, "init_scheme", "reference"))
+        if t.init_weights_path:
+            ckpt.load_weights(full, t.init_weights_path, strict=False)
+        else:
+            init_weights(full, seed=t.seed, scheme=getattr(t, "init_scheme", "reference"))
         src = dict(full.named_parameters())
         lo = self.model.layer_lo
         with torch.no_grad():
@@ -135,56 +157,73 @@ class PipelineTrainer:
                     p.copy_(src[n])
         del full
 
-    # ------------------------------------------------------------------
-    def _send(self, tensors, dst_stage) -> list:
-        dst = self.dp_idx * self.pp + dst_stage
+    # ---- transfers ----------------------------------------------------------------------------------
+    def _peer(self, stage: int) -> int:
+        return self.dp_idx * self.pp + stage
+
+    def _send(self, tensors, dst_stage: int, group) -> list:
         hs = []
         for t in tensors:
             t = t.contiguous()
             self.comm_bytes += t.numel() * t.element_size()
-            hs.append((dist.isend(t, dst), t))
+            hs.append((dist.isend(t, self._peer(dst_stage), group=group), t))
         return hs
 
-    def _recv(self, shapes, src_stage) -> list:
-        src = self.dp_idx * self.pp + src_stage
+    def _post_recv(self, op, act_shape) -> list:
+        """Receives that pass `op` of the schedule needs: activations (x, x0) from the previous stage for a forward,
+        gradients (d_x, d_x0) from the next stage for a backward."""
+        kind, _ = op
+        if kind == "F" and not self.first:
+            src, group = self._peer(self.stage - 1), self.fwd_group
+        elif kind == "B" and not self.last:
+            src, group = self._peer(self.stage + 1), self.bwd_group
+        else:
+            return []
         out = []
-        for shp in shapes:
-            buf = torch.empty(shp, dtype=self.dtype, device=self.device)
-            out.append((dist.irecv(buf, src), buf))
+        for _ in range(2):
+            buf = torch.empty(act_shape, dtype=self.dtype, device=self.device)
+            out.append((dist.irecv(buf, src, group=group), buf))
         return out
 
     def train_step(self):
         m = self.mcfg
-        self.wsd.update(self.step)
+        self._pre_step()
+        if not self.step_data_ready():
+            return None
+        self.timer.mark("start")
+        self.wsd.update(self.step, triggered=self._cooldown_triggered())
         self.layout.zero_grad()
         B, T, D = self.micro_batch, m.seq_len, m.d_model
         act_shape = (B * T, D)
         tokens_micro = B * T
         grad_scale = 1.0 / (tokens_micro * self.accum * self.dp)
-        batches = [self.loader.next_batch() for _ in range(self.accum)]
-        if any(b is None for b in batches):
-            return None
-        batches = [(i.to(self.device), t.to(self.device)) for i, t in batches]
+        batches = [self._stage_batch(i) for i in range(self.accum)]
         saved = {}
         pending = []
-        loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
-        for kind, i in self.sched:
+        self._loss_acc.zero_()
+        sched = self.sched
+        posted = {0: self._post_recv(sched[0], act_shape)}
+        for k, (kind, i) in enumerate(sched):
+            if k + 1 < len(sched):                                 # the next pass's inputs travel under this pass
+                posted[k + 1] = self._post_recv(sched[k + 1], act_shape)
+            got = posted.pop(k)
+            for h, _buf in got:
+                h.wait()
             ids, tgt = batches[i]
             if kind == "F":
                 if self.first:
                     x_in = x0_in = None
                 else:
-                    (hx, x_in), (h0, x0_in) = self._recv([act_shape, act_shape], self.stage - 1)
-                    hx.wait(); h0.wait()
+                    x_in, x0_in = got[0][1], got[1][1]
                     x_in.requires_grad_(True); x0_in.requires_grad_(True)
                 out = self.model(ids, tgt, grad_scale=grad_scale, x_in=x_in, x0_in=x0_in)
                 if self.last:
                     scaled, per_tok = out
-                    loss_acc += per_tok.sum() / (tokens_micro * self.accum)
+                    self._loss_acc += per_tok.sum() / (tokens_micro * self.accum)
                     saved[i] = (x_in, x0_in, scaled, None)
                 else:
                     x_out, x0_out = out
-                    pending += self._send([x_out.detach(), x0_out.detach()], self.stage + 1)
+                    pending += self._send([x_out.detach(), x0_out.detach()], self.stage + 1, self.fwd_group)
                     saved[i] = (x_in, x0_in, x_out, x0_out)
             else:
                 x_in, x0_in, y, x0_out = saved.pop(i)
@@ -192,8 +231,7 @@ class PipelineTrainer:
                     y.backward()
                     d_x0_down = None
                 else:
-                    (hx, d_x), (h0, d_x0_down) = self._recv([act_shape, act_shape], self.stage + 1)
-                    hx.wait(); h0.wait()
+                    d_x, d_x0_down = got[0][1], got[1][1]
                     if self.first:
                         # x0_out is the embedding output itself: both gradients enter the graph
                         torch.autograd.backward([y, x0_out], [d_x, d_x0_down])
@@ -204,47 +242,108 @@ class PipelineTrainer:
                     g0 = x0_in.grad if x0_in.grad is not None else torch.zeros_like(x0_in)
                     if d_x0_down is not None:
                         g0 = g0 + d_x0_down
-                    pending += self._send([x_in.grad, g0], self.stage - 1)
+                    pending += self._send([x_in.grad, g0], self.stage - 1, self.bwd_group)
         for h, _keep in pending:
             h.wait()
+        self.timer.mark("bwd_end")
         self.comm.reduce_scatter_grads(self.layout)
         progress = self.wsd.progress(self.step)
-        self.opt.step(self.step + 1, progress, warmup_multiplier(self.step + 1, self.wsd.warmup_steps))
+        gs = self.comm.grad_source(self.layout) if hasattr(self.comm, "grad_source") else None
+        self.opt.step(self.step + 1, progress, warmup_multiplier(self.step + 1, self.wsd.warmup_steps), grad_source=gs)
         self.comm.all_gather_params(self.layout)
+        self.timer.mark("opt_end")
+        self.timer.mark("end")
         self.step += 1
-        return loss_acc
+        return self._loss_acc
 
-    def loss_on_all_ranks(self, loss: torch.Tensor) -> float:
+    def _stage_batch(self, micro: int):
+        got = self.prefetch.next()
+        slot, h_ids, h_tgt = got
+        d_ids, d_tgt = self._d[micro]
+        d_ids.copy_(h_ids, non_blocking=True)
+        d_tgt.copy_(h_tgt, non_blocking=True)
+        ev = None
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+        self.prefetch.release(slot, ev)
+        return d_ids, d_tgt
+
+    def global_loss(self, loss: torch.Tensor) -> float:
         """The loss lives on the last stage; share it (mean over DP replicas)."""
         v = loss.detach().clone() if self.last else torch.zeros((), dtype=torch.float32, device=self.device)
         dist.all_reduce(v)
         return float(v.item()) / self.dp
 
-    def run(self):
-        t = self.tcfg
-        tokens = self.micro_batch * self.mcfg.seq_len * self.accum * self.dp
-        if self.rank == 0 and not self.quiet:
-            print(f"Pipeline: {self.pp} stages x dp {self.dp}; stage layers {split_layers(self.mcfg.n_layer, self.pp)}; "
-                  f"{self.accum} micro-batches of {self.micro_batch} sequences (1F1B)", flush=True)
-        ema, n = 0.0, 0
-        while not self.wsd.finished(self.step):
-            t0 = time.perf_counter()
-            loss = self.train_step()
-            if loss is None:
-                break
-            if self.device.type == "cuda":
-                torch.cuda.synchronize()
-            dt = time.perf_counter() - t0
-            step = self.step - 1
-            if step % t.log_interval == 0 or step <= 10:
-                lv = self.loss_on_all_ranks(loss)
-                ema = 0.9 * ema + 0.1 * lv; n += 1
-                if self.rank == self.world - 1 and not self.quiet:
-                    lrm = lr_multiplier(self.wsd.progress(step), t.schedule_cfg)
-                    left = (t.max_steps - self.step) if t.max_steps else -1
-                    print(f"step {step:>5} | loss {ema / (1 - 0.9 ** n):.4f} | lr {lrm:.3f} | dt {dt:.3f}s | "
-                          f"tok/s {int(tokens / dt)} | mfu 0.0% | vram 0MB | steps_left {left}", flush=True)
-        if t.checkpoint_dir and not t.synthetic_data and self.dp_idx == 0:
-            p = ckpt.save_checkpoint(self.model, t.checkpoint_dir, subdir=f"stage_{self.stage}")
-            print(f"[checkpoint] saved {p}", flush=True)
+    loss_on_all_ranks = global_loss
+
+    def banner(self):
+        m = self.mcfg
+        return [f"Model: {m.name} {m.num_params()['total'] / 1e6:.1f}M params, impl={self.impl}, "
+                f"dtype={str(self.dtype).split('.')[-1]}, world={self.world}",
+                f"Pipeline: {self.pp} stages x dp {self.dp} ({self.comm.name}); stage layers "
+                f"{split_layers(m.n_layer, self.pp)}; {self.accum} micro-batches of {self.micro_batch} sequences (1F1B) = "
+                f"{self.tokens_per_step} tokens/step"]
+
+    # ---- evaluation: a forward-only pass down the pipeline; the last stage scores ---------------------
+    def evaluate(self, max_batches: Optional[int]) -> float:
+        from ..eval.bpb import eval_bpb, load_token_bytes
+        if self.token_bytes is None:
+            self.token_bytes = load_token_bytes(self.tcfg.tokenizer_dir, self.mcfg.vocab, self.device)
+        act_shape = (self.micro_batch * self.mcfg.seq_len, self.mcfg.d_model)
+
+        def forward(ids, tgt):
+            x_in = x0_in = None
+            if not self.first:
+                got = self._post_recv(("F", 0), act_shape)
+                for h, _b in got:
+                    h.wait()
+                x_in, x0_in = got[0][1], got[1][1]
+            out = self.model(ids, tgt, x_in=x_in, x0_in=x0_in)
+            if self.last:
+                return out[1], tgt
+            for h, _t in self._send([out[0], out[1]], self.stage + 1, self.fwd_group):
+                h.wait()
+            return torch.zeros(0, device=self.device), tgt.reshape(-1)[:0]
+
+        return eval_bpb(self.model, self._make_loader("val"), self.token_bytes, max_batches, self.device,
+                        group=dist.group.WORLD, forward=forward)
+
+    # ---- checkpoints: every rank its own directory ------------------------------------------------------
+    def _dir(self) -> Path:
+        return Path(self.tcfg.checkpoint_dir) / f"rank_{self.rank}"
+
+    def save(self, step: Optional[int] = None) -> Optional[str]:
+        if hasattr(self.comm, "flush"):
+            self.comm.flush()
+        state = dict(step=self.step, loss_ema=self.loss_ema, ema_steps=self.ema_steps, wsd=self.wsd.state_dict(),
+                     pp=self.pp, dp=self.dp, stage=self.stage, data=self.prefetch.state_dict())
+        path = ckpt.save_checkpoint(self.model, self.tcfg.checkpoint_dir, step=step, optimizer=self.opt,
+                                    trainer_state=state, subdir=f"rank_{self.rank}")
         dist.barrier()
+        # the logging rank reports its own file; every rank has written one
+        return path
+
+    def _resume(self):
+        from ..ckpt.safetensors_io import load_file
+        d = self._dir()
+        p = d / "model.safetensors"
+        if not p.exists():
+            return
+        ckpt.load_weights(self.model, str(p), strict=True)
+        for gi, st in self.opt.state.items():
+            st["master"].copy_(self.layout.group_view(self.layout.flat_param, self.layout.groups[gi]).float())
+        if (d / "optim_state.safetensors").exists():
+            self.opt.load_state_dict(load_file(str(d / "optim_state.safetensors")))
+            for gi, st in self.opt.state.items():           # exact parameters from the fp32 masters
+                self.layout.group_view(self.layout.flat_param, self.layout.groups[gi]).copy_(st["master"])
+            self.comm.all_gather_params(self.layout)
+        sp = d / "trainer_state.json"
+        if sp.exists():
+            st = json.loads(sp.read_text())
+            self.step = int(st["step"])
+            self.loss_ema, self.ema_steps = st.get("loss_ema", 0.0), st.get("ema_steps", 0)
+            self.wsd.load_state_dict(st["wsd"])
+            if st.get("data") and hasattr(self.train_loader, "load_state_dict"):
+                self.prefetch.load_state_dict(st["data"])
+        self._say(f"Resumed from {d} at step {self.step}")

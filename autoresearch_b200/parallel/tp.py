@@ -24,7 +24,8 @@ weights.  Two communication arms:
 from __future__ import annotations
 
 import ctypes as C
-import time
+import json
+from pathlib import Path
 from typing import List, Optional
 
 import torch
@@ -35,7 +36,8 @@ from ..models.gpt import GPT
 from ..models.init import init_weights
 from ..ops.backend import get_backend
 from ..optim.muon_adamw import MuonAdamW
-from ..optim.schedule import WSDState, lr_multiplier, warmup_multiplier
+from ..loop import TrainerBase
+from ..optim.schedule import WSDState, warmup_multiplier
 from .dp import LibraryComm, LocalComm
 from .layout import ParamLayout
 
@@ -304,8 +306,9 @@ def gather_full_model(model: GPT, tp_group, tp_rank: int, tp: int) -> Optional[G
 REPLICATED_KINDS = ("adamw_emb", "adamw_head", "adamw_lr", "adamw_l0", "adamw_router")
 
 
-class TPTrainer:
-    """world = tp x dp; rank = dp_index * tp + tp_rank.  A TP group shares one micro-batch."""
+class TPTrainer(TrainerBase):
+    """world = tp x dp; rank = dp_index * tp + tp_rank.  A TP group shares one micro-batch.  The step loop, logging,
+    timing, evaluation and checkpoint cadence are the shared ones of ``TrainerBase``."""
 
     def __init__(self, mcfg: ModelConfig, tcfg: TrainConfig, tp: int, device: str = "cpu", quiet: bool = False):
         if not dist.is_initialized():
@@ -318,12 +321,14 @@ class TPTrainer:
             raise ValueError("world size and head count must be multiples of tp")
         self.dp = self.world // tp
         self.tp_rank, self.dp_idx = self.rank % tp, self.rank // tp
+        self.data_rank, self.data_world = self.dp_idx, self.dp
         self.device = torch.device(device)
         self.quiet = quiet
         on_gpu = self.device.type == "cuda"
         impl = tcfg.impl
         if impl == "auto":
             impl = "sm100" if (on_gpu and torch.cuda.get_device_capability(self.device)[0] == 10) else "oracle"
+        self.impl = impl
         self.dtype = torch.bfloat16 if on_gpu and impl != "oracle" else torch.float32
         self.tp_group = self.dp_group = None
         for d in range(self.dp):
@@ -340,75 +345,166 @@ class TPTrainer:
         if n_tokens % tp:
             raise ValueError("tokens per micro-batch must divide over tp")
         self.backend = get_backend(impl, mcfg)
-        if tcfg.parallel.comm == "fused" and on_gpu and impl == "sm100":
+        fused = tcfg.parallel.comm == "fused" and on_gpu and impl == "sm100"
+        if fused:
             self.backend.tp = FusedTPContext(self.tp_group, self.tp_rank, tp, self.device, n_tokens, mcfg.d_model)
         else:
             self.backend.tp = TPContext(self.tp_group, self.tp_rank, tp)
         self.model = GPT(mcfg, self.backend, dtype=self.dtype, device=self.device, tp=tp)
         full = GPT(mcfg, get_backend("oracle", mcfg), dtype=torch.float32, device="cpu")
-        init_weights(full, seed=tcfg.seed, scheme=getattr(tcfg, "init_scheme", "reference"))
+        if tcfg.load_checkpoint or tcfg.init_weights_path:
+            from ..ckpt import checkpoint as ckpt
+            ckpt.load_weights(full, tcfg.load_checkpoint or tcfg.init_weights_path, strict=bool(tcfg.load_checkpoint))
+        else:
+            init_weights(full, seed=tcfg.seed, scheme=getattr(tcfg, "init_scheme", "reference"))
         shard_full_model_into(full, self.model, self.tp_rank, tp)
         del full
         groups = self.model.named_matrix_groups()
         rep = [g for g in groups if g[2] in REPLICATED_KINDS]
         shd = [g for g in groups if g[2] not in REPLICATED_KINDS]
-        bucket = torch.bfloat16 if on_gpu else None
-        # replicated parameters: reduced over ALL ranks; sharded ones over the DP group of this TP index
-        self.comm_rep = LibraryComm(None, bucket)
-        self.lay_rep = ParamLayout(rep, self.world, self.rank)
-        self.comm_shd = LocalComm() if self.dp == 1 else LibraryComm(self.dp_group, bucket)
-        self.lay_shd = ParamLayout(shd, self.dp, self.dp_idx)
+        # replicated parameters: gradients summed over ALL ranks; sharded ones over the DP group of this TP index.
+        # With the peer-memory arm both exchanges are the fused data-parallel path (reduce-scatter inside the
+        # optimizer kernels, all-gather inside the consuming GEMMs), each over its own group.
+        self.comm_rep = self._make_dp_comm(None, self.world, fused)
+        self.lay_rep = ParamLayout(rep, self.world, self.rank, allocator=getattr(self.comm_rep, "allocator", None))
+        if hasattr(self.comm_rep, "attach"):
+            self.comm_rep.attach(self.lay_rep)
+        self.comm_shd = self._make_dp_comm(self.dp_group, self.dp, fused)
+        self.lay_shd = ParamLayout(shd, self.dp, self.dp_idx, allocator=getattr(self.comm_shd, "allocator", None))
+        if hasattr(self.comm_shd, "attach"):
+            self.comm_shd.attach(self.lay_shd)
         kernels = getattr(self.backend, "optim_kernels", None)
         kk = kernels() if callable(kernels) else None
         self.opt_rep = MuonAdamW(self.lay_rep, tcfg.schedule_cfg, mcfg.d_model, kernels=kk)
         self.opt_shd = MuonAdamW(self.lay_shd, tcfg.schedule_cfg, mcfg.d_model, kernels=kk)
         self.wsd = WSDState(tcfg.max_steps, tcfg.cooldown_steps, tcfg.schedule_cfg.warmdown_ratio,
                             int(round(tcfg.schedule_cfg.warmup_ratio * (tcfg.max_steps or 0))))
-        self.step = 0
-        from ..trainer import Trainer
-        shim = type("S", (), {})()
-        shim.tcfg, shim.mcfg, shim.micro_batch, shim.rank, shim.world = tcfg, mcfg, self.micro_batch, self.dp_idx, self.dp
-        self.loader = Trainer._make_loader(shim, "train")
+        self._init_common()
+        self.h2d_bytes_per_step = 2 * self.micro_batch * mcfg.seq_len * 4 * self.accum
+        if tcfg.resume and tcfg.checkpoint_dir:
+            self._resume()
+
+    def _make_dp_comm(self, group, size: int, fused: bool):
+        if size == 1:
+            return LocalComm()
+        if fused:
+            from .fused_dp import FusedComm
+            return FusedComm(group, self.device)
+        return LibraryComm(group, torch.bfloat16 if self.device.type == "cuda" else None)
+
+    @property
+    def comm_name(self) -> str:
+        return f"tp-{self.backend.tp.mode}+dp-{self.comm_shd.name if self.dp > 1 else self.comm_rep.name}"
+
+    @property
+    def comm_bytes(self) -> int:
+        return int(self.backend.tp.bytes)
 
     def train_step(self):
         m = self.mcfg
-        self.wsd.update(self.step)
+        self._pre_step()
+        if not self.step_data_ready():
+            return None
+        self.timer.mark("start")
+        self.wsd.update(self.step, triggered=self._cooldown_triggered())
         self.lay_rep.zero_grad(); self.lay_shd.zero_grad()
         n_tokens = self.micro_batch * m.seq_len
         grad_scale = 1.0 / (n_tokens * self.accum * self.dp)
-        loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
-        for _ in range(self.accum):
-            b = self.loader.next_batch()
-            if b is None:
-                return None
-            ids, tgt = (t.to(self.device) for t in b)
+        self._loss_acc.zero_()
+        for micro in range(self.accum):
+            ids, tgt = self._stage_batch(micro)
             scaled, per_tok = self.model(ids, tgt, grad_scale=grad_scale)
             scaled.backward()
             self.lay_rep.accumulate_autograd_grads(); self.lay_shd.accumulate_autograd_grads()
-            loss_acc += per_tok.sum() / (n_tokens * self.accum)
+            self._loss_acc += per_tok.sum() / (n_tokens * self.accum)
+        self.timer.mark("bwd_end")
         self.comm_rep.reduce_scatter_grads(self.lay_rep)
         self.comm_shd.reduce_scatter_grads(self.lay_shd)
         progress = self.wsd.progress(self.step)
         wm = warmup_multiplier(self.step + 1, self.wsd.warmup_steps)
-        self.opt_rep.step(self.step + 1, progress, wm)
-        self.opt_shd.step(self.step + 1, progress, wm)
+        src = lambda c, lay: c.grad_source(lay) if hasattr(c, "grad_source") else None
+        self.opt_rep.step(self.step + 1, progress, wm, grad_source=src(self.comm_rep, self.lay_rep))
+        self.opt_shd.step(self.step + 1, progress, wm, grad_source=src(self.comm_shd, self.lay_shd))
         self.comm_rep.all_gather_params(self.lay_rep)
         self.comm_shd.all_gather_params(self.lay_shd)
+        self.timer.mark("opt_end")
+        self.timer.mark("end")
         self.step += 1
-        return loss_acc
+        return self._loss_acc
+
+    # ---- evaluation: every rank scores its token shard of its replica's batch -----------------------
+    def evaluate(self, max_batches: Optional[int]) -> float:
+        from ..eval.bpb import eval_bpb, load_token_bytes
+        if self.token_bytes is None:
+            self.token_bytes = load_token_bytes(self.tcfg.tokenizer_dir, self.mcfg.vocab, self.device)
+        n = (self.micro_batch * self.mcfg.seq_len) // self.tp
+        shard = slice(self.tp_rank * n, (self.tp_rank + 1) * n)
+
+        def forward(ids, tgt):
+            _, per_tok = self.model(ids, tgt)
+            return per_tok, tgt.reshape(-1)[shard]
+
+        return eval_bpb(self.model, self._make_loader("val"), self.token_bytes, max_batches, self.device,
+                        group=dist.group.WORLD, forward=forward)
+
+    # ---- checkpoints --------------------------------------------------------------------------------
+    def _flush(self):
+        for c in (self.comm_rep, self.comm_shd):
+            if hasattr(c, "flush"):
+                c.flush()
 
     def save(self, step: Optional[int] = None) -> Optional[str]:
-        """One standard checkpoint file (full, unsharded tensors), written by rank 0; the TP group of the first
-        DP replica gathers its shards (collective within that group)."""
+        """One standard checkpoint file (full, unsharded tensors), written by rank 0: the TP group of the first
+        DP replica gathers its shards (collective within that group).  Optimizer state is written per rank."""
         from ..ckpt import checkpoint as ckpt
+        from ..ckpt.safetensors_io import save_file
+        self._flush()
+        d = Path(self.tcfg.checkpoint_dir)
+        d.mkdir(parents=True, exist_ok=True)
+        osd = dict(self.opt_rep.state_dict())
+        osd.update(self.opt_shd.state_dict())
+        save_file(osd, str(d / f"optim_state.rank{self.rank}.safetensors"))
         path = None
         if self.dp_idx == 0:
             full = gather_full_model(self.model, self.tp_group, self.tp_rank, self.tp)
             if full is not None:
-                path = ckpt.save_checkpoint(full, self.tcfg.checkpoint_dir, step=step,
-                                            trainer_state=dict(step=self.step, wsd=self.wsd.state_dict(), tp=self.tp, dp=self.dp))
+                state = dict(step=self.step, loss_ema=self.loss_ema, ema_steps=self.ema_steps, wsd=self.wsd.state_dict(),
+                             tp=self.tp, dp=self.dp, world=self.world, data=self.prefetch.state_dict())
+                path = ckpt.save_checkpoint(full, str(d), step=step, trainer_state=state)
         dist.barrier()
         return path
+
+    def _resume(self):
+        from ..ckpt import checkpoint as ckpt
+        from ..ckpt.safetensors_io import load_file
+        d = Path(self.tcfg.checkpoint_dir)
+        p = d / "model.safetensors"
+        if not p.exists():
+            return
+        full = GPT(self.mcfg, get_backend("oracle", self.mcfg), dtype=torch.float32, device="cpu")
+        ckpt.load_weights(full, str(p), strict=True)
+        shard_full_model_into(full, self.model, self.tp_rank, self.tp)
+        del full
+        for opt, lay in ((self.opt_rep, self.lay_rep), (self.opt_shd, self.lay_shd)):
+            for gi, st in opt.state.items():
+                st["master"].copy_(lay.group_view(lay.flat_param, lay.groups[gi]).float())
+        f = d / f"optim_state.rank{self.rank}.safetensors"
+        sp = d / "trainer_state.json"
+        if sp.exists():
+            st = json.loads(sp.read_text())
+            if f.exists() and (st.get("tp"), st.get("world")) == (self.tp, self.world):
+                sd = load_file(str(f))
+                for opt, lay, comm in ((self.opt_rep, self.lay_rep, self.comm_rep), (self.opt_shd, self.lay_shd, self.comm_shd)):
+                    opt.load_state_dict(sd)
+                    for gi, ost in opt.state.items():       # exact parameters from the fp32 masters
+                        lay.group_view(lay.flat_param, lay.groups[gi]).copy_(ost["master"])
+                    comm.all_gather_params(lay)
+            self.step = int(st["step"])
+            self.loss_ema, self.ema_steps = st.get("loss_ema", 0.0), st.get("ema_steps", 0)
+            self.wsd.load_state_dict(st["wsd"])
+            if st.get("data") and hasattr(self.train_loader, "load_state_dict"):
+                self.prefetch.load_state_dict(st["data"])
+        self._say(f"Resumed from {d} at step {self.step}")
 
     def global_loss(self, loss: torch.Tensor) -> float:
         """Each rank holds the loss of its token shard (already divided by the full micro-batch
@@ -417,32 +513,9 @@ class TPTrainer:
         dist.all_reduce(v)
         return float(v.item()) / self.dp
 
-    def run(self):
-        t = self.tcfg
-        tokens = self.micro_batch * self.mcfg.seq_len * self.accum * self.dp
-        if self.rank == 0 and not self.quiet:
-            print(f"Tensor parallel: tp {self.tp} x dp {self.dp} ({self.backend.tp.mode} collectives); "
-                  f"{self.micro_batch} x {self.mcfg.seq_len} x accum {self.accum} per TP group", flush=True)
-        ema, n = 0.0, 0
-        while not self.wsd.finished(self.step):
-            t0 = time.perf_counter()
-            loss = self.train_step()
-            if loss is None:
-                break
-            if self.device.type == "cuda":
-                torch.cuda.synchronize()
-            dt = time.perf_counter() - t0
-            step = self.step - 1
-            if step % t.log_interval == 0 or step <= 10:
-                lv = self.global_loss(loss)
-                ema = 0.9 * ema + 0.1 * lv; n += 1
-                if self.rank == 0 and not self.quiet:
-                    lrm = lr_multiplier(self.wsd.progress(step), t.schedule_cfg)
-                    left = (t.max_steps - self.step) if t.max_steps else -1
-                    print(f"step {step:>5} | loss {ema / (1 - 0.9 ** n):.4f} | lr {lrm:.3f} | dt {dt:.3f}s | "
-                          f"tok/s {int(tokens / dt)} | mfu 0.0% | vram 0MB | steps_left {left}", flush=True)
-        if t.checkpoint_dir and not t.synthetic_data:
-            p = self.save()
-            if self.rank == 0 and not self.quiet:
-                print(f"[checkpoint] saved {p}", flush=True)
-        dist.barrier()
+    def banner(self):
+        m = self.mcfg
+        return [f"Model: {m.name} {m.num_params()['total'] / 1e6:.1f}M params, impl={self.impl}, "
+                f"dtype={str(self.dtype).split('.')[-1]}, world={self.world}",
+                f"Tensor parallel: tp {self.tp} x dp {self.dp} ({self.comm_name}); "
+                f"{self.micro_batch} x {m.seq_len} x accum {self.accum} per TP group = {self.tokens_per_step} tokens/step"]

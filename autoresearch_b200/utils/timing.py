@@ -6,9 +6,8 @@ The reference records four events per step and reads them only when it logs
 """
 from __future__ import annotations
 
-import json
+import os as _os
 import time
-from pathlib import Path
 
 import torch
 
@@ -38,15 +37,22 @@ class PhaseTimer:
                 (w["end"] - w["start"]) * 1e3)
 
 
-def measured_peak_flops(default: float = 1.59e15) -> float:
-    """bf16 tensor peak used as the MFU denominator: the pool's measured cuBLAS burst
-    throughput when the driver-written file is present, otherwise the fallback figure."""
-    for p in (Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json",):
-        try:
-            return float(json.loads(p.read_text())["bf16_tflops"]) * 1e12
-        except Exception:
-            pass
-    return default
+B200_NOMINAL_BF16_FLOPS = 2.25e15   # dense bf16 tensor peak of one B200 (the reference hard-codes its H100's 990e12)
+
+
+def resolve_peak_flops(explicit: "float | None" = None) -> float:
+    """MFU denominator per GPU: the configured value (TrainConfig.peak_flops), else the environment variable
+    ARB_PEAK_TFLOPS, else the nominal dense bf16 peak of a B200.  A benchmark that wants MFU against a measured
+    matmul rate passes that rate in."""
+    if explicit:
+        return float(explicit)
+    env = _os.environ.get("ARB_PEAK_TFLOPS", "")
+    try:
+        if env and float(env) > 0:
+            return float(env) * 1e12
+    except ValueError:
+        pass
+    return B200_NOMINAL_BF16_FLOPS
 
 
 def vram_mb() -> float:
@@ -61,7 +67,6 @@ def vram_mb() -> float:
 # package keeps as PhaseTimer; the reference has no NVTX).  Off by default: a range push/pop costs host time in the
 # launch path.
 import contextlib as _contextlib
-import os as _os
 
 NVTX = _os.environ.get("ARB_NVTX", "0") == "1"
 

@@ -143,3 +143,45 @@ def test_gemm_pulls_its_b_operand_in_the_prologue(shape):
     K.flush_pending_pulls()
     torch.cuda.synchronize()
     assert torch.equal(w, w_new) and not K.pending_pulls
+
+
+@pytest.mark.parametrize("shape", [(1024, 512, 256), (4096, 3072, 1024)])
+def test_gemm_copies_the_next_operand_while_it_computes(shape):
+    """With two operands pending, the first GEMM copies its own B in the prologue and, in a spare warp, the
+    OTHER pending operand while its tiles run; the second GEMM then finds its operand local already."""
+    from autoresearch_b200.ops import kernels as K
+    M, N, Kd = shape
+    torch.manual_seed(4)
+    x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
+    new = [(torch.randn(N, Kd, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(2)]
+    # the second operand's size is not a multiple of the copy loop's stride: exercises its tail
+    new.append((torch.randn(N + 8, Kd, device="cuda") * 0.05).to(torch.bfloat16))
+    stale = [torch.zeros_like(w) for w in new]
+    K.pending_pulls.clear()
+    for s, w in zip(stale, new):
+        K.pending_pulls[s.data_ptr()] = (w.data_ptr(), w.numel() * 2)
+    K.pull_stream = K._stream()
+    y0 = K.gemm(x, stale[0])
+    assert len(K.pending_pulls) == 1                  # own operand + one ahead
+    torch.cuda.synchronize()
+    assert torch.equal(stale[0], new[0]) and torch.equal(stale[1], new[1]) and stale[2].abs().max().item() == 0
+    y1 = K.gemm(x, stale[1])                          # nothing pending for it; copies operand 2 ahead
+    assert not K.pending_pulls
+    y2 = K.gemm(x, stale[2])
+    torch.cuda.synchronize()
+    K.check_err_flag()
+    assert torch.equal(stale[2], new[2])
+    for y, w in zip((y0, y1, y2), new):
+        ref = x.float() @ w.float().t()
+        assert ((y.float() - ref).norm() / ref.norm()).item() < 1e-2
+    # a GEMM on another stream leaves the ahead copies to the stream they were registered on
+    stale[1].zero_()
+    K.pending_pulls[stale[1].data_ptr()] = (new[1].data_ptr(), new[1].numel() * 2)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        K.gemm(x, stale[0])
+    assert len(K.pending_pulls) == 1
+    K.flush_pending_pulls()
+    torch.cuda.synchronize()
+    assert torch.equal(stale[1], new[1])

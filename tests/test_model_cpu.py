@@ -225,8 +225,8 @@ def test_trainer_resume_is_exact(tmp_path):
     assert c.step == 3
     rest = [float(c.train_step()) for _ in range(3)]
     assert first == full[:3]
-    # weights travel through bf16 in the checkpoint file; the optimizer's fp32 masters do not
-    assert all(abs(x - y) < 2e-2 for x, y in zip(rest, full[3:])), (rest, full[3:])
+    # the weight file holds bf16 roundings, but the parameters are rebuilt from the saved fp32 masters
+    assert rest == full[3:], (rest, full[3:])
 
 
 DP_WORKER = r"""
