@@ -117,7 +117,18 @@ def main(argv: Optional[List[str]] = None) -> int:
     pp = max(t.n_pipeline_stages, 1)
     if t.distributed and pp == 1:
         pp = world  # the reference's --distributed mode: every rank is a pipeline stage
-    if pp > 1:
+    if pp > 1 and world == 1:
+        # `--pipeline N` in a single process: this process drives N GPUs (brain/src/main.rs:126-134 -> train_pipeline)
+        from .parallel.pipeline_inproc import InProcPipelineTrainer
+        n_dev = torch.cuda.device_count() if on_gpu else 0
+        if on_gpu and n_dev < pp:
+            raise SystemExit(f"--pipeline {pp} needs {pp} GPUs in this process, {n_dev} visible")
+        devices = [f"cuda:{i}" for i in range(pp)] if on_gpu else ["cpu"] * pp
+        print(f"Launching {pp}-stage pipeline training...", flush=True)
+        InProcPipelineTrainer(mcfg, t, devices).run()
+    elif pp > 1:
+        # one process per stage (launched by torchrun, or with PIPELINE_RANK / PIPELINE_WORLD_SIZE as in
+        # brain/src/train.rs:1623-1632); world = pp x dp
         from .parallel.pipeline import PipelineTrainer
         if rank == 0:
             print(f"Launching {pp}-stage pipeline training...", flush=True)

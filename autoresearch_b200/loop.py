@@ -88,6 +88,20 @@ class TrainerBase:
                                 interval_s=max(t.heartbeat_timeout_s / 10.0, 0.05),
                                 timeout_s=t.heartbeat_timeout_s).start()
 
+    # ---- device memory ---------------------------------------------------------------------------
+    def plan_memory(self, **kw) -> None:
+        """Computes this rank's memory plan, reserves the step-time part in one allocation (a configuration that
+        cannot fit is refused here, before step 0) and prints the reference's start-up line
+        ``Allocated N MB GPU memory (B=..)`` (brain/src/train.rs:721)."""
+        from .utils import memplan
+        self.mem_plan = memplan.plan(self.mcfg, self.micro_batch, **kw)
+        self.mem_reserved = {"reserved_mb": 0.0}
+        if self.device.type == "cuda" and self.impl == "sm100" and os.environ.get("ARB_NO_RESERVE", "0") != "1":
+            self.mem_reserved = memplan.reserve(self.mem_plan.step_bytes, self.device)
+        self._say(f"Allocated {self.mem_plan.total_bytes / memplan.MB:.1f} MB GPU memory (B={self.micro_batch})")
+        if os.environ.get("ARB_MEMPLAN_VERBOSE", "0") == "1":
+            self._say(self.mem_plan.report())
+
     # ---- small helpers ---------------------------------------------------------------------------
     def _say(self, msg: str) -> None:
         if not self.quiet and self.rank == self.log_rank:

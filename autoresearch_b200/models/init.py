@@ -6,6 +6,12 @@ Wo, Wdn, ve_gate = 0; resid_lambdas = 1.0, x0_lambdas = 0.1; MoE: router = 0,
 expert fc ~ U(-s, s), expert proj = 0.  Random numbers come from one process-wide
 xorshift64 stream seeded 42 with Box-Muller normals (brain/src/train.rs:2424-2483), drawn
 in the reference's order: wte, lm_head, then per layer wq, wk, wv, wfc, ve, experts.
+
+scheme="torch" draws from PyTorch's CPU generator in the call order of the upstream Python trainer's
+``init_weights`` (original/train.py:148-180, reproduced by brain/tools/generate_init_weights.py:48-91):
+``torch.manual_seed(seed)``; wte normal_(0, 1); lm_head normal_(0, 0.001); for every layer c_q, c_k, c_v,
+c_fc uniform_(-s, s) as separate fp32 tensors; then the value embeddings uniform_(-s, s) in layer order.
+A file written with it starts this engine and the Python trainer from bit-identical bf16 weights.
 """
 from __future__ import annotations
 
@@ -66,6 +72,27 @@ def init_weights(model, seed: int = 42, scheme: str = "reference", std: float = 
                 put(p, (torch.randn(full, generator=g) * std)[r0:r0 + p.shape[0]])
             else:
                 put(p, torch.randn(p.shape, generator=g) * std)
+        return
+
+    if scheme == "torch":
+        if cfg.moe is not None or getattr(model, "tp", 1) > 1 or model.layer_lo != 0 or model.layer_hi != cfg.n_layer:
+            raise ValueError('scheme="torch" initialises a full dense model (shard or warm-start it afterwards)')
+        g = torch.Generator().manual_seed(seed)
+        V = cfg.vocab
+        put(model.wte, torch.empty(V, D).normal_(0.0, 1.0, generator=g))
+        put(model.lm_head, torch.empty(V, D).normal_(0.0, 0.001, generator=g))
+        for blk in model.blocks:
+            q, k, v = (torch.empty(D, D).uniform_(-s, s, generator=g) for _ in range(3))
+            put(blk.wqkv, torch.cat([q, k, v], 0))
+            blk.wo.data.zero_()
+            put(blk.wfc, torch.empty(cfg.mlp_dim, D).uniform_(-s, s, generator=g))
+            blk.wdn.data.zero_()
+        model.resid_lambdas.data.fill_(1.0)
+        model.x0_lambdas.data.fill_(0.1)
+        for blk in model.blocks:
+            if blk.ve is not None:
+                put(blk.ve, torch.empty(V, D).uniform_(-s, s, generator=g))
+                blk.ve_gate.data.zero_()
         return
 
     dt = model.dtype

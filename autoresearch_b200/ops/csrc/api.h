@@ -26,6 +26,20 @@ enum ArbError {
   ERR_SMEM_ALIGN = 5,   // dynamic shared memory base not 1 KB aligned (kernel returned before doing any work)
 };
 
+// Function attributes (dynamic shared memory size) belong to a device's context: a launcher sets them the first
+// time it runs on EACH device, so that one process can drive several GPUs (the in-process pipeline driver).
+struct PerDeviceOnce {
+  unsigned long long done = 0;
+  bool first() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess) return true;
+    const unsigned long long bit = 1ull << (d & 63);
+    if (done & bit) return false;
+    done |= bit;
+    return true;
+  }
+};
+
 extern "C" {
 
 // ---- tensor-core GEMM (gemm_sm100.cu) ----------------------------------------------------
@@ -121,21 +135,22 @@ int arb_softcap_ce(void* logits, long long ld, const int* targets, float* loss, 
 // ---- optimizer (optim.cu) -----------------------------------------------------------------------
 int arb_adamw(float* master, const float* grad, float* m, float* v, void* shadow_bf16, long long n, float lr,
               float beta1, float beta2, float eps, float wd, float bc1, float bc2, cudaStream_t s);
-// buf = mu*buf + (1-mu)*g ; u = (1-mu)*g + mu*buf -> bf16 ; sumsq[mat] += sum(u_bf16^2)
-int arb_muon_nesterov(float* buf, const float* grad, void* u_bf16, float* sumsq, long long per_mat, int n_mat,
+// buf = mu*buf + (1-mu)*g ; u = (1-mu)*g + mu*buf -> bf16 ; partials[mat][64] = per-block sums of u_bf16^2
+// (no atomics: arb_muon_frob_scale adds the 64 slots in a fixed order)
+int arb_muon_nesterov(float* buf, const float* grad, void* u_bf16, float* partials, long long per_mat, int n_mat,
                       float mu, cudaStream_t s);
 // The same two updates with the data-parallel reduce-scatter fused in: the gradient of element i
 // is grad_scale * sum_p bucket_p[bucket_offset + i] over all ranks' bf16 buckets, read through
 // NVLink peer pointers (HOST array peer_buckets, world entries) or, when mc_bucket is non-null,
 // with one multimem.ld_reduce through the switch.  n / per_mat / bucket_offset multiples of 8.
 int arb_muon_nesterov_rs(float* buf, const void* const* peer_buckets, int world, int rank, const void* mc_bucket,
-                         long long bucket_offset, float grad_scale, void* u_bf16, float* sumsq, long long per_mat,
+                         long long bucket_offset, float grad_scale, void* u_bf16, float* partials, long long per_mat,
                          int n_mat, float mu, cudaStream_t s);
 int arb_adamw_rs(float* master, const void* const* peer_buckets, int world, int rank, const void* mc_bucket,
                  long long bucket_offset, float grad_scale, float* m, float* v, void* shadow_bf16, long long n,
                  float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2, cudaStream_t s);
-// x = u / (sqrt(sumsq[mat])*1.02 + 1e-6)
-int arb_muon_frob_scale(void* u_bf16, const float* sumsq, long long per_mat, int n_mat, cudaStream_t s);
+// x = u / (sqrt(sum of partials[mat][0..63])*1.02 + 1e-6)
+int arb_muon_frob_scale(void* u_bf16, const float* partials, long long per_mat, int n_mat, cudaStream_t s);
 // NorMuon statistics + cautious update, per matrix [m, n]; reduce over columns if m >= n.
 int arb_normuon_stats(const void* x_bf16, float* v_mean, int n_mat, int m, int n, cudaStream_t s);
 int arb_normuon_scales(const float* v_mean, float* second, float* scale, int n_mat, int n_stat, int red_size,
@@ -150,6 +165,8 @@ int arb_muon_update(float* master, void* shadow_bf16, const void* x_bf16, const 
 // index cast to a pointer.
 int arb_reduce_scatter_peers(const void* const* peer_bufs, int world, long long offset, long long n, int src_is_bf16,
                              float* out, float scale, cudaStream_t s);
+// out[i] = bf16(sum over the `count` bf16 buffers slabs[s][i]), fp32 accumulation; n a multiple of 8.
+int arb_sum_slabs_bf16(const void* const* slabs, int count, long long n, void* out_bf16, cudaStream_t s);
 int arb_reduce_scatter_multimem(const void* mc_ptr, long long offset, long long n, int src_is_bf16, float* out,
                                 float scale, cudaStream_t s);
 // push this rank's shard [offset, offset+n) of `src` to the same offset of every peer buffer

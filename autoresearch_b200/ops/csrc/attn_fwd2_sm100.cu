@@ -303,9 +303,9 @@ attn_fwd2_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 
 int attn_fwd2_launch(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv, AttnArgs a,
                      cudaStream_t stream) {
-  static bool cfg = false;
+  static PerDeviceOnce cfg;
   int r;
-  if (!cfg) { if ((r = set_smem(attn_fwd2_k, Fwd2Smem::TOTAL))) return r; cfg = true; }
+  if (cfg.first()) { if ((r = set_smem(attn_fwd2_k, Fwd2Smem::TOTAL))) return r; }
   CUtensorMap tq, tk, tv;
   if ((r = make_qkv_tmap(&tq, q, a.B, a.T, a.H, ldq, 128))) return 1000 + r;
   if ((r = make_qkv_tmap(&tk, k, a.B, a.T, a.H, ldk, 128))) return 1000 + r;

@@ -13,7 +13,11 @@
 //     every GPU loading this library holds until the process exits).  Larger problems are
 //     rejected with ARB_ERR_NOALLOC_TOO_LARGE before anything is launched.
 //   * The first call on each device looks up the device address of the array (with that device
-//     current) and caches it; make that first call outside any stream capture.
+//     current) and caches it; make that first call outside any stream capture.  The cache is
+//     atomic: host threads may make their first calls concurrently.
+//   * `stream` must belong to the device that is current in the calling thread: the array of
+//     THAT device is used, and a stream of another device fails at launch with a CUDA error
+//     code as the return value.
 //   * Nothing here calls cudaMalloc, cudaFree or any allocating library routine.  Inputs and
 //     outputs are still the caller's.
 //   * All calls on one device share the one array and it keeps whatever the previous call left

@@ -824,27 +824,27 @@ extern "C" void arb_attn_set_mode(int mode) { g_attn_mode = mode < 0 ? 0 : (mode
 template <bool TS>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a, dim3 grid,
                       cudaStream_t stream) {
-  static bool cfg = false;
+  static PerDeviceOnce cfg;
   int r;
-  if (!cfg) { if ((r = set_smem(attn_fwd_k<TS>, FwdSmemT<TS>::TOTAL))) return r; cfg = true; }
+  if (cfg.first()) { if ((r = set_smem(attn_fwd_k<TS>, FwdSmemT<TS>::TOTAL))) return r; }
   attn_fwd_k<TS><<<grid, ATT_THREADS, FwdSmemT<TS>::TOTAL, stream>>>(tq, tk, tv, a);
   return int(cudaGetLastError());
 }
 template <bool TS>
 static int launch_dq(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                      const AttnArgs& a, dim3 grid, cudaStream_t stream) {
-  static bool cfg = false;
+  static PerDeviceOnce cfg;
   int r;
-  if (!cfg) { if ((r = set_smem(attn_bwd_dq_k<TS>, DqSmem::TOTAL))) return r; cfg = true; }
+  if (cfg.first()) { if ((r = set_smem(attn_bwd_dq_k<TS>, DqSmem::TOTAL))) return r; }
   attn_bwd_dq_k<TS><<<grid, ATT_THREADS, DqSmem::TOTAL, stream>>>(tq, tk, tv, tdo, a);
   return int(cudaGetLastError());
 }
 template <bool TS>
 static int launch_dkv(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                       const AttnArgs& a, dim3 grid, cudaStream_t stream) {
-  static bool cfg = false;
+  static PerDeviceOnce cfg;
   int r;
-  if (!cfg) { if ((r = set_smem(attn_bwd_dkv_k<TS>, DkvSmem::TOTAL))) return r; cfg = true; }
+  if (cfg.first()) { if ((r = set_smem(attn_bwd_dkv_k<TS>, DkvSmem::TOTAL))) return r; }
   attn_bwd_dkv_k<TS><<<grid, ATT_THREADS, DkvSmem::TOTAL, stream>>>(tq, tk, tv, tdo, a);
   return int(cudaGetLastError());
 }
@@ -920,6 +920,8 @@ extern "C" int arb_attn_bwd(const void* q, const void* k, const void* v, const v
 // ---------------------------------------------------------------------------------------------
 #include "attn_noalloc.h"
 
+#include <atomic>
+
 static __device__ __align__(256) float g_attn_noalloc_delta[ARB_ATTN_NOALLOC_MAX_ROWS];
 
 extern "C" int arb_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* o, const void* d_o,
@@ -928,17 +930,19 @@ extern "C" int arb_attn_bwd_noalloc(const void* q, const void* k, const void* v,
                                     long long lddq, long long lddk, long long lddv, int window, float scale,
                                     int* err_flag, cudaStream_t stream) {
   constexpr int MAX_DEVICES = 64;
-  static float* scratch_of_device[MAX_DEVICES] = {nullptr};
+  // one slot per device; atomic, so that two host threads making their first call on a device at the same
+  // time both end up with the (identical) address without a data race
+  static std::atomic<float*> scratch_of_device[MAX_DEVICES];
   if (B <= 0 || T <= 0 || H <= 0) return -3;
   if ((long long)B * T * H > (long long)ARB_ATTN_NOALLOC_MAX_ROWS) return ARB_ERR_NOALLOC_TOO_LARGE;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return ARB_ERR_NOALLOC_SYMBOL;
-  if (scratch_of_device[dev] == nullptr) {
-    float* ptr = nullptr;
-    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_attn_noalloc_delta);
-    if (e != cudaSuccess || ptr == nullptr) return ARB_ERR_NOALLOC_SYMBOL;
-    scratch_of_device[dev] = ptr;
+  float* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_attn_noalloc_delta);
+    if (e != cudaSuccess || scratch == nullptr) return ARB_ERR_NOALLOC_SYMBOL;
+    scratch_of_device[dev].store(scratch, std::memory_order_release);
   }
-  return arb_attn_bwd(q, k, v, o, d_o, lse, dq, dk, dv, scratch_of_device[dev], nullptr, B, T, H, ldq, ldk, ldv, ldo,
+  return arb_attn_bwd(q, k, v, o, d_o, lse, dq, dk, dv, scratch, nullptr, B, T, H, ldq, ldk, ldv, ldo,
                       lddo, lddq, lddk, lddv, window, scale, err_flag, stream);
 }

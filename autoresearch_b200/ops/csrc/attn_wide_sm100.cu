@@ -559,12 +559,11 @@ attn_bwd_dkv_wide_k(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 int attn_wide_bwd_launch(const void* q, const void* k, const void* v, const void* d_o, void* dq, void* dk, void* dv,
                          long long ldq, long long ldk, long long ldv, long long lddo, long long lddq, long long lddk,
                          long long lddv, AttnArgs a, cudaStream_t stream) {
-  static bool cfg = false;
+  static PerDeviceOnce cfg;
   int r;
-  if (!cfg) {
+  if (cfg.first()) {
     if ((r = set_smem(attn_bwd_dq_wide_k, WideSmem::TOTAL))) return r;
     if ((r = set_smem(attn_bwd_dkv_wide_k, WideSmem::TOTAL))) return r;
-    cfg = true;
   }
   CUtensorMap tq, tk, tv, tdo;
   if ((r = make_qkv_tmap(&tq, q, a.B, a.T, a.H, ldq, 128))) return 1000 + r;

@@ -46,6 +46,22 @@ __global__ void __launch_bounds__(256) reduce_scatter_peers_k(PeerPtrs peers, in
   }
 }
 
+// out[i] = bf16(sum_s slab_s[i]), fp32 accumulation: the local half of a tensor-parallel reduce-scatter (the slabs
+// were filled by the peers' GEMM epilogues or push copies; every read here is local memory).
+__global__ void __launch_bounds__(256) sum_slabs_bf16_k(PeerPtrs slabs, int count, long long n8, uint4* __restrict__ out) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int q = 0; q < count; ++q) {
+      const uint4 u = reinterpret_cast<const uint4*>(slabs.p[q])[i];
+      float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]); o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    out[i] = o;
+  }
+}
+
 // The same reduction performed by the switch: one multimem.ld_reduce per 16 bytes.
 template <bool BF16>
 __global__ void __launch_bounds__(256) reduce_scatter_mc_k(const void* mc, long long offset, long long n, float* __restrict__ out,
@@ -166,6 +182,17 @@ int arb_reduce_scatter_peers(const void* const* peer_bufs, int world, long long 
   const int rank = int(reinterpret_cast<intptr_t>(peer_bufs[world]));
   if (src_is_bf16) reduce_scatter_peers_k<true><<<comm_grid(n / 8), 256, 0, s>>>(pp, world, rank, offset, n, out, scale);
   else reduce_scatter_peers_k<false><<<comm_grid(n / 4), 256, 0, s>>>(pp, world, rank, offset, n, out, scale);
+  return int(cudaGetLastError());
+}
+
+int arb_sum_slabs_bf16(const void* const* slabs, int count, long long n, void* out_bf16, cudaStream_t s) {
+  if (count < 1 || count > MAX_WORLD || n <= 0 || (n & 7) || (reinterpret_cast<uintptr_t>(out_bf16) & 15)) return -3;
+  PeerPtrs pp;
+  for (int i = 0; i < count; ++i) {
+    if (reinterpret_cast<uintptr_t>(slabs[i]) & 15) return -4;
+    pp.p[i] = slabs[i];
+  }
+  sum_slabs_bf16_k<<<comm_grid(n / 8), 256, 0, s>>>(pp, count, n / 8, reinterpret_cast<uint4*>(out_bf16));
   return int(cudaGetLastError());
 }
 

@@ -659,11 +659,10 @@ template <bool A_MN, bool B_MN, int EPI, int BN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, cudaStream_t st) {
   using L = SmemLayout<BN>;
   auto kern = gemm_kernel<A_MN, B_MN, EPI, BN>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return int(e);
-    configured = true;
   }
   const int items = a.batch * a.m_tiles * a.n_tiles * a.splitk;
   const int grid = items < g_num_sms ? items : g_num_sms;
@@ -676,7 +675,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, cudaStream_t st) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, EPI>;
-  static bool configured = false;
+  static PerDeviceOnce configured;
   CUtensorMap tc, tx;
   std::memset(&tc, 0, sizeof tc);
   std::memset(&tx, 0, sizeof tx);
@@ -693,10 +692,9 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
       if (r) return 4000 + r;
     }
   }
-  if (!configured) {
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<EPI>::TOTAL);
     if (e != cudaSuccess) return int(e);
-    configured = true;
   }
   const int items = a.batch * a.m_tiles * a.n_tiles * a.splitk;
   int clusters = g_num_sms / 2;

@@ -237,11 +237,10 @@ int arb_moe_router_fwd(const void* xn, const void* wr, float* probs, int* idx, f
   if ((reinterpret_cast<uintptr_t>(xn) | reinterpret_cast<uintptr_t>(wr)) & 15) return -4;
   const size_t smem = size_t(E) * D * 2;
   if (smem > 200 * 1024) return -3;
-  static bool cfg = false;
-  if (!cfg) {
+  static PerDeviceOnce cfg;
+  if (cfg.first()) {
     cudaError_t e = cudaFuncSetAttribute(moe_router_fwd_k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return int(e);
-    cfg = true;
   }
   moe_router_fwd_k<<<unsigned((N + 7) / 8), 256, smem, s>>>((const bf16*)xn, (const bf16*)wr, probs, idx, gates, N, D, E, K);
   return int(cudaGetLastError());

@@ -23,23 +23,13 @@ __global__ void adamw_k(float* __restrict__ p, const float* __restrict__ g, floa
   }
 }
 
-// grid: (blocks_per_mat, n_mat)
-__global__ void __launch_bounds__(256) muon_nesterov_k(float* __restrict__ buf, const float* __restrict__ g,
-                                                       __nv_bfloat16* __restrict__ u, float* __restrict__ sumsq,
-                                                       long long per_mat, float mu) {
+// Frobenius norms without atomics: every block of a matrix leaves ONE partial sum in its own slot of
+// partials[mat][MUON_PARTS] (unused slots are zeroed by block 0), and the scale kernel adds the slots in a fixed
+// order, so the norm - and with it the whole Muon update - is the same bit pattern run after run.
+constexpr int MUON_PARTS = 64;
+
+__device__ __forceinline__ void muon_store_partial(float acc, float* __restrict__ partials, int mat) {
   __shared__ float red[8];
-  const int mat = blockIdx.y;
-  const long long base = (long long)mat * per_mat;
-  float acc = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per_mat; i += (long long)gridDim.x * blockDim.x) {
-    const float gi = g[base + i];
-    const float b = mu * buf[base + i] + (1.f - mu) * gi;
-    buf[base + i] = b;
-    const __nv_bfloat16 ub = __float2bfloat16((1.f - mu) * gi + mu * b);
-    u[base + i] = ub;
-    const float uf = __bfloat162float(ub);
-    acc += uf * uf;
-  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
@@ -47,16 +37,87 @@ __global__ void __launch_bounds__(256) muon_nesterov_k(float* __restrict__ buf, 
   if (threadIdx.x == 0) {
     float t = 0.f;
     for (int w = 0; w < 8; ++w) t += red[w];
-    atomicAdd(sumsq + mat, t);
+    partials[mat * MUON_PARTS + blockIdx.x] = t;
   }
+  if (blockIdx.x == 0 && threadIdx.x >= gridDim.x && threadIdx.x < MUON_PARTS) partials[mat * MUON_PARTS + threadIdx.x] = 0.f;
 }
 
-__global__ void muon_frob_scale_k(__nv_bfloat16* __restrict__ u, const float* __restrict__ sumsq, long long per_mat) {
+// One step for 8 consecutive elements: b = mu*b + (1-mu)*g ; u = bf16((1-mu)*g + mu*b); returns sum u^2
+__device__ __forceinline__ float nesterov8(float* __restrict__ buf, __nv_bfloat16* __restrict__ u, long long at, const float (&g)[8],
+                                           float mu) {
+  float4 b0 = *reinterpret_cast<const float4*>(buf + at), b1 = *reinterpret_cast<const float4*>(buf + at + 4);
+  float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  float uu[8], acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    b[j] = mu * b[j] + (1.f - mu) * g[j];
+    uu[j] = __bfloat162float(__float2bfloat16((1.f - mu) * g[j] + mu * b[j]));
+    acc += uu[j] * uu[j];
+  }
+  *reinterpret_cast<float4*>(buf + at) = make_float4(b[0], b[1], b[2], b[3]);
+  *reinterpret_cast<float4*>(buf + at + 4) = make_float4(b[4], b[5], b[6], b[7]);
+  uint4 o;
+  o.x = pack_bf16(uu[0], uu[1]); o.y = pack_bf16(uu[2], uu[3]); o.z = pack_bf16(uu[4], uu[5]); o.w = pack_bf16(uu[6], uu[7]);
+  *reinterpret_cast<uint4*>(u + at) = o;
+  return acc;
+}
+
+// grid: (blocks_per_mat <= MUON_PARTS, n_mat).  VEC: per_mat is a multiple of 8 and every pointer 16-byte aligned.
+template <bool VEC>
+__global__ void __launch_bounds__(256) muon_nesterov_k(float* __restrict__ buf, const float* __restrict__ g,
+                                                       __nv_bfloat16* __restrict__ u, float* __restrict__ partials,
+                                                       long long per_mat, float mu) {
   const int mat = blockIdx.y;
-  const float inv = 1.f / (sqrtf(sumsq[mat]) * 1.02f + 1e-6f);
   const long long base = (long long)mat * per_mat;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per_mat; i += (long long)gridDim.x * blockDim.x)
-    u[base + i] = __float2bfloat16(__bfloat162float(u[base + i]) * inv);
+  float acc = 0.f;
+  if (VEC) {
+    const long long stride = (long long)gridDim.x * blockDim.x * 8;
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < per_mat; i += stride) {
+      const float4 g0 = *reinterpret_cast<const float4*>(g + base + i), g1 = *reinterpret_cast<const float4*>(g + base + i + 4);
+      const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      acc += nesterov8(buf, u, base + i, gg, mu);
+    }
+  } else {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per_mat; i += (long long)gridDim.x * blockDim.x) {
+      const float gi = g[base + i];
+      const float b = mu * buf[base + i] + (1.f - mu) * gi;
+      buf[base + i] = b;
+      const __nv_bfloat16 ub = __float2bfloat16((1.f - mu) * gi + mu * b);
+      u[base + i] = ub;
+      const float uf = __bfloat162float(ub);
+      acc += uf * uf;
+    }
+  }
+  muon_store_partial(acc, partials, mat);
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) muon_frob_scale_k(__nv_bfloat16* __restrict__ u, const float* __restrict__ partials,
+                                                         long long per_mat) {
+  __shared__ float s_inv;
+  const int mat = blockIdx.y;
+  if (threadIdx.x < 32) {      // fixed-order sum of the 64 slots
+    float t = partials[mat * MUON_PARTS + threadIdx.x] + partials[mat * MUON_PARTS + 32 + threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) s_inv = 1.f / (sqrtf(t) * 1.02f + 1e-6f);
+  }
+  __syncthreads();
+  const float inv = s_inv;
+  const long long base = (long long)mat * per_mat;
+  if (VEC) {
+    const long long stride = (long long)gridDim.x * blockDim.x * 8;
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < per_mat; i += stride) {
+      uint4 v = *reinterpret_cast<const uint4*>(u + base + i);
+      const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), d = unpack_bf16(v.w);
+      v.x = pack_bf16(a.x * inv, a.y * inv); v.y = pack_bf16(b.x * inv, b.y * inv);
+      v.z = pack_bf16(c.x * inv, c.y * inv); v.w = pack_bf16(d.x * inv, d.y * inv);
+      *reinterpret_cast<uint4*>(u + base + i) = v;
+    }
+  } else {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per_mat; i += (long long)gridDim.x * blockDim.x)
+      u[base + i] = __float2bfloat16(__bfloat162float(u[base + i]) * inv);
+  }
 }
 
 // v_mean[mat, r] = mean_c x[mat, r, c]^2 (ROWS=true, one warp per row) or the column version
@@ -109,21 +170,56 @@ __global__ void __launch_bounds__(256) normuon_scales_k(const float* __restrict_
     scale[(long long)mat * n_stat + i] = rsqrtf(fmaxf(sm[i], 1e-10f)) * ratio;
 }
 
-// g = x*scale[row or col]; mask = (g*p >= 0); p -= lr*g + lr*wd*p*mask
-template <bool ROWS>
+// g = x*scale[row or col]; mask = (g*p >= 0); p -= lr*g + lr*wd*p*mask.  VEC: n is a multiple of 8 (a chunk of 8
+// elements never crosses a row) and every pointer is 16-byte aligned; one division per chunk instead of per element.
+template <bool ROWS, bool VEC>
 __global__ void muon_update_k(float* __restrict__ master, __nv_bfloat16* __restrict__ shadow, const __nv_bfloat16* __restrict__ x,
                               const float* __restrict__ scale, int m, int n, float lr, float wd) {
   const int mat = blockIdx.y;
   const long long per = (long long)m * n;
   const int n_stat = ROWS ? m : n;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
-    const int r = int(i / n), c = int(i - (long long)r * n);
-    const float g = __bfloat162float(x[mat * per + i]) * scale[(long long)mat * n_stat + (ROWS ? r : c)];
-    float p = master[mat * per + i];
-    const float mask = (g * p >= 0.f) ? 1.f : 0.f;
-    p -= lr * g + lr * wd * p * mask;
-    master[mat * per + i] = p;
-    shadow[mat * per + i] = __float2bfloat16(p);
+  const float* sc = scale + (long long)mat * n_stat;
+  if (VEC) {
+    const long long stride = (long long)gridDim.x * blockDim.x * 8;
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < per; i += stride) {
+      const int r = int(i / n), c = int(i - (long long)r * n);
+      float s8[8];
+      if (ROWS) {
+        const float sr = sc[r];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s8[j] = sr;
+      } else {
+        const float4 s0 = *reinterpret_cast<const float4*>(sc + c), s1 = *reinterpret_cast<const float4*>(sc + c + 4);
+        s8[0] = s0.x; s8[1] = s0.y; s8[2] = s0.z; s8[3] = s0.w; s8[4] = s1.x; s8[5] = s1.y; s8[6] = s1.z; s8[7] = s1.w;
+      }
+      const long long at = mat * per + i;
+      const uint4 xv = *reinterpret_cast<const uint4*>(x + at);
+      const float2 xa = unpack_bf16(xv.x), xb = unpack_bf16(xv.y), xc = unpack_bf16(xv.z), xd = unpack_bf16(xv.w);
+      const float xs[8] = {xa.x, xa.y, xb.x, xb.y, xc.x, xc.y, xd.x, xd.y};
+      const float4 p0 = *reinterpret_cast<const float4*>(master + at), p1 = *reinterpret_cast<const float4*>(master + at + 4);
+      float p[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float g = xs[j] * s8[j];
+        const float mask = (g * p[j] >= 0.f) ? 1.f : 0.f;
+        p[j] -= lr * g + lr * wd * p[j] * mask;
+      }
+      *reinterpret_cast<float4*>(master + at) = make_float4(p[0], p[1], p[2], p[3]);
+      *reinterpret_cast<float4*>(master + at + 4) = make_float4(p[4], p[5], p[6], p[7]);
+      uint4 o;
+      o.x = pack_bf16(p[0], p[1]); o.y = pack_bf16(p[2], p[3]); o.z = pack_bf16(p[4], p[5]); o.w = pack_bf16(p[6], p[7]);
+      *reinterpret_cast<uint4*>(shadow + at) = o;
+    }
+  } else {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
+      const int r = int(i / n), c = int(i - (long long)r * n);
+      const float g = __bfloat162float(x[mat * per + i]) * sc[ROWS ? r : c];
+      float p = master[mat * per + i];
+      const float mask = (g * p >= 0.f) ? 1.f : 0.f;
+      p -= lr * g + lr * wd * p * mask;
+      master[mat * per + i] = p;
+      shadow[mat * per + i] = __float2bfloat16(p);
+    }
   }
 }
 
@@ -191,52 +287,27 @@ __device__ __forceinline__ void load_grad8x2(const GradPeers& g, long long i0, l
   for (int j = 0; j < 8; ++j) { o0[j] *= g.scale; o1[j] *= g.scale; }
 }
 
-// grid (blocks_per_mat, n_mat); elements of matrix `mat` sit at bucket offset `offset + mat*per_mat`
+// grid (blocks_per_mat <= MUON_PARTS, n_mat); elements of matrix `mat` sit at bucket offset `offset + mat*per_mat`
 __global__ void __launch_bounds__(256) muon_nesterov_rs_k(float* __restrict__ buf, GradPeers gp, long long offset,
-                                                          __nv_bfloat16* __restrict__ u, float* __restrict__ sumsq,
+                                                          __nv_bfloat16* __restrict__ u, float* __restrict__ partials,
                                                           long long per_mat, float mu) {
-  __shared__ float red[8];
   const int mat = blockIdx.y;
   const long long base = (long long)mat * per_mat;
   float acc = 0.f;
-  auto update8 = [&](long long i, const float (&g)[8]) {
-    float4 b0 = *reinterpret_cast<const float4*>(buf + base + i), b1 = *reinterpret_cast<const float4*>(buf + base + i + 4);
-    float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-    float uu[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      b[j] = mu * b[j] + (1.f - mu) * g[j];
-      uu[j] = __bfloat162float(__float2bfloat16((1.f - mu) * g[j] + mu * b[j]));
-      acc += uu[j] * uu[j];
-    }
-    *reinterpret_cast<float4*>(buf + base + i) = make_float4(b[0], b[1], b[2], b[3]);
-    *reinterpret_cast<float4*>(buf + base + i + 4) = make_float4(b[4], b[5], b[6], b[7]);
-    uint4 o;
-    o.x = pack_bf16(uu[0], uu[1]); o.y = pack_bf16(uu[2], uu[3]); o.z = pack_bf16(uu[4], uu[5]); o.w = pack_bf16(uu[6], uu[7]);
-    *reinterpret_cast<uint4*>(u + base + i) = o;
-  };
   const long long stride = (long long)gridDim.x * blockDim.x * 8;
   long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   for (; i + stride < per_mat; i += 2 * stride) {
     float g0[8], g1[8];
     load_grad8x2(gp, offset + base + i, offset + base + i + stride, g0, g1);
-    update8(i, g0);
-    update8(i + stride, g1);
+    acc += nesterov8(buf, u, base + i, g0, mu);
+    acc += nesterov8(buf, u, base + i + stride, g1, mu);
   }
   if (i < per_mat) {
     float g[8];
     load_grad8(gp, offset + base + i, g);
-    update8(i, g);
+    acc += nesterov8(buf, u, base + i, g, mu);
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = 0.f;
-    for (int w = 0; w < 8; ++w) t += red[w];
-    atomicAdd(sumsq + mat, t);
-  }
+  muon_store_partial(acc, partials, mat);
 }
 
 __device__ __forceinline__ void adamw8(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
@@ -314,25 +385,30 @@ int arb_adamw(float* master, const float* grad, float* m, float* v, void* shadow
   adamw_k<<<blocks_for(n, 256, 148 * 8), 256, 0, s>>>(master, grad, m, v, (__nv_bfloat16*)shadow_bf16, n, lr, beta1, beta2, eps, wd, bc1, bc2);
   return int(cudaGetLastError());
 }
-int arb_muon_nesterov(float* buf, const float* grad, void* u_bf16, float* sumsq, long long per_mat, int n_mat, float mu, cudaStream_t s) {
+static inline bool aligned16(const void* a, const void* b = nullptr, const void* c = nullptr, const void* d = nullptr) {
+  return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+           reinterpret_cast<uintptr_t>(d)) & 15) == 0;
+}
+// `partials`: n_mat x 64 floats (per-block partial sums of u^2, consumed by arb_muon_frob_scale)
+int arb_muon_nesterov(float* buf, const float* grad, void* u_bf16, float* partials, long long per_mat, int n_mat, float mu, cudaStream_t s) {
   if (per_mat <= 0 || n_mat <= 0 || n_mat > 65535) return -3;
-  cudaError_t e = cudaMemsetAsync(sumsq, 0, sizeof(float) * n_mat, s);
-  if (e != cudaSuccess) return int(e);
-  const int bpm = blocks_for(per_mat, 256 * 4, 64);
-  muon_nesterov_k<<<dim3(bpm, n_mat), 256, 0, s>>>(buf, grad, (__nv_bfloat16*)u_bf16, sumsq, per_mat, mu);
+  if ((per_mat & 7) == 0 && aligned16(buf, grad, u_bf16)) {
+    muon_nesterov_k<true><<<dim3(blocks_for(per_mat / 8, 256, MUON_PARTS), n_mat), 256, 0, s>>>(buf, grad, (__nv_bfloat16*)u_bf16, partials, per_mat, mu);
+  } else {
+    muon_nesterov_k<false><<<dim3(blocks_for(per_mat, 256 * 4, MUON_PARTS), n_mat), 256, 0, s>>>(buf, grad, (__nv_bfloat16*)u_bf16, partials, per_mat, mu);
+  }
   return int(cudaGetLastError());
 }
 int arb_muon_nesterov_rs(float* buf, const void* const* peer_buckets, int world, int rank, const void* mc_bucket,
-                         long long bucket_offset, float grad_scale, void* u_bf16, float* sumsq, long long per_mat, int n_mat,
+                         long long bucket_offset, float grad_scale, void* u_bf16, float* partials, long long per_mat, int n_mat,
                          float mu, cudaStream_t s) {
   if (per_mat <= 0 || (per_mat & 7) || (bucket_offset & 7) || n_mat <= 0 || n_mat > 65535) return -3;
+  if (!aligned16(buf, u_bf16)) return -4;
   GradPeers gp;
   int rc = fill_peers(gp, peer_buckets, world, rank, mc_bucket, grad_scale);
   if (rc) return rc;
-  cudaError_t e = cudaMemsetAsync(sumsq, 0, sizeof(float) * n_mat, s);
-  if (e != cudaSuccess) return int(e);
-  const int bpm = blocks_for(per_mat / 8, 256, 64);
-  muon_nesterov_rs_k<<<dim3(bpm, n_mat), 256, 0, s>>>(buf, gp, bucket_offset, (__nv_bfloat16*)u_bf16, sumsq, per_mat, mu);
+  const int bpm = blocks_for(per_mat / 8, 256, MUON_PARTS);
+  muon_nesterov_rs_k<<<dim3(bpm, n_mat), 256, 0, s>>>(buf, gp, bucket_offset, (__nv_bfloat16*)u_bf16, partials, per_mat, mu);
   return int(cudaGetLastError());
 }
 int arb_adamw_rs(float* master, const void* const* peer_buckets, int world, int rank, const void* mc_bucket,
@@ -346,9 +422,12 @@ int arb_adamw_rs(float* master, const void* const* peer_buckets, int world, int 
                                                               beta2, eps, wd, bc1, bc2);
   return int(cudaGetLastError());
 }
-int arb_muon_frob_scale(void* u_bf16, const float* sumsq, long long per_mat, int n_mat, cudaStream_t s) {
+int arb_muon_frob_scale(void* u_bf16, const float* partials, long long per_mat, int n_mat, cudaStream_t s) {
   if (per_mat <= 0 || n_mat <= 0 || n_mat > 65535) return -3;
-  muon_frob_scale_k<<<dim3(blocks_for(per_mat, 256 * 4, 64), n_mat), 256, 0, s>>>((__nv_bfloat16*)u_bf16, sumsq, per_mat);
+  if ((per_mat & 7) == 0 && aligned16(u_bf16))
+    muon_frob_scale_k<true><<<dim3(blocks_for(per_mat / 8, 256, 64), n_mat), 256, 0, s>>>((__nv_bfloat16*)u_bf16, partials, per_mat);
+  else
+    muon_frob_scale_k<false><<<dim3(blocks_for(per_mat, 256 * 4, 64), n_mat), 256, 0, s>>>((__nv_bfloat16*)u_bf16, partials, per_mat);
   return int(cudaGetLastError());
 }
 int arb_normuon_stats(const void* x_bf16, float* v_mean, int n_mat, int m, int n, cudaStream_t s) {
@@ -365,9 +444,17 @@ int arb_normuon_scales(const float* v_mean, float* second, float* scale, int n_m
 int arb_muon_update(float* master, void* shadow_bf16, const void* x_bf16, const float* scale, int n_mat, int m, int n, float lr,
                     float wd, cudaStream_t s) {
   if (n_mat <= 0 || m <= 0 || n <= 0 || n_mat > 65535) return -3;
-  const int bpm = blocks_for((long long)m * n, 256 * 4, 64);
-  if (m >= n) muon_update_k<true><<<dim3(bpm, n_mat), 256, 0, s>>>(master, (__nv_bfloat16*)shadow_bf16, (const __nv_bfloat16*)x_bf16, scale, m, n, lr, wd);
-  else muon_update_k<false><<<dim3(bpm, n_mat), 256, 0, s>>>(master, (__nv_bfloat16*)shadow_bf16, (const __nv_bfloat16*)x_bf16, scale, m, n, lr, wd);
+  auto* sh = (__nv_bfloat16*)shadow_bf16;
+  auto* xx = (const __nv_bfloat16*)x_bf16;
+  if ((n & 7) == 0 && aligned16(master, shadow_bf16, x_bf16, scale)) {
+    const dim3 grid(blocks_for((long long)m * n / 8, 256, 128), n_mat);
+    if (m >= n) muon_update_k<true, true><<<grid, 256, 0, s>>>(master, sh, xx, scale, m, n, lr, wd);
+    else muon_update_k<false, true><<<grid, 256, 0, s>>>(master, sh, xx, scale, m, n, lr, wd);
+  } else {
+    const dim3 grid(blocks_for((long long)m * n, 256 * 4, 64), n_mat);
+    if (m >= n) muon_update_k<true, false><<<grid, 256, 0, s>>>(master, sh, xx, scale, m, n, lr, wd);
+    else muon_update_k<false, false><<<grid, 256, 0, s>>>(master, sh, xx, scale, m, n, lr, wd);
+  }
   return int(cudaGetLastError());
 }
 

@@ -79,6 +79,7 @@ def lib() -> C.CDLL:
         "arb_muon_update": [vp, vp, vp, vp, i32, i32, i32, f32, f32, vp],
         "arb_reduce_scatter_peers": [vp, i32, i64, i64, i32, vp, f32, vp],
         "arb_reduce_scatter_multimem": [vp, i64, i64, i32, vp, f32, vp],
+        "arb_sum_slabs_bf16": [vp, i32, i64, vp, vp],
         "arb_all_gather_push": [vp, i32, i32, vp, i64, i64, vp],
         "arb_all_gather_pull": [vp, i32, i32, vp, i64, vp],
         "arb_peer_barrier": [vp, i32, i32, i32, vp, vp],
@@ -325,7 +326,7 @@ def _embedding_plan(ids, vocab: int):
     """Sort order and work-item tables of one batch of token ids; cached, since the word-embedding and every
     value-embedding gradient of a micro-batch use the same ids.  Fixed-size tensors only (no host sync)."""
     key = (ids.data_ptr(), ids._version, ids.numel(), vocab)
-    hit = _emb_plan.get("plan")
+    hit = _emb_plan.get(("plan", ids.device.index))
     if hit is not None and hit[0] == key:
         return hit[1]
     R = EMB_BWD_ROWS_PER_ITEM
@@ -342,7 +343,7 @@ def _embedding_plan(ids, vocab: int):
     item_id = torch.searchsorted(it_end, item, right=True)
     item_id = torch.where(item < it_end[-1], item_id, torch.full_like(item_id, -1)).to(torch.int32)
     plan = (perm, item_id.contiguous(), item_start.contiguous(), seg_start.contiguous(), counts.to(torch.int32).contiguous(), n_max)
-    _emb_plan["plan"] = (key, plan)
+    _emb_plan[("plan", ids.device.index)] = (key, plan)
     return plan
 
 
@@ -354,10 +355,10 @@ def embedding_bwd(ids, g, dw_f32):
                "embedding_bwd")
         return
     perm, item_id, item_start, seg_start, counts, n_max = _embedding_plan(ids, vocab)
-    scratch = _emb_plan.get("scratch")
-    if scratch is None or scratch.numel() < n_max * D or scratch.device != g.device:
+    scratch = _emb_plan.get(("scratch", g.device.index))
+    if scratch is None or scratch.numel() < n_max * D:
         scratch = torch.empty(n_max * D, dtype=torch.float32, device=g.device)
-        _emb_plan["scratch"] = scratch
+        _emb_plan[("scratch", g.device.index)] = scratch
     _check(lib().arb_embedding_bwd_sorted(perm.data_ptr(), item_id.data_ptr(), item_start.data_ptr(), seg_start.data_ptr(),
                                           counts.data_ptr(), g.data_ptr(), dw_f32.data_ptr(), scratch.data_ptr(), n_max, D,
                                           EMB_BWD_ROWS_PER_ITEM, vocab, _stream()), "embedding_bwd_sorted")

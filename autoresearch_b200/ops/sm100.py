@@ -448,9 +448,34 @@ class PeerGrad:
 
 
 class OptimKernels:
-    """Fused optimizer steps for MuonAdamW (same math as optim.muon_adamw's reference)."""
+    """Fused optimizer steps for MuonAdamW (same math as optim.muon_adamw's reference).
+
+    The Newton-Schulz work buffers (two copies of the stacked matrices, the Gram matrix, the combined polynomial,
+    the norm partials and the NorMuon statistics) are allocated once per group shape and reused by every step and
+    by every group of that shape: groups run one after the other on one stream.  The reference aliases these
+    buffers onto activation gradients (brain/src/optim.rs:742-748,842-848)."""
 
     MIN_GEMM_DIM = 64
+
+    def __init__(self):
+        self._scratch = {}
+
+    def scratch(self, G, m, n, dev):
+        key = (G, m, n, str(dev))
+        sc = self._scratch.get(key)
+        if sc is None:
+            d = n if m > n else m
+            n_stat = m if m >= n else n
+            bf = dict(dtype=torch.bfloat16, device=dev)
+            f32 = dict(dtype=torch.float32, device=dev)
+            sc = dict(x=torch.empty(G, m, n, **bf), x2=torch.empty(G, m, n, **bf), A=torch.empty(G, d, d, **bf),
+                      C=torch.empty(G, d, d, **bf), partials=torch.empty(G * 64, **f32),
+                      vmean=torch.empty(G, n_stat, **f32), scale=torch.empty(G, n_stat, **f32))
+            self._scratch[key] = sc
+        return sc
+
+    def scratch_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for sc in self._scratch.values() for t in sc.values())
 
     def adamw_group(self, st, grad, pv, step, lr, b1, b2, eps, wd):
         n = grad.numel()
@@ -487,8 +512,8 @@ class OptimKernels:
         dev = pv.device
         L = K.lib()
         s = K._stream()
-        x = torch.empty(G, m, n, dtype=torch.bfloat16, device=dev)
-        sumsq = torch.empty(G, dtype=torch.float32, device=dev)
+        sc = self.scratch(G, m, n, dev)
+        x, x2, A, Cm, sumsq, vmean, scale = sc["x"], sc["x2"], sc["A"], sc["C"], sc["partials"], sc["vmean"], sc["scale"]
         if isinstance(grad, PeerGrad):
             K._check(L.arb_muon_nesterov_rs(st["momentum"].data_ptr(), grad.peer_ptrs, grad.world, grad.rank, grad.mc,
                                             grad.offset, grad.scale, x.data_ptr(), sumsq.data_ptr(), m * n, G, mu, s),
@@ -498,10 +523,6 @@ class OptimKernels:
                                          m * n, G, mu, s), "muon_nesterov")
         K._check(L.arb_muon_frob_scale(x.data_ptr(), sumsq.data_ptr(), m * n, G, s), "muon_frob_scale")
         tall = m > n
-        d = n if tall else m
-        A = torch.empty(G, d, d, dtype=torch.bfloat16, device=dev)
-        Cm = torch.empty(G, d, d, dtype=torch.bfloat16, device=dev)
-        x2 = torch.empty_like(x)
         for a, b, c in MA.POLAR_EXPRESS[:ns_steps]:
             if tall:
                 K.gemm(x, x, trans_a=True, trans_b=False, out=A)          # X^T X
@@ -515,8 +536,6 @@ class OptimKernels:
             x, x2 = x2, x
         n_stat = m if m >= n else n
         red = n if m >= n else m
-        vmean = torch.empty(G, n_stat, dtype=torch.float32, device=dev)
-        scale = torch.empty(G, n_stat, dtype=torch.float32, device=dev)
         K._check(L.arb_normuon_stats(x.data_ptr(), vmean.data_ptr(), G, m, n, s), "normuon_stats")
         K._check(L.arb_normuon_scales(vmean.data_ptr(), st["second"].data_ptr(), scale.data_ptr(), G, n_stat, red,
                                       beta2, s), "normuon_scales")
@@ -537,7 +556,9 @@ class Sm100Backend(OracleBackend):
         self.big_ce_chunk = 16384
 
     def optim_kernels(self):
-        return OptimKernels()
+        if getattr(self, "_optim_kernels", None) is None:
+            self._optim_kernels = OptimKernels()      # one scratch pool for all optimizers of this backend
+        return self._optim_kernels
 
     def embedding(self, ids, w):
         return EmbeddingFn.apply(ids.contiguous(), w)

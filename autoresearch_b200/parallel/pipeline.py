@@ -128,6 +128,11 @@ class PipelineTrainer(TrainerBase):
         B, T = self.micro_batch, mcfg.seq_len
         self._d = [(torch.empty(B, T, dtype=torch.int32, device=self.device),
                     torch.empty(B, T, dtype=torch.int32, device=self.device)) for _ in range(self.accum)]
+        # a stage keeps the forward tensors of up to (pp - stage) micro-batches in flight
+        in_flight = min(pp - self.stage, self.accum)
+        self.plan_memory(dp=self.dp, n_layer_local=(hi - lo) * in_flight, has_embedding=self.first, has_head=self.last,
+                         fused_dp=fused and self.dp > 1, act_bytes=2 if self.dtype == torch.bfloat16 else 4,
+                         ce_chunk=max(mcfg.ce_chunk, getattr(self.backend, "big_ce_chunk", 0)))
         if tcfg.resume and tcfg.checkpoint_dir:
             self._resume()
 

@@ -198,11 +198,10 @@ class FusedTPContext(TPContext):
         """Sum of the `size` source slabs of staging half `half` -> [n, D] bf16 (local reads only)."""
         K = self.K
         base = self.rs.tensor.data_ptr() + half * self.max_rows * self.D * 2
-        ptrs = (C.c_void_p * (self.size + 1))(*([base + s * self.n_max * self.D * 2 for s in range(self.size)] + [0]))
-        out32 = torch.empty(n, D, dtype=torch.float32, device=self.device)
-        K._check(K.lib().arb_reduce_scatter_peers(ptrs, self.size, 0, n * D, 1, out32.data_ptr(), 1.0, K._stream()),
-                 "tp_reduce_slabs")
-        return out32.to(torch.bfloat16)
+        ptrs = (C.c_void_p * self.size)(*[base + s * self.n_max * self.D * 2 for s in range(self.size)])
+        out = torch.empty(n, D, dtype=torch.bfloat16, device=self.device)
+        K._check(K.lib().arb_sum_slabs_bf16(ptrs, self.size, n * D, out.data_ptr(), K._stream()), "tp_reduce_slabs")
+        return out
 
     def _slab(self, dst_rank, half, n, D):
         """Rank `dst_rank`'s staging slab for rows sent by this rank, as an [n, D] tensor."""
@@ -219,9 +218,15 @@ class FusedTPContext(TPContext):
         half = self.n_rs & 1
         self.n_rs += 1
         self.bytes += (N - n) * D * 2
-        for i in range(self.size):
-            r = (self.rank + 1 + i) % self.size
-            self._slab(r, half, n, D).copy_(x[r * n:(r + 1) * n])
+        # one kernel of this package stores every row block into its owner's slab (peer stores over NVLink)
+        x = x.contiguous()
+        K = self.K
+        order = [(self.rank + 1 + i) % self.size for i in range(self.size)]
+        off = (half * self.max_rows + self.rank * self.n_max) * self.D * 2
+        src = (C.c_void_p * self.size)(*[x.data_ptr() + r * n * D * 2 for r in order])
+        dst = (C.c_void_p * self.size)(*[self.rs.peer_ptrs[r] + off for r in order])
+        nb = (C.c_longlong * self.size)(*[n * D * 2] * self.size)
+        K._check(K.lib().arb_pull_ranges(src, dst, nb, self.size, K._stream()), "tp_push_rows")
         self.barrier()
         return self._reduce_slabs(half, n, D)
 
@@ -380,7 +385,9 @@ class TPTrainer(TrainerBase):
         self.wsd = WSDState(tcfg.max_steps, tcfg.cooldown_steps, tcfg.schedule_cfg.warmdown_ratio,
                             int(round(tcfg.schedule_cfg.warmup_ratio * (tcfg.max_steps or 0))))
         self._init_common()
-        self.h2d_bytes_per_step = 2 * self.micro_batch * mcfg.seq_len * 4 * self.accum
+        self.plan_memory(dp=self.dp, tp=tp, fused_dp=fused and self.dp > 1,
+                         act_bytes=2 if self.dtype == torch.bfloat16 else 4,
+                         ce_chunk=max(mcfg.ce_chunk, getattr(self.backend, "big_ce_chunk", 0)))
         if tcfg.resume and tcfg.checkpoint_dir:
             self._resume()
 

@@ -91,6 +91,9 @@ class Trainer(TrainerBase):
         self.wsd = WSDState(tcfg.max_steps, tcfg.cooldown_steps, tcfg.schedule_cfg.warmdown_ratio,
                             warmup_steps=int(round(tcfg.schedule_cfg.warmup_ratio * (tcfg.max_steps or 0))))
         self._init_common()
+        self.plan_memory(dp=self.world, ep=self.ep, fused_dp=(self.comm.name == "fused"),
+                         act_bytes=2 if self.dtype == torch.bfloat16 else 4,
+                         ce_chunk=max(mcfg.ce_chunk, getattr(self.backend, "big_ce_chunk", 0)))
         if tcfg.resume and tcfg.checkpoint_dir:
             self._resume()
 

@@ -36,6 +36,7 @@ def main() -> int:
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (world = tp x dp); dense models")
     ap.add_argument("--ep", type=int, default=1, help="expert-parallel group size (MoE models; 1 or the world size)")
+    ap.add_argument("--pp", type=int, default=1, help="pipeline stages (world = pp x dp); one process per stage, 1F1B")
     ap.add_argument("--layers", type=int, default=None, help="debug only: marks the result invalid")
     args = ap.parse_args()
 
@@ -77,19 +78,29 @@ def main() -> int:
         args.micro_batch = 64 if args.model == "phase1" else 4
         if args.impl == "baseline" and args.model != "phase1":
             args.micro_batch = 2   # the library arm keeps every autograd intermediate: 4 x 32768 tokens do not fit
+    # MFU denominator: the pool's measured cuBLAS bf16 burst rate when the driver's record is beside this file
+    peak, peak_kind = 1.59e15, "fallback"
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            peak, peak_kind = float(json.load(f)["bf16_tflops"]) * 1e12, "measured"
+    except Exception:
+        pass
+    model_par = max(1, args.tp) * max(1, args.pp)
     tcfg = TrainConfig(device_batch_size=args.micro_batch, total_batch_size=args.total_batch,
                        max_steps=1000, cooldown_steps=300, synthetic_data=True, synthetic_kind="zipf",
-                       impl=args.impl, schedule_cfg=sched, cooldown_trigger_file="",
-                       parallel=ParallelConfig(dp=world // max(1, args.tp), tp=args.tp, ep=args.ep, comm=args.comm))
+                       impl=args.impl, schedule_cfg=sched, cooldown_trigger_file="", peak_flops=peak,
+                       parallel=ParallelConfig(dp=world // model_par, tp=args.tp, ep=args.ep, pp=args.pp, comm=args.comm))
     if args.tp > 1:
         from autoresearch_b200.parallel.tp import TPTrainer
         tr = TPTrainer(mcfg, tcfg, tp=args.tp, device=f"cuda:{local}", quiet=True)
-        tr.comm = type("C", (), {"name": f"tp-{tr.backend.tp.mode}"})()
-        tr.h2d_bytes_per_step = tr.micro_batch * mcfg.seq_len * 8 * tr.accum
-        from autoresearch_b200.utils.timing import measured_peak_flops
-        tr.peak_flops = measured_peak_flops()
+        comm_name = tr.comm_name
+    elif args.pp > 1:
+        from autoresearch_b200.parallel.pipeline import PipelineTrainer
+        tr = PipelineTrainer(mcfg, tcfg, pp=args.pp, device=f"cuda:{local}", quiet=True)
+        comm_name = f"pp-nccl-p2p+dp-{tr.comm.name}"
     else:
         tr = Trainer(mcfg, tcfg, device=f"cuda:{local}", quiet=True)
+        comm_name = tr.comm.name
     if args.attn and hasattr(tr.backend, "attn"):
         tr.backend.attn = args.attn
 
@@ -118,7 +129,7 @@ def main() -> int:
     t0 = time.perf_counter()
     last = None
     for _ in range(args.steps):
-        last = float(tr.train_step().item())
+        last = tr.global_loss(tr.train_step()) if model_par > 1 else float(tr.train_step().item())
     sync()
     e2e_s = time.perf_counter() - t0
     K.check_err_flag()
@@ -126,7 +137,7 @@ def main() -> int:
         t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_s = float(t[0].item()), float(t[1].item())
-    tokens_step = tr.micro_batch * mcfg.seq_len * tr.accum * (world // max(1, args.tp))
+    tokens_step = tr.tokens_per_step
     value = tokens_step * args.steps / (ms / 1e3)
     e2e = tokens_step * args.steps / e2e_s
     valid = args.layers is None and args.seq_len is None and args.model == "phase2" and args.total_batch == 524288
@@ -143,7 +154,8 @@ def main() -> int:
                    "global_batch": tokens_step, "seq_len": mcfg.seq_len,
                    "micro_batch_per_gpu": tr.micro_batch, "grad_accum": tr.accum,
                    "parallelism": (f"tp{args.tp}xdp{world // args.tp}" if args.tp > 1 else
-                                   (f"dp{world} ep{args.ep}" if args.ep > 1 else f"dp{world}")), "comm": tr.comm.name,
+                                   (f"pp{args.pp}xdp{world // args.pp}" if args.pp > 1 else
+                                    (f"dp{world} ep{args.ep}" if args.ep > 1 else f"dp{world}"))), "comm": comm_name,
                    "attention": getattr(tr.backend, "attn", "library"),
                    "l2": "inputs larger than L2 (per-step working set of tens of GB)",
                    "valid_headline_config": valid},
@@ -151,7 +163,7 @@ def main() -> int:
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": tr.h2d_bytes_per_step,
                 "d2h_bytes_per_step": 4, "last_loss": last},
         "gpu_launches": launches,
-        "mfu_vs_measured_peak": round(mcfg.flops_per_token() * value / (tr.peak_flops * world), 4),
+        f"mfu_vs_{peak_kind}_peak": round(mcfg.flops_per_token() * value / (peak * world), 4),
     }
     if rank == 0:
         print(json.dumps(out), flush=True)

@@ -66,6 +66,7 @@ def test_dp2_matches_single_gpu():
     # after a step the dense weights owned by the other rank wait for the GEMMs that will pull them
     assert fused["pending_pulls"] > 0 and lib["pending_pulls"] == 0
     for a, b, c in zip(one["losses"], fused["losses"], lib["losses"]):
-        assert abs(a - b) < 0.05 * abs(a) + 0.02, (one, fused)
-        assert abs(a - c) < 0.05 * abs(a) + 0.02, (one, lib)
+        # every decomposition sees the identical global batch: only the bf16 summation order differs
+        assert abs(a - b) < 1e-2, (one, fused)
+        assert abs(a - c) < 1e-2, (one, lib)
     assert fused["losses"][-1] < fused["losses"][0]

@@ -159,6 +159,35 @@ def test_adamw_and_muon_kernels_match_reference():
         _close(st["second"], rsec, 5e-2, "second moment")
 
 
+def test_muon_step_is_bitwise_reproducible_and_handles_ragged_shapes():
+    """The Frobenius norm is summed in a fixed order (no atomics), so two runs of a Muon step from the same state
+    give the same bits; a matrix whose column count is not a multiple of 8 takes the scalar kernels."""
+    from autoresearch_b200.ops.sm100 import OptimKernels
+    from autoresearch_b200.optim import muon_adamw as MA
+    torch.manual_seed(11)
+    ok = OptimKernels()
+    for (G, m, nn) in [(5, 512, 256), (2, 192, 1024), (3, 256, 264)]:
+        master = torch.randn(G, m, nn, device="cuda") * 0.05
+        grad = torch.randn(G, m, nn, device="cuda") * 0.01
+        sshape = (G, m, 1) if m >= nn else (G, 1, nn)
+        outs = []
+        for _ in range(2):
+            st = dict(master=master.clone(), momentum=torch.zeros_like(master), second=torch.zeros(sshape, device="cuda"))
+            pv = master.to(torch.bfloat16)
+            for _ in range(2):
+                ok.muon_group(st, grad, pv, 0.9, 0.02, 0.1, 0.95, 5)
+            outs.append((st["master"].clone(), st["momentum"].clone(), pv.clone()))
+        for a, b in zip(*outs):
+            assert torch.equal(a, b)
+        rmaster, rmom, rsec = master.clone(), torch.zeros_like(master), torch.zeros(sshape, device="cuda")
+        for _ in range(2):
+            u = MA.muon_nesterov(rmom, grad, 0.9, torch.bfloat16)
+            MA.cautious_update(rmaster, MA.normuon(MA.newton_schulz(MA.frob_normalise(u), 5), rsec, 0.95), 0.02, 0.1)
+        upd, rupd = outs[0][0] - master, rmaster - master
+        assert (upd - rupd).norm() / rupd.norm() < 0.05
+    assert ok.scratch_bytes() > 0
+
+
 def test_embedding_backward_sorted_is_exact_and_deterministic():
     """The sorted, atomic-free embedding gradient: equal to an fp64 index_add within fp32 rounding, bitwise
     reproducible, also with ids that fill many 64-row work items and ids that never occur."""

@@ -73,3 +73,59 @@ def test_two_stage_pipeline_matches_single_process(tmp_path):
     assert res["accum"] == 4 and res["bytes"] > 0
     for a, b in zip(ref, res["losses"]):
         assert abs(a - b) < 2e-3, (ref, res)
+
+
+def test_merged_schedule_respects_stage_order_and_dependencies():
+    from autoresearch_b200.parallel.pipeline_inproc import merged_schedule
+    for P in (1, 2, 3, 4):
+        for M in (1, 2, 5, 8):
+            order = merged_schedule(P, M)
+            assert len(order) == 2 * P * M
+            seen = set()
+            for s, k, i in order:
+                if k == "F" and s > 0:
+                    assert (s - 1, "F", i) in seen
+                if k == "B":
+                    assert (s, "F", i) in seen
+                    if s < P - 1:
+                        assert (s + 1, "B", i) in seen
+                seen.add((s, k, i))
+            for s in range(P):
+                assert [(k, i) for ss, k, i in order if ss == s] == one_f_one_b(s, P, M)
+
+
+def test_in_process_pipeline_matches_single_stage_and_resumes(tmp_path):
+    """The one-process pipeline driver on two (CPU) 'devices': same losses as the plain trainer, per-stage
+    checkpoints under stage_{i}/, and an exact resume."""
+    import torch
+    from autoresearch_b200.config import TrainConfig, model_preset
+    from autoresearch_b200.models.init import init_weights
+    from autoresearch_b200.parallel.pipeline_inproc import InProcPipelineTrainer
+    from autoresearch_b200.trainer import Trainer
+    cfg = model_preset("tiny")
+
+    def tc(**kw):
+        t = TrainConfig(device_batch_size=2, total_batch_size=8 * 128, max_steps=10, cooldown_steps=3, synthetic_data=True,
+                        synthetic_kind="zipf", impl="oracle", cooldown_trigger_file="", **kw)
+        t.init_scheme = "normal"
+        return t
+
+    one = Trainer(cfg, tc(), device="cpu", quiet=True)
+    init_weights(one.model, seed=42, scheme="normal")
+    for gi, st in one.opt.state.items():
+        st["master"].copy_(one.layout.group_view(one.layout.flat_param, one.layout.groups[gi]).float())
+    ref = [float(one.train_step()) for _ in range(5)]
+    one.prefetch.close()
+    pp = InProcPipelineTrainer(cfg, tc(checkpoint_dir=str(tmp_path)), ["cpu", "cpu"], quiet=True)
+    assert pp.accum == 4 and pp.world == 2
+    got = [float(pp.train_step()) for _ in range(3)]
+    pp.save()
+    pp.prefetch.close()
+    assert (tmp_path / "stage_0" / "model.safetensors").exists() and (tmp_path / "stage_1" / "optim_state.safetensors").exists()
+    again = InProcPipelineTrainer(cfg, tc(checkpoint_dir=str(tmp_path), resume=True), ["cpu", "cpu"], quiet=True)
+    assert again.step == 3
+    got += [float(again.train_step()) for _ in range(2)]
+    again.prefetch.close()
+    assert pp.comm_bytes > 0
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 2e-3, (ref, got)

@@ -30,7 +30,81 @@ def test_oracle_dump_files(tmp_path):
 
 def test_compare_train_identical_implementations_agree(tmp_path):
     r = compare_train.run("tiny", "oracle", "oracle", steps=4, batch=2, csv_path=str(tmp_path / "c.csv"), device="cpu")
-    assert r["max_rel"] == 0.0 and (tmp_path / "c.csv").read_text().startswith("step,oracle,oracle,rel_diff")
+    assert r["max_rel"] == 0.0 and (tmp_path / "c.csv").read_text().startswith("step,loss_oracle,loss_oracle,rel_diff")
+
+
+def test_compare_train_init_weights_streamed_rows_and_proxy_eval(tmp_path):
+    """--init-weights, --stream-input (rows replayed to both implementations) and the proxy evaluation column."""
+    import io
+    import numpy as np
+    init = tmp_path / "init.safetensors"
+    generate_init_weights.generate("tiny", str(init), scheme="torch", init_scale=1.0, python_names=True)
+    rng = np.random.default_rng(1)
+    rows = rng.integers(1, 256, size=(2 * 6 + 2 * 2, 129), dtype=np.uint16)
+    got = compare_train.read_rows(io.BytesIO(rows.astype("<u2").tobytes() + b"\x01"), 128, None)   # trailing partial row ignored
+    assert np.array_equal(got, rows)
+    csvp = tmp_path / "s.csv"
+    r = compare_train.run("tiny", "oracle", "oracle", steps=6, batch=2, csv_path=str(csvp), device="cpu", cooldown=2,
+                          init_weights=str(init), rows=got, eval_every=3, eval_batches=2)
+    assert r["steps"] == 6 and r["max_rel"] == 0.0
+    assert sorted(r["evals"]["oracle"]) == [2, 5] and r["evals"]["oracle"][5] < r["evals"]["oracle"][2] + 1.0
+    lines = csvp.read_text().splitlines()
+    assert lines[0].endswith("val_bpb_oracle,val_bpb_oracle") and lines[3].split(",")[-1] != "" and lines[2].split(",")[-1] == ""
+    # the streamed rows, not the synthetic stream, were trained on: another stream gives another loss
+    r2 = compare_train.run("tiny", "oracle", "none", steps=2, batch=2, device="cpu", init_weights=str(init))
+    assert abs(r2["losses"]["oracle"][0] - r["losses"]["oracle"][0]) > 1e-4
+    compare_train.write_report(r, str(tmp_path / "p.md"), "t", "cmd")
+    assert "| step | oracle | oracle |" in (tmp_path / "p.md").read_text()
+
+
+def test_torch_order_init_matches_the_python_trainers_draws(tmp_path):
+    """scheme='torch' reproduces torch.manual_seed(42) followed by the upstream init_weights call order."""
+    import math
+    from autoresearch_b200.ckpt.safetensors_io import load_file
+    out = tmp_path / "t.safetensors"
+    generate_init_weights.generate("tiny", str(out), scheme="torch", init_scale=1.0)
+    sd = load_file(str(out))
+    D, V, M = 64, 256, 256
+    s = math.sqrt(3) * D ** -0.5
+    torch.manual_seed(42)
+    wte = torch.nn.init.normal_(torch.empty(V, D), 0.0, 1.0)
+    lm = torch.nn.init.normal_(torch.empty(V, D), 0.0, 0.001)
+    layers = []
+    for _ in range(2):
+        layers.append([torch.nn.init.uniform_(torch.empty(r, D), -s, s) for r in (D, D, D, M)])
+    ve1 = torch.nn.init.uniform_(torch.empty(V, D), -s, s)
+    bf = lambda t: t.to(torch.bfloat16)
+    assert torch.equal(sd["wte.weight"], bf(wte)) and torch.equal(sd["lm_head.weight"], bf(lm))
+    for i, (q, k, v, fc) in enumerate(layers):
+        assert torch.equal(sd[f"h.{i}.attn.c_q.weight"], bf(q)) and torch.equal(sd[f"h.{i}.attn.c_v.weight"], bf(v))
+        assert torch.equal(sd[f"h.{i}.attn.c_k.weight"], bf(k)) and torch.equal(sd[f"h.{i}.mlp.c_fc.weight"], bf(fc))
+    assert torch.equal(sd["ve.1.weight"], bf(ve1))
+
+
+def test_multi_epoch_store_spills_to_disk_and_replays_every_epoch(tmp_path):
+    from autoresearch_b200.tools import multi_epoch as ME
+
+    class Tok:
+        def encode(self, text, bos=True):
+            return [8188] + [ord(c) for c in text]
+
+    texts = [chr(65 + i) * (5 + 3 * i) for i in range(12)]
+    in_mem = ME.collect(texts, Tok(), 2, 33, None, mem_limit=1 << 30)
+    spilled = ME.collect(texts, Tok(), 2, 33, None, mem_limit=64, tmp_dir=str(tmp_path))
+    assert not in_mem.on_disk and spilled.on_disk and spilled.path.startswith(str(tmp_path))
+    assert len(in_mem) == len(spilled) == 12 and in_mem.n_tokens == spilled.n_tokens
+    a = [d.tolist() for d in ME.epoch_stream(in_mem, 3, seed=42)]
+    b = [d.tolist() for d in ME.epoch_stream(spilled, 3, seed=42)]
+    assert a == b and len(a) == 36
+    first, second = a[:12], a[12:24]
+    assert sorted(map(tuple, first)) == sorted(map(tuple, second)) and first != second     # same set, reshuffled
+    path = spilled.path
+    spilled.close()
+    import os
+    assert not os.path.exists(path)
+    # --target-rows: stop collecting once epochs x tokens covers the rows
+    few = ME.collect(texts, Tok(), 2, 33, target_rows=2, mem_limit=1 << 30)
+    assert len(few) < 12 and few.n_tokens * 2 >= 2 * 33
 
 
 def test_monitor_parses_reference_log_lines():

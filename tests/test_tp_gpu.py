@@ -63,6 +63,5 @@ def test_tp2_fused_and_library_follow_single_gpu():
     lib = run(2, "nccl", 29642)
     os.remove(path)
     assert fused["mode"] == "fused" and lib["mode"] == "library"
-    assert abs(one["losses"][0] - fused["losses"][0]) < 0.02
     for a, b, c in zip(one["losses"], fused["losses"], lib["losses"]):
-        assert abs(a - b) < 0.05 * abs(a) + 0.02 and abs(b - c) < 0.03 * abs(b) + 0.02, (one, fused, lib)
+        assert abs(a - b) < 1e-2 and abs(b - c) < 1e-2, (one, fused, lib)

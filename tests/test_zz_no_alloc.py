@@ -3,7 +3,8 @@
 For callers that cannot hand the library any scratch memory (a host without an allocator at
 hand, a thread that must not block in cudaMalloc), the statistic buffer of the backward pass
 sits in a fixed array inside the library.  The results must equal those of the regular entry
-point, also on a second call that reuses the array with a different problem size.
+point bit for bit (the kernels are deterministic), also on a second call that reuses the array with
+a different problem size.
 """
 import ctypes as C
 import math
@@ -43,8 +44,8 @@ def _case(lib, B, T, H, window, seed):
     assert rc == 0
     torch.cuda.synchronize()
     K.check_err_flag()
-    den = ref.float().abs().max().item() + 1e-6
-    assert (got.float() - ref.float()).abs().max().item() / den < 2e-2
+    # both entry points run the same deterministic kernels: the results are bitwise equal
+    assert torch.equal(got, ref)
 
 
 def test_noalloc_backward_matches_regular_entry_point_twice():
