@@ -214,6 +214,9 @@ class ParallelConfig:
     pp: int = 1
     # "fused" = peer-memory kernels, "nccl" = library collectives (the measured baseline)
     comm: str = "fused"
+    # gradient buckets by depth for the fused data-parallel exchange: > 1 starts the reduce-scatter and the owner
+    # update of the upper layers while the backward pass is still working on the lower ones; 1 = after the backward pass
+    dp_buckets: int = 3
 
     @property
     def world(self) -> int:

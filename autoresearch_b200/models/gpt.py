@@ -91,6 +91,11 @@ class GPT(nn.Module):
         self.register_buffer("rope_cos", cos.to(tdt), persistent=False)
         self.register_buffer("rope_sin", sin.to(tdt), persistent=False)
         self.aux_loss = None
+        # {layer: bucket}: when the backward pass has produced the gradient of that layer's input, the parameter
+        # gradients of gradient bucket `bucket` (that layer and everything above it) are final; the trainer sets
+        # `grad_bucket_cb(bucket)` for the micro-step after which the data-parallel exchange may start early
+        self.grad_bucket_boundaries = {}
+        self.grad_bucket_cb = None
 
     # ------------------------------------------------------------------
     def embed(self, ids: torch.Tensor) -> torch.Tensor:
@@ -105,6 +110,9 @@ class GPT(nn.Module):
         aux_total = None
         for bi, blk in enumerate(self.blocks):
             l = blk.layer
+            if self.grad_bucket_cb is not None and l in self.grad_bucket_boundaries and x.requires_grad:
+                cb, b = self.grad_bucket_cb, self.grad_bucket_boundaries[l]
+                x.register_hook(lambda g, cb=cb, b=b: cb(b))
             with nvtx_range(f"layer {l}"):
                 x, xn = be.resid_scale_norm(x, x0, self.resid_lambdas, self.x0_lambdas, bi)
                 a = be.attention_block(xn, blk, ids_flat, B, T, cfg, self.rope_cos, self.rope_sin,

@@ -5,10 +5,12 @@ Wr^T) in fp32; top-k experts, gates renormalised over the selected ones; y = sum
 Expert_k(xn) with Expert(x) = relu(x Wfc^T)^2 Wproj^T; auxiliary load-balance loss
 coeff * E * sum_e f_e P_e.  Differences from the reference: fixed-capacity expert buffers (token
 order decides who is dropped when an expert is over capacity; the reference never drops), no
-host synchronisation when a capacity factor is set, experts run as ONE strided-batched tcgen05
-GEMM per projection instead of a host loop over cuBLAS calls, deterministic slot order, and
-optional expert parallelism where dispatch and combine go through NVLink peer pointers
-(``parallel.ep``).
+host synchronisation when a capacity factor is set, deterministic slot order, and the experts run
+as ONE ragged grouped tcgen05 GEMM per projection instead of a host loop over cuBLAS calls: the
+kernel reads the per-expert row counts from device memory, skips the tiles beyond them (the
+capacity padding is never multiplied) and cuts the K range of the weight-gradient products to the
+rows that hold data.  With expert parallelism (``parallel.ep``) dispatch and combine go through
+NVLink peer pointers and the owner's GEMMs read the received slabs in place.
 """
 from __future__ import annotations
 
@@ -43,14 +45,21 @@ def _gather_rows(tab, idx, row, n_rows, k, D, E, resid=None, gates=None):
     return out
 
 
+def _finish(L, s, table, cnt_table, counts, keep, cap, D, E, tile):
+    K._check(L.arb_moe_finish_dispatch(table, cnt_table, counts.data_ptr(), keep, cap, D, E, tile, s), "moe_finish_dispatch")
+
+
 class MoEFn(torch.autograd.Function):
     """(out, aux) = (resid + MoE(xn), load-balance loss).  w_fc [E_local, M, D], w_proj [E_local, D, M];
     with expert parallelism (`ep`) E_local = E / world and the router still scores all E experts."""
 
+    TILE = 256
+
     @staticmethod
-    def forward(ctx, xn, resid, router_w, w_fc, w_proj, top_k, aux_coeff, capacity_factor, ep):
+    def forward(ctx, xn, resid, router_w, w_fc, w_proj, top_k, aux_coeff, capacity_factor, ep, layer):
         N, D = xn.shape
         E = router_w.shape[0]
+        M = w_fc.shape[1]
         dev = xn.device
         L, s = K.lib(), K._stream()
         probs = torch.empty(N, E, dtype=torch.float32, device=dev)
@@ -65,81 +74,91 @@ class MoEFn(torch.autograd.Function):
         scratch = torch.empty(((S + 1023) // 1024) * E, dtype=torch.int32, device=dev)
         K._check(L.arb_moe_slot_positions(idx.data_ptr(), S, E, scratch.data_ptr(), pos.data_ptr(), counts.data_ptr(), s),
                  "moe_slot_positions")
+        # `keep`: slots an expert accepts (the rule of ops.reference.moe_capacity); `cap`: rows of a slab, a multiple
+        # of 64 (K blocks of the weight-gradient products)
         if ep is not None:
-            cap = ep.cap_src
+            keep, cap = ep.keep, ep.cap_src
         elif capacity_factor > 0:
-            cap = R.moe_capacity(N, E, top_k, capacity_factor)
+            keep = R.moe_capacity(N, E, top_k, capacity_factor)
+            cap = (keep + 63) // 64 * 64
         else:
-            cap = (int(counts.max().item()) + 7) // 8 * 8     # never drop: one host read per layer
-        row = torch.where(pos < cap, pos, torch.full_like(pos, -1)).contiguous()
+            # never drop (the reference's behaviour): the buffer size depends on the routing, one host read per layer
+            keep = int(counts.max().item())
+            cap = (keep + 63) // 64 * 64
+        row = torch.where(pos < keep, pos, torch.full_like(pos, -1)).contiguous()
         f = counts.float() / float(N * top_k)
         aux = aux_coeff * E * (f * probs.mean(0)).sum()
+        T_ = MoEFn.TILE
         if ep is None:
-            xg = torch.zeros(E, cap, D, dtype=torch.bfloat16, device=dev)
-            K._check(L.arb_moe_dispatch(xn.data_ptr(), _ptr_table(xg), idx.data_ptr(), row.data_ptr(), N, top_k, D, E, s),
-                     "moe_dispatch")
-            act = K.gemm(xg, w_fc, epi=K.EPI_RELU2)
-            y = K.gemm(act, w_proj)
-            out = _gather_rows(_ptr_table(y), idx, row, N, top_k, D, E, resid, gates)
-            y_rows = None
+            W = 1
+            xg = torch.empty(E, cap, D, dtype=torch.bfloat16, device=dev)
+            y = torch.empty(E, cap, D, dtype=torch.bfloat16, device=dev)
+            mv = torch.empty(E, dtype=torch.int32, device=dev)
+            x_tab, y_tab = _ptr_table(xg), _ptr_table(y)
+            cnt_tab = (C.c_void_p * E)(*[mv.data_ptr() + 4 * e for e in range(E)])
+            K._check(L.arb_moe_dispatch(xn.data_ptr(), x_tab, idx.data_ptr(), row.data_ptr(), N, top_k, D, E, s), "moe_dispatch")
+            _finish(L, s, x_tab, cnt_tab, counts, keep, cap, D, E, T_)
         else:
-            ep.local("x").zero_()
-            ep.barrier()                                      # every owner has cleared its slabs
-            K._check(L.arb_moe_dispatch(xn.data_ptr(), ep.table("x"), idx.data_ptr(), row.data_ptr(), N, top_k, D, E, s),
-                     "moe_dispatch")
-            ep.barrier()                                      # all routed tokens have arrived
-            xg = ep.local("x").clone()
-            act = K.gemm(xg, w_fc, epi=K.EPI_RELU2)
-            cs = ep.cap_src
-            for i in range(ep.world):                         # peers first: their tiles have the longer way
-                r = (ep.rank + 1 + i) % ep.world
-                K.gemm(act[:, r * cs:(r + 1) * cs], w_proj, out=ep.recv_view("y", r))
-            ep.barrier()                                      # every expert's outputs for my tokens have arrived
-            out = _gather_rows(ep.recv_table("y"), idx, row, N, top_k, D, E, resid, gates)
-            # unscaled expert outputs of this rank's own slots, kept for the gate gradient
-            y_rows = _gather_rows(ep.recv_table("y"), idx.view(-1, 1), row.view(-1, 1), N * top_k, 1, D, E)
-            y = None
-        ctx.save_for_backward(xn, router_w, w_fc, w_proj, probs, idx, gates, row, xg, act,
-                              y if y is not None else y_rows, f)
-        ctx.cfg = (top_k, aux_coeff, ep)
+            W = ep.world
+            x_tab, y_tab = ep.table("x", layer), ep.table("y", layer)
+            K._check(L.arb_moe_dispatch(xn.data_ptr(), x_tab, idx.data_ptr(), row.data_ptr(), N, top_k, D, E, s), "moe_dispatch")
+            _finish(L, s, x_tab, ep.table("cnt", layer), counts, keep, cap, D, E, T_)
+            ep.barrier()                                      # all routed tokens and their counts have arrived
+            xg, y, mv = ep.local("x", layer), ep.local("y", layer), ep.local("cnt", layer)
+        act = torch.empty(xg.shape[0], cap, M, dtype=torch.bfloat16, device=dev)
+        K.gemm(xg, w_fc, out=act, epi=K.EPI_RELU2, m_valid=mv, b_div=W)
+        K.gemm(act, w_proj, out=y, m_valid=mv, b_div=W)
+        if ep is not None:
+            ep.barrier()                                      # every expert's outputs are complete
+        out = _gather_rows(y_tab, idx, row, N, top_k, D, E, resid, gates)
+        ctx.save_for_backward(xn, router_w, w_fc, w_proj, probs, idx, gates, row, xg, act, y, f, counts, mv)
+        ctx.cfg = (top_k, aux_coeff, ep, layer, keep, cap)
         return out, aux
 
     @staticmethod
     def backward(ctx, d_out, g_aux):
-        xn, router_w, w_fc, w_proj, probs, idx, gates, row, xg, act, y_or_rows, f = ctx.saved_tensors
-        top_k, aux_coeff, ep = ctx.cfg
+        xn, router_w, w_fc, w_proj, probs, idx, gates, row, xg, act, y, f, counts, mv = ctx.saved_tensors
+        top_k, aux_coeff, ep, layer, keep, cap = ctx.cfg
         N, D = xn.shape
         E = router_w.shape[0]
+        El = w_fc.shape[0]
         dev = xn.device
         L, s = K.lib(), K._stream()
+        T_ = MoEFn.TILE
         d_out = d_out.contiguous()
         d_gates = torch.empty(N, top_k, dtype=torch.float32, device=dev)
         if ep is None:
-            dy = torch.zeros_like(y_or_rows)
-            K._check(L.arb_moe_combine_bwd(d_out.data_ptr(), _ptr_table(y_or_rows), 0, _ptr_table(dy), idx.data_ptr(),
-                                           row.data_ptr(), gates.data_ptr(), d_gates.data_ptr(), N, top_k, D, E, s),
-                     "moe_combine_bwd")
+            W = 1
+            dy = torch.empty_like(y)
+            d_xg = torch.empty_like(xg)
+            y_tab, dy_tab, dx_tab = _ptr_table(y), _ptr_table(dy), _ptr_table(d_xg)
         else:
-            ep.local("dy").zero_()
-            ep.barrier()
-            K._check(L.arb_moe_combine_bwd(d_out.data_ptr(), 0, y_or_rows.data_ptr(), ep.table("dy"), idx.data_ptr(),
-                                           row.data_ptr(), gates.data_ptr(), d_gates.data_ptr(), N, top_k, D, E, s),
-                     "moe_combine_bwd")
+            W = ep.world
+            y_tab, dy_tab, dx_tab = ep.table("y", layer), ep.table("dy"), ep.table("dx")
+            dy, d_xg = ep.local("dy"), ep.local("dx")
+        # d(expert output) = gate * d_out scattered to the owners; d(gate) = <expert output, d_out> (outputs read in place)
+        K._check(L.arb_moe_combine_bwd(d_out.data_ptr(), y_tab, 0, dy_tab, idx.data_ptr(), row.data_ptr(), gates.data_ptr(),
+                                       d_gates.data_ptr(), N, top_k, D, E, s), "moe_combine_bwd")
+        _finish(L, s, dy_tab, None, counts, keep, cap, D, E, T_)
+        if ep is not None:
             ep.barrier()                                      # every source has pushed gate * d_out
-            dy = ep.local("dy").clone()
-        d_act = K.gemm(dy, w_proj, trans_b=False, epi=K.EPI_RELU2_BWD, aux=act)
-        g_proj = _acc_grad(w_proj, dy, act)
-        g_fc = _acc_grad(w_fc, d_act, xg)
-        if ep is None:
-            d_xg = K.gemm(d_act, w_fc, trans_b=False)
-            d_xn = _gather_rows(_ptr_table(d_xg), idx, row, N, top_k, D, E)
-        else:
-            cs = ep.cap_src
-            for i in range(ep.world):
-                r = (ep.rank + 1 + i) % ep.world
-                K.gemm(d_act[:, r * cs:(r + 1) * cs], w_fc, trans_b=False, out=ep.recv_view("dx", r))
-            ep.barrier()                                      # the input gradients of my tokens have arrived
-            d_xn = _gather_rows(ep.recv_table("dx"), idx, row, N, top_k, D, E)
+        d_act = torch.empty_like(act)
+        K.gemm(dy, w_proj, trans_b=False, out=d_act, epi=K.EPI_RELU2_BWD, aux=act, m_valid=mv, b_div=W)
+        kv = mv.view(El, W)
+        flat = lambda t: t.view(El, W * cap, t.shape[-1])
+
+        def acc_grad(w, a, b):
+            mg = getattr(w, "main_grad", None)
+            tgt = mg if mg is not None else torch.zeros(w.shape, dtype=torch.float32, device=dev)
+            K.gemm(flat(a), flat(b), trans_a=True, trans_b=False, out=tgt, epi=K.EPI_ATOMIC_F32, k_valid=kv, k_seg=cap)
+            return None if mg is not None else tgt.to(w.dtype)
+
+        g_proj = acc_grad(w_proj, dy, act)
+        g_fc = acc_grad(w_fc, d_act, xg)
+        K.gemm(d_act, w_fc, trans_b=False, out=d_xg, m_valid=mv, b_div=W)
+        if ep is not None:
+            ep.barrier()                                      # the input gradients of my tokens are complete
+        d_xn = _gather_rows(dx_tab, idx, row, N, top_k, D, E)
         aux_dp = None
         if g_aux is not None and aux_coeff != 0.0:
             aux_dp = ((g_aux.float() * (aux_coeff * E / float(N))) * f).contiguous()
@@ -151,4 +170,4 @@ class MoEFn(torch.autograd.Function):
         d_logits = d_logits[:, :E]
         d_xn = K.gemm(d_logits, router_w, trans_b=False, epi=K.EPI_ADD_AUX, aux=d_xn)
         g_router = _acc_grad(router_w, d_logits, xn)
-        return d_xn, d_out, g_router, g_fc, g_proj, None, None, None, None
+        return d_xn, d_out, g_router, g_fc, g_proj, None, None, None, None, None

@@ -51,6 +51,21 @@ int arb_gemm_bf16(const void* A, const void* B, void* C, const void* aux, int M,
                   long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha, float beta,
                   float gamma, int* err_flag, cudaStream_t stream);
 
+// The same with ragged batches (grouped expert GEMMs; device arrays, read by the kernel, no host synchronisation):
+//   m_valid[batch]     rows of each batch item that hold data; output tiles starting at or beyond it are skipped
+//                      (neither computed nor written).  b_div: B is indexed by batch_item / b_div, so b_div row slabs
+//                      share one weight matrix (B then holds batch / b_div matrices).
+//   k_valid[batch * (K / k_seg_rows)]   for EPI_ATOMIC_F32 products whose K dimension runs over rows: K is a sequence
+//                      of segments of k_seg_rows rows (a multiple of 64), and of every segment only the 64-row blocks
+//                      below k_valid are multiplied.  Rows between k_valid and the next multiple of 64 must be zero in
+//                      at least one operand.
+int arb_gemm_bf16_ragged(const void* A, const void* B, void* C, const void* aux, int M, int N, int K, int batch,
+                         long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                         long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha, float beta,
+                         float gamma, int* err_flag, cudaStream_t stream, const void* pull_src, long long pull_bytes,
+                         const void* ahead_src, void* ahead_dst, long long ahead_bytes, const int* m_valid, int b_div,
+                         const int* k_valid, int k_seg_rows);
+
 // Tile selection: 0 = automatic (2-CTA 256x256 tiles when M >= 512 and N >= 256, else 1-CTA
 // 128x256/128x128), 1 = always 1-CTA, 2 = always 2-CTA.  Process-wide; meant for tests / benchmarks.
 int arb_gemm_set_mode(int mode);
@@ -197,6 +212,11 @@ int arb_moe_router_bwd(const float* probs, const int* idx, const float* gates, c
 int arb_moe_slot_positions(const int* idx, long long S, int E, int* scratch, int* pos, int* counts, cudaStream_t s);
 int arb_moe_dispatch(const void* x, void* const* expert_bufs, const int* idx, const int* row, long long N, int K,
                      int D, int E, cudaStream_t s);
+// After a dispatch (or the backward's scatter of output gradients): *count_slots[e] = c = min(counts[e], keep), keep <= cap
+// = rows of a slab, when the slot pointer is non-null (with expert parallelism it points into the owner's row-count table: a peer store), and rows
+// [c, next multiple of `tile`) of expert e's slab are zeroed (the grouped GEMMs work in whole tiles of `tile` rows).
+int arb_moe_finish_dispatch(void* const* expert_bufs, int* const* count_slots, const int* counts, int keep, int cap, int D,
+                            int E, int tile, cudaStream_t s);
 // out[t] = resid[t] + sum_k gates[t,k] * buf[idx][row]  (resid / gates may be null: 0 / 1)
 int arb_moe_combine_fwd(const void* resid, void* const* expert_bufs, const int* idx, const int* row,
                         const float* gates, void* out, long long N, int K, int D, int E, cudaStream_t s);

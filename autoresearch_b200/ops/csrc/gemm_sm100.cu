@@ -50,7 +50,33 @@ struct GemmArgs {
   const uint4* ahead_src;
   uint4* ahead_dst;
   long long ahead_n16;
+  // Ragged batches (grouped expert GEMMs).  All three roles of a CTA evaluate the same predicates, so an item that
+  // is skipped touches no barrier and no output.
+  //   m_valid[b]   rows of batch item b that hold data: M-tiles that start at or beyond it are skipped.
+  //   b_div        the B operand (and nothing else) is indexed by b / b_div: several row slabs share one weight.
+  //   k_valid[b * k_nseg + seg]  (fp32-accumulate GEMMs whose K runs over rows) the K range is k_nseg segments of
+  //                k_seg_kb 64-row blocks; of segment seg only the blocks below k_valid are multiplied.
+  const int* m_valid;
+  int b_div;
+  const int* k_valid;
+  int k_seg_kb, k_nseg;
 };
+
+// K blocks of [kb0, kb1) of batch item b that are multiplied
+__device__ __forceinline__ bool kb_live(const GemmArgs& p, int b, int kb) {
+  if (!p.k_valid) return true;
+  const int seg = kb / p.k_seg_kb;
+  return (kb - seg * p.k_seg_kb) * BK < p.k_valid[b * p.k_nseg + seg];
+}
+__device__ __forceinline__ bool item_live(const GemmArgs& p, int b, int m_start, int kb0, int kb1) {
+  if (p.m_valid && m_start >= p.m_valid[b]) return false;
+  if (p.k_valid) {
+    for (int kb = kb0; kb < kb1; ++kb)
+      if (kb_live(p, b, kb)) return true;
+    return false;
+  }
+  return true;
+}
 
 __device__ __forceinline__ uint4 ld_peer16(const uint4* a) {
   uint4 v;
@@ -232,9 +258,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int b = t / p.splitk;
         const int kb0 = ks * p.kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        if (!item_live(p, b, mt * BM, kb0, kb1)) continue;
+        const int bB = b / p.b_div;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!kb_live(p, b, kb)) continue;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          ++it;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + s * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
@@ -249,9 +279,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (B_MN) {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_3d(sb + c * 8192, &tmB, &full_bar[s], nt * BN + c * 64, kb * BK, b);
+              tma_load_3d(sb + c * 8192, &tmB, &full_bar[s], nt * BN + c * 64, kb * BK, bB);
           } else {
-            tma_load_3d(sb, &tmB, &full_bar[s], kb * BK, nt * BN, b);
+            tma_load_3d(sb, &tmB, &full_bar[s], kb * BK, nt * BN, bB);
           }
         }
       }
@@ -267,19 +297,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++tile_it) {
-        int t = w / (p.n_tiles * p.m_tiles);
+      for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+        int t = w / p.n_tiles;
+        const int mt = t % p.m_tiles; t /= p.m_tiles;
         const int ks = t % p.splitk;
+        const int b = t / p.splitk;
         const int kb0 = ks * p.kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        if (!item_live(p, b, mt * BM, kb0, kb1)) continue;
         const int acc = tile_it & 1;
         const uint32_t aph = (tile_it >> 1) & 1;
+        ++tile_it;
         if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        bool first = true;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!kb_live(p, b, kb)) continue;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          ++it;
           if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
@@ -288,8 +325,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t ad = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 0, 1024);
             const uint64_t bd = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 0, 1024);
-            tc_mma_ss(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            tc_mma_ss(d_tmem, ad, bd, idesc, (!first || k > 0) ? 1u : 0u);
           }
+          first = false;
           tc_commit(&empty_bar[s]);
         }
         if (ok) tc_commit(&tfull_bar[acc]);
@@ -302,13 +340,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int q = warp & 3;
     uint32_t tile_it = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++tile_it) {
+    for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
       int t = w;
       const int nt = t % p.n_tiles; t /= p.n_tiles;
       const int mt = t % p.m_tiles; t /= p.m_tiles;
+      const int ks = t % p.splitk;
       const int b = t / p.splitk;
+      {
+        const int kb0 = ks * p.kb_per_split;
+        if (!item_live(p, b, mt * BM, kb0, min(p.kb_total, kb0 + p.kb_per_split))) continue;
+      }
       const int acc = tile_it & 1;
       const uint32_t aph = (tile_it >> 1) & 1;
+      ++tile_it;
       if (!mbar_wait(&tfull_bar[acc], aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = mt * BM + q * 32 + lane;
@@ -415,9 +459,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
         const int m0 = mt * 256 + int(rank) * 128;
         const int n0 = nt * 256 + int(rank) * 128;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        if (!item_live(p, b, mt * 256, kb0, kb1)) continue;
+        const int bB = b / p.b_div;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!kb_live(p, b, kb)) continue;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          ++it;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + s * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
@@ -433,9 +481,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (B_MN) {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tma_load_3d_pair(sb + c * 8192, &tmB, lead_bar, n0 + c * 64, kb * BK, b);
+            for (int c = 0; c < 2; ++c) tma_load_3d_pair(sb + c * 8192, &tmB, lead_bar, n0 + c * 64, kb * BK, bB);
           } else {
-            tma_load_3d_pair(sb, &tmB, lead_bar, kb * BK, n0, b);
+            tma_load_3d_pair(sb, &tmB, lead_bar, kb * BK, n0, bB);
           }
         }
       }
@@ -445,19 +493,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = make_idesc_bf16(256, BN2, A_MN, B_MN);
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
-      for (int w = cluster_id; w < items && ok; w += n_clusters, ++tile_it) {
-        int t = w / (p.n_tiles * p.m_tiles);
+      for (int w = cluster_id; w < items && ok; w += n_clusters) {
+        int t = w / p.n_tiles;
+        const int mt = t % p.m_tiles; t /= p.m_tiles;
         const int ks = t % p.splitk;
+        const int b = t / p.splitk;
         const int kb0 = ks * p.kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        if (!item_live(p, b, mt * 256, kb0, kb1)) continue;
         const int acc = tile_it & 1;
         const uint32_t aph = (tile_it >> 1) & 1;
+        ++tile_it;
         if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN2;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        bool first = true;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!kb_live(p, b, kb)) continue;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          ++it;
           if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
@@ -466,8 +521,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t ad = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 0, 1024);
             const uint64_t bd = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 0, 1024);
-            tc_mma_ss_pair(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            tc_mma_ss_pair(d_tmem, ad, bd, idesc, (!first || k > 0) ? 1u : 0u);
           }
+          first = false;
           const uint32_t eb = smem_u32(&empty_bar[s]);
           tc_commit_pair(eb);
           tc_commit_pair(mapa_u32(eb, 1));
@@ -485,13 +541,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;
     uint32_t tile_it = 0, slab_it = 0;
     bool ok = true;
-    for (int w = cluster_id; w < items; w += n_clusters, ++tile_it) {
+    for (int w = cluster_id; w < items; w += n_clusters) {
       int t = w;
       const int nt = t % p.n_tiles; t /= p.n_tiles;
       const int mt = t % p.m_tiles; t /= p.m_tiles;
+      const int ks = t % p.splitk;
       const int b = t / p.splitk;
+      {
+        const int kb0 = ks * p.kb_per_split;
+        if (!item_live(p, b, mt * 256, kb0, min(p.kb_total, kb0 + p.kb_per_split))) continue;
+      }
       const int acc = tile_it & 1;
       const uint32_t aph = (tile_it >> 1) & 1;
+      const bool first_tile = tile_it == 0;
+      ++tile_it;
       // after a time-out keep walking the loop (named barriers below need all four warps) but skip waits
       if (ok && !mbar_wait(&tfull_bar[acc], aph, abort_flag)) ok = false;
       tc_fence_after();
@@ -538,7 +601,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
-        if (L::AUX && t0 && tile_it == 0) {               // first aux slab of this CTA's first tile
+        if (L::AUX && t0 && first_tile) {                 // first aux slab of this CTA's first tile
           mbar_expect_tx(&xfull_bar[0], 16384);
           tma_load_3d(smem + L::X_STAGE, &tmX, &xfull_bar[0], nt * BN2, row0, b);
         }
@@ -551,7 +614,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (L::AUX) {
             if (t0) {                                      // prefetch the next aux slab (this tile or the next one)
               int nsl = sl + 1, nw = w;
-              if (nsl == 4) { nsl = 0; nw = w + n_clusters; }
+              if (nsl == 4) {                              // the next item of this cluster that is not skipped
+                nsl = 0;
+                for (nw = w + n_clusters; nw < items; nw += n_clusters) {
+                  int tt = nw / p.n_tiles;
+                  const int nmt = tt % p.m_tiles; tt /= p.m_tiles;
+                  const int nks = tt % p.splitk;
+                  const int nkb0 = nks * p.kb_per_split;
+                  if (item_live(p, tt / p.splitk, nmt * 256, nkb0, min(p.kb_total, nkb0 + p.kb_per_split))) break;
+                }
+              }
               if (nw < items) {
                 int tt = nw;
                 const int nnt = tt % p.n_tiles; tt /= p.n_tiles;
@@ -771,7 +843,20 @@ extern "C" int arb_gemm_bf16_ex(const void* A, const void* B, void* C, const voi
                                 long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha,
                                 float beta, float gamma, int* err_flag, cudaStream_t stream, const void* pull_src,
                                 long long pull_bytes, const void* ahead_src, void* ahead_dst, long long ahead_bytes) {
+  return arb_gemm_bf16_ragged(A, B, C, aux, M, N, K, batch, lda, ldb, ldc, stride_a, stride_b, stride_c, a_mn_major, b_mn_major,
+                              epi, splitk, alpha, beta, gamma, err_flag, stream, pull_src, pull_bytes, ahead_src, ahead_dst,
+                              ahead_bytes, nullptr, 1, nullptr, 0);
+}
+
+extern "C" int arb_gemm_bf16_ragged(const void* A, const void* B, void* C, const void* aux, int M, int N, int K, int batch,
+                                    long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                                    long long stride_c, int a_mn_major, int b_mn_major, int epi, int splitk, float alpha,
+                                    float beta, float gamma, int* err_flag, cudaStream_t stream, const void* pull_src,
+                                    long long pull_bytes, const void* ahead_src, void* ahead_dst, long long ahead_bytes,
+                                    const int* m_valid, int b_div, const int* k_valid, int k_seg_rows) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -3;
+  if (b_div < 1 || batch % b_div) return -3;
+  if (k_valid && (k_seg_rows <= 0 || (k_seg_rows % BK) || (K % k_seg_rows) || epi != EPI_ATOMIC_F32)) return -3;
   if (pull_src && bad_copy(pull_src, B, pull_bytes)) return -3;
   if (ahead_src && bad_copy(ahead_src, ahead_dst, ahead_bytes)) return -3;
   // TMA needs 16-byte aligned bases and row strides; vector epilogue needs ldc % 8 == 0.
@@ -822,6 +907,9 @@ extern "C" int arb_gemm_bf16_ex(const void* A, const void* B, void* C, const voi
   a.ahead_src = reinterpret_cast<const uint4*>(ahead_src);
   a.ahead_dst = reinterpret_cast<uint4*>(ahead_dst);
   a.ahead_n16 = ahead_src ? ahead_bytes / 16 : 0;
+  a.m_valid = m_valid; a.b_div = b_div; a.k_valid = k_valid;
+  a.k_seg_kb = k_valid ? k_seg_rows / BK : 1;
+  a.k_nseg = k_valid ? K / k_seg_rows : 1;
 
   CUtensorMap ta, tb;
   {
@@ -836,6 +924,7 @@ extern "C" int arb_gemm_bf16_ex(const void* A, const void* B, void* C, const voi
     if (r) return 1000 + r;
     if (b_mn_major) { dims[0] = uint64_t(N); dims[1] = uint64_t(K); box[0] = 64; box[1] = BK; }
     else { dims[0] = uint64_t(K); dims[1] = uint64_t(N); box[0] = BK; box[1] = uint32_t(pair ? 128 : BN); }
+    dims[2] = uint64_t(batch / b_div);
     str[0] = uint64_t(ldb) * 2;
     str[1] = batch > 1 ? uint64_t(stride_b) * 2 : dims[1] * str[0];
     r = make_tmap_bf16(&tb, B, 3, dims, str, box);

@@ -100,6 +100,23 @@ __global__ void __launch_bounds__(256) moe_dispatch_k(const __nv_bfloat16* __res
     *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(x + t * D + c);
 }
 
+// After a dispatch: for every expert e, c = min(counts[e], keep) (keep <= cap = rows of a slab) is written to *cnt[e] (the entry of this source in the
+// owner's row-count table; a peer store with expert parallelism) and the rows [c, next multiple of `tile`) of the
+// expert's slab are zeroed, so that the grouped GEMMs, which work in whole tiles and skip everything beyond, never
+// multiply stale rows.  grid (E, tile / 8), one warp per row.
+struct CountPtrs { int* p[MOE_MAX_E]; };
+__global__ void __launch_bounds__(256) moe_finish_dispatch_k(ExpertPtrs bufs, CountPtrs cnt, const int* __restrict__ counts, int keep,
+                                                             int cap, int D, int tile) {
+  const int e = blockIdx.x;
+  const int c = min(counts[e], keep);
+  if (blockIdx.y == 0 && threadIdx.x == 0 && cnt.p[e]) *cnt.p[e] = c;
+  const int r = c + int(blockIdx.y) * 8 + (threadIdx.x >> 5);
+  const int end = min((c + tile - 1) / tile * tile, cap);
+  if (r >= end) return;
+  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(bufs.p[e]) + (long long)r * D;
+  for (int col = (threadIdx.x & 31) * 8; col < D; col += 256) *reinterpret_cast<uint4*>(dst + col) = make_uint4(0, 0, 0, 0);
+}
+
 // out[t] = resid[t] + sum_k gate[t,k] * y_buf[idx][row]       (one warp per token)
 __global__ void __launch_bounds__(256) moe_combine_fwd_k(const __nv_bfloat16* __restrict__ resid, ExpertPtrs bufs, const int* __restrict__ idx,
                                                          const int* __restrict__ row, const float* __restrict__ gates,
@@ -259,6 +276,17 @@ int arb_moe_dispatch(const void* x, void* const* expert_bufs, const int* idx, co
   int rc = fill_ptrs(ep, expert_bufs, E);
   if (rc || N <= 0 || (D & 7)) return rc ? rc : -3;
   moe_dispatch_k<<<unsigned((N * K + 7) / 8), 256, 0, s>>>((const bf16*)x, ep, idx, row, N * K, K, D);
+  return int(cudaGetLastError());
+}
+
+int arb_moe_finish_dispatch(void* const* expert_bufs, int* const* count_slots, const int* counts, int keep, int cap, int D, int E,
+                            int tile, cudaStream_t s) {
+  ExpertPtrs ep;
+  int rc = fill_ptrs(ep, expert_bufs, E);
+  if (rc || cap <= 0 || keep < 0 || keep > cap || (D & 7) || tile < 8 || tile > 256 || (tile & 7)) return rc ? rc : -3;
+  CountPtrs cp;
+  for (int e = 0; e < E; ++e) cp.p[e] = count_slots ? count_slots[e] : nullptr;
+  moe_finish_dispatch_k<<<dim3(unsigned(E), unsigned(tile / 8)), 256, 0, s>>>(ep, cp, counts, keep, cap, D, tile);
   return int(cudaGetLastError());
 }
 

@@ -29,14 +29,29 @@ inline int make_tmap_typed(CUtensorMap* out, const void* base, int rank, const u
                            bool swizzle128 = true) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
+  // The encoder is a driver call and needs a context current in the calling thread.  A thread that has made no
+  // runtime call yet (an autograd worker whose first operation is a GEMM, e.g. a pipeline stage without the loss)
+  // has none: one runtime call binds the device's primary context to the thread.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   cuuint64_t d[5];
   cuuint64_t s[4];
   cuuint32_t b[5], e[5];
   for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; e[i] = 1; }
   for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
-  CUresult r = fn(out, dtype, cuuint32_t(rank), const_cast<void*>(base), d, s, b, e,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  auto encode = [&]() {
+    return fn(out, dtype, cuuint32_t(rank), const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {   // the thread switched devices without a runtime call in between
+    cudaFree(nullptr);
+    r = encode();
+  }
   return int(r);
 }
 

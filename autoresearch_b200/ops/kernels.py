@@ -50,6 +50,8 @@ def lib() -> C.CDLL:
                           f32, f32, f32, vp, vp],
         "arb_gemm_bf16_ex": [vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32,
                              f32, f32, f32, vp, vp, vp, i64, vp, vp, i64],
+        "arb_gemm_bf16_ragged": [vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32,
+                                 f32, f32, f32, vp, vp, vp, i64, vp, vp, i64, vp, i32, vp, i32],
         "arb_attn_fwd": [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, f32, vp, vp],
         "arb_attn_bwd": [vp] * 11 + [i32, i32, i32] + [i64] * 8 + [i32, f32, vp, vp],
         "arb_rmsnorm_fwd": [vp, vp, i64, i32, f32, vp],
@@ -88,6 +90,7 @@ def lib() -> C.CDLL:
         "arb_moe_router_bwd": [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, vp],
         "arb_moe_slot_positions": [vp, i64, i32, vp, vp, vp, vp],
         "arb_moe_dispatch": [vp, vp, vp, vp, i64, i32, i32, i32, vp],
+        "arb_moe_finish_dispatch": [vp, vp, vp, i32, i32, i32, i32, i32, vp],
         "arb_moe_combine_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
         "arb_moe_combine_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
     }
@@ -152,12 +155,19 @@ def _row_major_2d(t: torch.Tensor, name: str):
 # --------------------------------------------------------------------------------------------
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = True,
          out: Optional[torch.Tensor] = None, epi: int = EPI_STORE_BF16, aux: Optional[torch.Tensor] = None,
-         splitk: int = 0, alpha: float = 0.0, beta: float = 0.0, gamma: float = 1.0) -> torch.Tensor:
+         splitk: int = 0, alpha: float = 0.0, beta: float = 0.0, gamma: float = 1.0,
+         m_valid: Optional[torch.Tensor] = None, b_div: int = 1, k_valid: Optional[torch.Tensor] = None,
+         k_seg: int = 0) -> torch.Tensor:
     """C = op(A) @ op(B) on the tcgen05 kernel.
 
     2-D or batched 3-D bf16 operands with unit inner stride.  ``trans_a=False``: ``a`` is
     [M, K]; True: ``a`` is [K, M] (A = a^T).  ``trans_b=True`` (default, "NT"): ``b`` is
     [N, K] (B = b^T); False: ``b`` is [K, N].
+
+    Ragged batches (grouped expert GEMMs): ``m_valid`` int32 [G] = rows of each batch item that hold data (output
+    tiles beyond are neither computed nor written); ``b_div``: ``b`` holds G / b_div matrices, item g uses matrix
+    g // b_div; ``k_valid`` int32 [G, K // k_seg] with ``k_seg`` rows per segment: for EPI_ATOMIC_F32 products over
+    rows, only the 64-row blocks below ``k_valid`` of each segment are multiplied.
     """
     _bf16(a, "a"); _bf16(b, "b")
     batched = a.dim() == 3
@@ -165,6 +175,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         G = a.shape[0]
         a2, b2 = a[0], b[0]
         sa, sb = a.stride(0), b.stride(0)
+        if b.shape[0] * b_div != G:
+            raise ValueError(f"b holds {b.shape[0]} matrices for {G} batch items with b_div={b_div}")
     else:
         G, a2, b2, sa, sb = 1, a, b, 0, 0
     _row_major_2d(a2, "a"); _row_major_2d(b2, "b")
@@ -206,13 +218,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         if ax2.stride(0) != o2.stride(0) or tuple(ax2.shape) != (M, N) or (batched and aux.stride(0) != so):
             raise ValueError("aux must have the layout of out")
         auxp = aux.data_ptr()
+    for t, n_want, nm in ((m_valid, G, "m_valid"), (k_valid, G * (K // k_seg) if k_seg else -1, "k_valid")):
+        if t is not None and (t.dtype != torch.int32 or not t.is_cuda or not t.is_contiguous() or t.numel() != n_want):
+            raise ValueError(f"{nm} must be a contiguous CUDA int32 tensor of {n_want} elements")
     try:
-        rc = lib().arb_gemm_bf16_ex(a.data_ptr(), b.data_ptr(), out.data_ptr(), auxp, M, N, K, G,
-                                    a2.stride(0), b2.stride(0), o2.stride(0), sa, sb, so,
-                                    int(trans_a), int(not trans_b), epi, splitk, alpha, beta, gamma,
-                                    err_flag(a.device).data_ptr(), _stream(),
-                                    pull[0] if pull else None, pull[1] if pull else 0,
-                                    ahead[1] if ahead else None, ahead[0] if ahead else None, ahead[2] if ahead else 0)
+        rc = lib().arb_gemm_bf16_ragged(a.data_ptr(), b.data_ptr(), out.data_ptr(), auxp, M, N, K, G,
+                                        a2.stride(0), b2.stride(0), o2.stride(0), sa, sb, so,
+                                        int(trans_a), int(not trans_b), epi, splitk, alpha, beta, gamma,
+                                        err_flag(a.device).data_ptr(), _stream(),
+                                        pull[0] if pull else None, pull[1] if pull else 0,
+                                        ahead[1] if ahead else None, ahead[0] if ahead else None, ahead[2] if ahead else 0,
+                                        m_valid.data_ptr() if m_valid is not None else None, b_div,
+                                        k_valid.data_ptr() if k_valid is not None else None, k_seg)
         _check(rc, "arb_gemm_bf16")
     except Exception:
         # nothing was launched: the copies are still owed

@@ -373,19 +373,30 @@ class AttentionFn(torch.autograd.Function):
 
 
 class LibraryAttentionFn(torch.autograd.Function):
-    """Library attention (flash-attn) on the packed buffer: the comparison arm."""
+    """Library attention on the packed buffer (a comparison arm: everything else stays on this package's kernels):
+    cuDNN's fused attention through torch SDPA for full-causal layers, flash-attn 2 for sliding windows."""
 
     @staticmethod
     def forward(ctx, qkv, B, T, H, window):
-        from flash_attn import flash_attn_func
         Dl = H * 128
         with torch.enable_grad():
             src = qkv.detach().requires_grad_(True)
             q = src[:, :Dl].view(B, T, H, 128)
             k = src[:, Dl:2 * Dl].view(B, T, H, 128)
             v = src[:, 2 * Dl:].view(B, T, H, 128)
-            ws = (window, 0) if window < T else (-1, -1)
-            o = flash_attn_func(q, k, v, causal=True, window_size=ws)
+            o = None
+            if window >= T:
+                from torch.nn.attention import SDPBackend, sdpa_kernel
+                try:
+                    with sdpa_kernel([SDPBackend.CUDNN_ATTENTION]):
+                        o = torch.nn.functional.scaled_dot_product_attention(
+                            q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True).transpose(1, 2)
+                except RuntimeError:
+                    o = None
+            if o is None:
+                from flash_attn import flash_attn_func
+                ws = (window, 0) if window < T else (-1, -1)
+                o = flash_attn_func(q, k, v, causal=True, window_size=ws)
         ctx.src, ctx.o = src, o
         return o.detach().reshape(B * T, Dl)
 
@@ -618,7 +629,7 @@ class Sm100Backend(OracleBackend):
         """x + MoE(xn) and the auxiliary loss; `self.ep` (an EPContext) switches on expert parallelism."""
         from ..models.moe import MoEFn
         return MoEFn.apply(xn, x, blk.router, blk.expert_fc, blk.expert_proj, moe.top_k, moe.aux_coeff,
-                           moe.capacity_factor, getattr(self, "ep", None))
+                           moe.capacity_factor, getattr(self, "ep", None), blk.layer)
 
     def lm_head_ce(self, xf, w, targets, grad_scale):
         need = torch.is_grad_enabled() and (xf.requires_grad or w.requires_grad)

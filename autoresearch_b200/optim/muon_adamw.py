@@ -149,11 +149,13 @@ class MuonAdamW:
         raise KeyError(kind)
 
     @torch.no_grad()
-    def step(self, step: int, progress: float, warmup_mult: float = 1.0, grad_source=None) -> None:
+    def step(self, step: int, progress: float, warmup_mult: float = 1.0, grad_source=None, bucket=None) -> None:
         """`step` is 1-indexed.  Expects the summed gradient of every owned group in
         ``layout.flat_grad``; writes the updated parameters into ``layout.flat_param``.
         ``grad_source(group)`` may return another gradient object for a group (the fused
-        data-parallel path hands out descriptors of the un-reduced peer buckets)."""
+        data-parallel path hands out descriptors of the un-reduced peer buckets).
+        ``bucket``: update only the groups of that gradient bucket (the overlapped exchange calls this once per
+        bucket, in the order in which the backward pass finishes them)."""
         c = self.cfg
         lr_mult = S.lr_multiplier(progress, c) * warmup_mult
         mu = S.muon_momentum(step, c)
@@ -161,6 +163,8 @@ class MuonAdamW:
         lay = self.layout
         for gi, st in self.state.items():
             g = lay.groups[gi]
+            if bucket is not None and g.bucket != bucket:
+                continue
             grad = grad_source(g) if grad_source is not None else None
             if grad is None:
                 grad = lay.group_view(lay.flat_grad, g)

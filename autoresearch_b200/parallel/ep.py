@@ -5,9 +5,16 @@ NVLink peer pointers into symmetric staging buffers.
 The reference has no expert parallelism (its MoE runs on one GPU and loops over the experts,
 brain/src/forward.rs:642-679).  Layout of every staging buffer on the rank that owns the
 experts: ``[E_local, world, cap_src, D]`` - one slab of ``cap_src`` rows per (local expert,
-source rank).  A source rank writes its routed tokens into its own slab of the owner's buffer
-(peer stores) and later reads the expert outputs back from the same rows (peer loads).  Three
-bounded flag barriers order zero-fill, dispatch, expert GEMMs and combine.
+source rank) - beside a row-count table ``[E_local, world]``.
+
+Forward of a layer: a source rank writes its routed tokens into its slab of the owner's ``x``
+buffer (peer stores), writes how many it sent into the owner's count table and zeroes the rows
+up to the next tile boundary; ONE bounded flag barrier; the owner runs its experts as ragged
+grouped GEMMs over the slabs in place (row counts from the table: empty tiles are skipped,
+nothing is copied or cleared); a second barrier; every source reads the expert outputs of its
+tokens straight from the owners' ``y`` buffers while it applies gates and residual (peer loads
+in the combine kernel).  The backward mirrors it with ``dy`` / ``dx``.  ``x`` and ``y`` exist
+once per layer (the backward needs them: nothing is cloned), ``dy`` / ``dx`` once.
 """
 from __future__ import annotations
 
@@ -22,6 +29,8 @@ from .symm import SymmBuffer
 
 
 class EPContext:
+    TILE = 256            # rows per GEMM tile: the dispatch zero-pads every slab to this boundary
+
     def __init__(self, group, device, n_experts: int, d_model: int, max_tokens: int, top_k: int,
                  capacity_factor: float):
         self.group = group
@@ -32,59 +41,63 @@ class EPContext:
         self.E, self.E_local, self.D, self.K = n_experts, n_experts // self.world, d_model, top_k
         if capacity_factor <= 0:
             raise ValueError("expert parallelism needs a capacity factor (fixed-size exchange buffers)")
-        self.cap_src = int(math.ceil(capacity_factor * max_tokens * top_k / n_experts))
-        self.cap_src = (self.cap_src + 7) // 8 * 8
+        # slots one source may send to one expert, and the rows of a slab: a multiple of 64 (K blocks of the
+        # weight-gradient GEMMs)
+        self.keep = (int(math.ceil(capacity_factor * max_tokens * top_k / n_experts)) + 7) // 8 * 8
+        self.cap_src = (self.keep + 63) // 64 * 64
         self.rows_local = self.E_local * self.world * self.cap_src
-        n = self.rows_local * d_model
+        self.G = self.E_local * self.world                    # slabs = batch items of the grouped GEMMs
         self.device = torch.device(device)
-        self.bufs = {name: SymmBuffer(n, torch.bfloat16, self.device, group) for name in ("x", "y", "dy", "dx")}
         self.flags = SymmBuffer(64, torch.int32, self.device, group)
-        for b in list(self.bufs.values()) + [self.flags]:
-            b.rendezvous()
-        dist.barrier(group=group)
+        self.flags.rendezvous()
         self._flag_ptrs = (C.c_void_p * self.world)(*self.flags.peer_ptrs)
         self.epoch = 0
-        self._tables = {name: self._expert_table(b) for name, b in self.bufs.items()}
+        self._bufs = {}
+        self._tables = {}
+        dist.barrier(group=group)
 
-    def _expert_table(self, buf: SymmBuffer):
-        """Pointer of this rank's slab inside every expert's buffer (host array of E pointers)."""
-        ptrs = []
-        slab = self.cap_src * self.D * 2
-        for e in range(self.E):
-            owner, el = divmod(e, self.E_local)
-            ptrs.append(buf.peer_ptrs[owner] + (el * self.world + self.rank) * slab)
-        return (C.c_void_p * self.E)(*ptrs)
+    # ---- buffers (created on first use: a collective, reached by all ranks in the same order) ------------
+    def buf(self, name: str, layer: int = -1) -> SymmBuffer:
+        key = (name, layer)
+        b = self._bufs.get(key)
+        if b is None:
+            if name == "cnt":
+                b = SymmBuffer(max(self.G, 16), torch.int32, self.device, self.group)
+            else:
+                b = SymmBuffer(self.rows_local * self.D, torch.bfloat16, self.device, self.group)
+            b.rendezvous()
+            self._bufs[key] = b
+        return b
 
-    def table(self, name: str):
-        return self._tables[name]
+    def table(self, name: str, layer: int = -1):
+        """For every expert e: pointer to THIS rank's slab inside the owner's buffer (host array of E pointers; peer
+        mappings for experts that live elsewhere).  For "cnt": pointer to this rank's entry in the owner's count table."""
+        key = (name, layer)
+        t = self._tables.get(key)
+        if t is None:
+            b = self.buf(name, layer)
+            unit = 4 if name == "cnt" else self.cap_src * self.D * 2
+            ptrs = []
+            for e in range(self.E):
+                owner, el = divmod(e, self.E_local)
+                ptrs.append(b.peer_ptrs[owner] + (el * self.world + self.rank) * unit)
+            t = (C.c_void_p * self.E)(*ptrs)
+            self._tables[key] = t
+        return t
 
-    def local(self, name: str) -> torch.Tensor:
-        """This rank's staging buffer viewed as [E_local, world * cap_src, D]."""
-        return self.bufs[name].tensor.view(self.E_local, self.world * self.cap_src, self.D)
-
-    # ---- receive side of the expert-output exchange -------------------------------------------------
-    # The "y" and "dx" buffers are laid out by the rank that RECEIVES them: [E, cap_src, D], expert e's rows for
-    # this rank's tokens.  The owner of expert e writes them with the epilogue of its output GEMM (TMA stores
-    # over NVLink), so the combine kernels read local memory only.
-    def recv_view(self, name: str, dst_rank: int) -> torch.Tensor:
-        """Rank `dst_rank`'s receive area for this rank's experts: [E_local, cap_src, D]."""
-        shape = (self.E_local, self.cap_src, self.D)
-        off = self.rank * self.E_local * self.cap_src * self.D
-        if dst_rank == self.rank:
-            return self.bufs[name].tensor[off: off + self.E_local * self.cap_src * self.D].view(shape)
-        return self.bufs[name].peer_tensor(dst_rank, shape, torch.bfloat16, off)
-
-    def recv_table(self, name: str):
-        """Local pointer of every expert's rows in this rank's receive area (host array of E pointers)."""
-        key = ("recv", name)
-        if key not in self._tables:
-            base = self.bufs[name].tensor.data_ptr()
-            slab = self.cap_src * self.D * 2
-            self._tables[key] = (C.c_void_p * self.E)(*[base + e * slab for e in range(self.E)])
-        return self._tables[key]
+    def local(self, name: str, layer: int = -1) -> torch.Tensor:
+        """This rank's own buffer as the batch of slabs the grouped GEMMs see: [E_local * world, cap_src, D]
+        (the count table: int32 [E_local * world])."""
+        t = self.buf(name, layer).tensor
+        if name == "cnt":
+            return t[:self.G]
+        return t.view(self.G, self.cap_src, self.D)
 
     def barrier(self):
         self.epoch += 1
         rc = K.lib().arb_peer_barrier(self._flag_ptrs, self.world, self.rank, self.epoch,
                                       K.err_flag(self.device).data_ptr(), K._stream())
         K._check(rc, "peer_barrier")
+
+    def symmetric_bytes(self) -> int:
+        return sum(b.tensor.numel() * b.tensor.element_size() for b in self._bufs.values())

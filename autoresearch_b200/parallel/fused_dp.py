@@ -18,6 +18,13 @@ Per optimizer step, on the compute stream:
    the tiles are computed (``GemmArgs::ahead_src``), so the transfer hides under the math; one small
    kernel pulls everything else (embeddings, head, scalars, gates, experts).
 
+Overlap with the backward pass (``exchange_bucket``): the parameters are laid out in gradient
+buckets by depth (``ParamLayout(bucket_of=...)``).  As soon as the last micro-step's backward
+has left a group of layers, steps 1-5 run for that bucket alone on a side stream - cast of its
+slices, barrier, fused reduce-scatter + owner update of its groups, barrier, pull of its small
+parameters - while the compute stream goes on with the earlier layers; only the last bucket
+(the first layers, embeddings and scalars) is left for after the backward pass.
+
 The library arm (``LibraryComm``) does the same with ncclReduceScatter / ncclAllGather and is
 what this path is measured against.
 """
@@ -50,6 +57,7 @@ class FusedComm:
         self._bucket: Optional[SymmBuffer] = None
         self._flags: Optional[SymmBuffer] = None
         self.epoch = 0
+        self._staged = {}
         K.lib()
 
     # the layout asks for its flat tensors through this hook: parameters go to symmetric memory
@@ -132,20 +140,67 @@ class FusedComm:
                                                 1.0, K._stream())
             K._check(rc, "reduce_scatter")
 
+    # ---- bucket by bucket, overlapped with the backward pass ------------------------------------------------
+    def exchange_bucket(self, layout: ParamLayout, bucket: int, run_optimizer, side: "torch.cuda.Stream") -> None:
+        """Called on the compute stream when the gradients of `bucket` are final.  The cast of the bucket's slices
+        stays on the compute stream (it reads what the backward kernels just wrote); everything that waits for peers
+        runs on `side`: barrier, `run_optimizer(bucket, grad_source)` (the owner update with the reduce-scatter fused
+        into its first kernel), barrier, and the pull of the bucket's small parameters.  The dense matrices of the
+        bucket are staged as pending pulls and handed to the GEMMs by ``activate_staged()`` once the compute stream has
+        joined the side stream."""
+        if bucket == 0:
+            K.flush_pending_pulls()   # normally empty: the forward pass has pulled every weight it used
+        for lo, hi in layout.bucket_ranges(bucket):
+            K.cast_f32_to_bf16(layout.flat_grad[lo:hi], self._bucket.tensor[lo:hi], 1.0)
+        ready = torch.cuda.Event()
+        ready.record()
+        L = K.lib()
+        with torch.cuda.stream(side):
+            side.wait_event(ready)
+            self.barrier()
+            src = self.grad_source(layout)
+            for g in layout.owned_groups(bucket):          # groups the fused optimizer kernels do not sum themselves
+                if src is not None and src(g) is not None:
+                    continue
+                n8 = (g.numel + 7) // 8 * 8
+                out = layout.flat_grad[g.offset:g.offset + n8]
+                if self._mc:
+                    rc = L.arb_reduce_scatter_multimem(self._mc, g.offset, n8, 1, out.data_ptr(), 1.0, K._stream())
+                else:
+                    rc = L.arb_reduce_scatter_peers(self._bucket_ptrs, self.world, g.offset, n8, 1, out.data_ptr(), 1.0,
+                                                    K._stream())
+                K._check(rc, "reduce_scatter")
+            run_optimizer(bucket, src)
+            self.barrier()
+            self._gather(layout, bucket, stage=True)
+
+    def activate_staged(self) -> None:
+        """Hands the staged dense matrices to the GEMMs of the next forward pass (call on the compute stream after
+        it has waited for the side stream)."""
+        order = K.pull_use_order
+        for dst, v in sorted(self._staged.items(), key=lambda kv: order.get(kv[0], 1 << 30)):
+            K.pending_pulls[dst] = v
+        self._staged = {}
+        K.pull_stream = K._stream()
+
     fuse_into_gemm = True
     GEMM_OPERANDS = (".wqkv", ".wo", ".wfc", ".wdn")
 
-    def _plan_gather(self, layout: ParamLayout):
-        """Per non-owned atom: pulled by its first GEMM, or part of a range copied right away.  Ranges are
-        the complement of the GEMM operands inside each peer's shard, merged and widened to 16 bytes (a
-        peer's shard holds only atoms that peer owns, so the neighbours copied along are current too)."""
+    def _plan_gather(self, layout: ParamLayout, bucket=None):
+        """Per non-owned atom (of one gradient bucket, or of all): pulled by its first GEMM, or part of a range copied
+        right away.  Ranges are the complement of the GEMM operands inside each peer's shard, merged and widened to 16
+        bytes (a peer's shard holds only atoms that peer owns, and inside a shard the atoms of a bucket are
+        neighbours, so what is copied along is current too)."""
         es = layout.flat_param.element_size()
         gemm_atoms, ranges = [], []
         for r in range(self.world):
             if r == self.rank:
                 continue
             lo, hi = layout.shard_range(r)
-            atoms = sorted((a for a in layout.atoms if a.owner == r), key=lambda a: a.offset)
+            atoms = sorted((a for a in layout.atoms if a.owner == r and (bucket is None or a.bucket == bucket)),
+                           key=lambda a: a.offset)
+            if bucket is not None and atoms:               # never widen into a neighbouring bucket's atoms
+                hi = min(hi, max(a.offset + a.numel for a in atoms) + 8)
             cur = None
             for a in atoms:
                 is_gemm = (self.fuse_into_gemm and a.name.endswith(self.GEMM_OPERANDS) and a.param.dim() == 2
@@ -164,17 +219,25 @@ class FusedComm:
 
     def all_gather_params(self, layout: ParamLayout) -> None:
         self.barrier()
-        if getattr(self, "_plan", None) is None:
-            self._plan = self._plan_gather(layout)
-        gemm_atoms, ranges = self._plan
+        self._gather(layout, None, stage=False)
+
+    def _gather(self, layout: ParamLayout, bucket, stage: bool) -> None:
+        plans = self.__dict__.setdefault("_plans", {})
+        if bucket not in plans:
+            plans[bucket] = self._plan_gather(layout, bucket)
+        gemm_atoms, ranges = plans[bucket]
         base = layout.flat_param.data_ptr()
         es = layout.flat_param.element_size()
         peers = self._param.peer_ptrs
-        # registered in the order in which the forward pass consumed them last time (unknown ones last), on this stream
-        order = K.pull_use_order
-        for a, r in sorted(gemm_atoms, key=lambda ar: order.get(base + ar[0].offset * es, 1 << 30)):
-            K.pending_pulls[base + a.offset * es] = (peers[r] + a.offset * es, a.numel * es)
-        K.pull_stream = K._stream()
+        if stage:
+            for a, r in gemm_atoms:
+                self._staged[base + a.offset * es] = (peers[r] + a.offset * es, a.numel * es)
+        else:
+            # registered in the order in which the forward pass consumed them last time (unknown ones last), on this stream
+            order = K.pull_use_order
+            for a, r in sorted(gemm_atoms, key=lambda ar: order.get(base + ar[0].offset * es, 1 << 30)):
+                K.pending_pulls[base + a.offset * es] = (peers[r] + a.offset * es, a.numel * es)
+            K.pull_stream = K._stream()
         if ranges:
             n = len(ranges)
             src = (C.c_void_p * n)(*[peers[r] + b0 for b0, _, r in ranges])

@@ -48,6 +48,7 @@ class Atom:
     units: List[Unit]
     owner: int = 0
     offset: int = 0
+    bucket: int = 0
 
     @property
     def numel(self) -> int:
@@ -67,6 +68,7 @@ class Group:
     offset: int
     count: int
     atoms: List[Atom] = field(default_factory=list)
+    bucket: int = 0
 
     @property
     def numel(self) -> int:
@@ -96,27 +98,37 @@ def _cost(atom: Atom) -> float:
 class ParamLayout:
     def __init__(self, named_groups: Sequence[Tuple[str, torch.nn.Parameter, str]],
                  world: int = 1, rank: int = 0, grad_dtype=torch.float32,
-                 allocator=None):
+                 allocator=None, bucket_of=None, n_buckets: int = 1):
         """named_groups: (name, parameter, kind) as returned by GPT.named_matrix_groups().
         allocator(numel, dtype, device) -> flat tensor (lets the caller place the flat
-        tensors in a symmetric peer-mapped heap)."""
+        tensors in a symmetric peer-mapped heap).
+        bucket_of(name) -> 0 .. n_buckets-1: parameters whose gradients become final together during the backward
+        pass (bucket 0 first).  Every shard holds its atoms bucket by bucket, so the slice of a bucket inside a shard
+        is one contiguous range, owners are balanced inside every bucket, and the gradient exchange and the
+        optimizer can run bucket by bucket while the backward pass is still at work on the later ones."""
         self.world, self.rank = world, rank
+        self.n_buckets = max(1, int(n_buckets))
         atoms = [Atom(n, p, k, _split_units(n, p, k)) for n, p, k in named_groups]
+        for a in atoms:
+            a.bucket = min(max(int(bucket_of(a.name)), 0), self.n_buckets - 1) if bucket_of is not None else 0
         self.atoms = atoms
         if not atoms:
             raise ValueError("no parameters")
         self.device = atoms[0].param.device
         self.param_dtype = atoms[0].param.dtype
         # ---- owner assignment (LPT greedy, deterministic) -----------------------------
-        load = [0.0] * world
-        for a in sorted(atoms, key=lambda a: (-_cost(a), a.name)):
-            r = min(range(world), key=lambda i: (load[i], i))
-            a.owner = r
-            load[r] += _cost(a)
+        total_load = [0.0] * world
+        for b in range(self.n_buckets):
+            load = [0.0] * world                      # balanced inside every bucket; ties go to the lighter rank overall
+            for a in sorted((a for a in atoms if a.bucket == b), key=lambda a: (-_cost(a), a.name)):
+                r = min(range(world), key=lambda i: (load[i], total_load[i], i))
+                a.owner = r
+                load[r] += _cost(a)
+                total_load[r] += _cost(a)
         # ---- offsets: per shard, sort atoms so equal-shape units are adjacent -----------
         def gkey(a: Atom):
             base = "muon" if a.kind.startswith("muon") else a.kind
-            return (0 if base == "muon" else 1, base, a.unit_shape)
+            return (a.bucket, 0 if base == "muon" else 1, base, a.unit_shape)
 
         self.groups: List[Group] = []
         sizes = []
@@ -130,9 +142,9 @@ class ParamLayout:
             gl: List[Group] = []
             for a in sorted(per_rank[r], key=lambda a: (gkey(a), a.name)):
                 k = gkey(a)
-                if cur is None or (cur.kind, cur.shape) != (k[1], k[2]):
+                if cur is None or (cur.bucket, cur.kind, cur.shape) != (k[0], k[2], k[3]):
                     off = (off + ALIGN - 1) // ALIGN * ALIGN
-                    cur = Group(k[1], k[2], r, off, 0)
+                    cur = Group(k[2], k[3], r, off, 0, bucket=k[0])
                     gl.append(cur)
                 a.offset = off
                 uo = off
@@ -172,8 +184,20 @@ class ParamLayout:
         r = self.rank if rank is None else rank
         return r * self.shard_size, (r + 1) * self.shard_size
 
-    def owned_groups(self) -> List[Group]:
-        return [g for g in self.groups if g.owner == self.rank]
+    def owned_groups(self, bucket: Optional[int] = None) -> List[Group]:
+        return [g for g in self.groups if g.owner == self.rank and (bucket is None or g.bucket == bucket)]
+
+    def bucket_ranges(self, bucket: int) -> List[Tuple[int, int]]:
+        """Per rank shard, the element range [lo, hi) (multiples of ALIGN) that holds the atoms of `bucket`."""
+        out = []
+        for r in range(self.world):
+            gs = [g for g in self.groups if g.owner == r and g.bucket == bucket]
+            if not gs:
+                continue
+            lo = min(g.offset for g in gs)
+            hi = max(g.offset + g.numel for g in gs)
+            out.append((lo, min((hi + ALIGN - 1) // ALIGN * ALIGN, (r + 1) * self.shard_size)))
+        return out
 
     def owned_atoms(self) -> List[Atom]:
         return [a for a in self.atoms if a.owner == self.rank]

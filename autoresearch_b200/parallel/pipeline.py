@@ -9,12 +9,14 @@ writes its checkpoint to ``rank_{r}/`` (brain/src/train.rs:1998-2002).
 
 What is different: the reference runs one micro-batch through all stages strictly in sequence
 (bubble (n-1)/n) with blocking sends and logs wall-clock time only; here micro-batches are
-interleaved one-forward-one-backward, the receive of the NEXT pass is posted before the current
-pass is computed and sends are never waited for before the end of the step, so transfers run
-under compute.  Activations and gradients travel on two separate communicators (one per
-direction): on each of them a rank only ever sends to, or only ever receives from, a given
-neighbour, so an early-posted receive can never sit in front of the send its peer is waiting
-for.  The gradient of ``x0`` is accumulated along the chain (each boundary carries d_x and d_x0
+interleaved one-forward-one-backward.  Transfers never block the host (a wait is a dependency
+of the compute stream on the transfer), sends are left in flight until the end of the step,
+and whenever a pass's output and the next pass's input travel between the same two stages
+(every pass of the steady state) the send and the receive are issued as ONE grouped NCCL
+operation.  That grouping is what keeps two neighbours from each sitting in a send the other
+has not posted a receive for; for the same reason receives are not posted a whole pass early:
+a receive kernel that spins for the length of a pass occupies a hardware queue which the
+compute stream, or the send its peer is waiting for, may share.  The gradient of ``x0`` is accumulated along the chain (each boundary carries d_x and d_x0
 back) instead of every stage sending its partial sum to stage 0.  Pipeline stages can be combined
 with data parallelism (rank = dp_index * n_stages + stage), whose gradient exchange is the same
 fused peer-memory path as in the plain data-parallel trainer.  Loop, logging, timing, evaluation,
@@ -89,15 +91,12 @@ class PipelineTrainer(TrainerBase):
         self.impl = impl
         self.dtype = torch.bfloat16 if on_gpu and impl != "oracle" else torch.float32
         self.backend = get_backend(impl, mcfg)
-        # process groups (collective creation: every rank calls all): one DP group per stage, and one
-        # communicator per transfer direction
+        # process groups (collective creation: every rank calls all): one DP group per stage
         self.dp_group = None
         for s in range(pp):
             g = dist.new_group([d * pp + s for d in range(self.dp)])
             if s == self.stage:
                 self.dp_group = g
-        self.fwd_group = dist.new_group()
-        self.bwd_group = dist.new_group()
         lo, hi = split_layers(mcfg.n_layer, pp)[self.stage]
         self.first, self.last = self.stage == 0, self.stage == pp - 1
         self.model = GPT(mcfg, self.backend, dtype=self.dtype, device=self.device, layer_range=(lo, hi),
@@ -166,29 +165,30 @@ class PipelineTrainer(TrainerBase):
     def _peer(self, stage: int) -> int:
         return self.dp_idx * self.pp + stage
 
-    def _send(self, tensors, dst_stage: int, group) -> list:
-        hs = []
-        for t in tensors:
-            t = t.contiguous()
-            self.comm_bytes += t.numel() * t.element_size()
-            hs.append((dist.isend(t, self._peer(dst_stage), group=group), t))
-        return hs
+    def _exchange(self, send, recv_from, act_shape):
+        """One grouped point-to-point operation: `send` = (tensors, stage) or None, `recv_from` = stage or None (two
+        tensors of `act_shape` are received).  Returns (received tensors, requests, tensors kept alive)."""
+        ops, bufs, keep = [], [], []
+        if send is not None:
+            for t in send[0]:
+                t = t.contiguous()
+                keep.append(t)
+                self.comm_bytes += t.numel() * t.element_size()
+                ops.append(dist.P2POp(dist.isend, t, self._peer(send[1])))
+        if recv_from is not None:
+            for _ in range(2):
+                b = torch.empty(act_shape, dtype=self.dtype, device=self.device)
+                bufs.append(b)
+                ops.append(dist.P2POp(dist.irecv, b, self._peer(recv_from)))
+        reqs = dist.batch_isend_irecv(ops) if ops else []
+        return bufs, reqs, keep
 
-    def _post_recv(self, op, act_shape) -> list:
-        """Receives that pass `op` of the schedule needs: activations (x, x0) from the previous stage for a forward,
-        gradients (d_x, d_x0) from the next stage for a backward."""
+    def _needs(self, op):
+        """The stage a pass receives its inputs from (None: it has them)."""
         kind, _ = op
-        if kind == "F" and not self.first:
-            src, group = self._peer(self.stage - 1), self.fwd_group
-        elif kind == "B" and not self.last:
-            src, group = self._peer(self.stage + 1), self.bwd_group
-        else:
-            return []
-        out = []
-        for _ in range(2):
-            buf = torch.empty(act_shape, dtype=self.dtype, device=self.device)
-            out.append((dist.irecv(buf, src, group=group), buf))
-        return out
+        if kind == "F":
+            return None if self.first else self.stage - 1
+        return None if self.last else self.stage + 1
 
     def train_step(self):
         m = self.mcfg
@@ -204,22 +204,31 @@ class PipelineTrainer(TrainerBase):
         grad_scale = 1.0 / (tokens_micro * self.accum * self.dp)
         batches = [self._stage_batch(i) for i in range(self.accum)]
         saved = {}
-        pending = []
+        in_flight = []            # requests (and their tensors) of sends that nobody has waited for yet
         self._loss_acc.zero_()
-        sched = self.sched
-        posted = {0: self._post_recv(sched[0], act_shape)}
-        for k, (kind, i) in enumerate(sched):
-            if k + 1 < len(sched):                                 # the next pass's inputs travel under this pass
-                posted[k + 1] = self._post_recv(sched[k + 1], act_shape)
-            got = posted.pop(k)
-            for h, _buf in got:
-                h.wait()
+        out_send = None           # (tensors, stage): what the previous pass produced for a neighbour
+        for kind, i in self.sched:
+            src = self._needs((kind, i))
+            got = []
+            if out_send is not None and src is not None and out_send[1] == src:
+                got, reqs, keep = self._exchange(out_send, src, act_shape)         # one grouped send + receive
+                out_send = None
+            else:
+                if out_send is not None:
+                    _, r0, k0 = self._exchange(out_send, None, act_shape)
+                    in_flight.append((r0, k0))
+                    out_send = None
+                reqs, keep = [], []
+                if src is not None:
+                    got, reqs, keep = self._exchange(None, src, act_shape)
+            for r in reqs:
+                r.wait()                                                             # the compute stream waits, not the host
             ids, tgt = batches[i]
             if kind == "F":
                 if self.first:
                     x_in = x0_in = None
                 else:
-                    x_in, x0_in = got[0][1], got[1][1]
+                    x_in, x0_in = got
                     x_in.requires_grad_(True); x0_in.requires_grad_(True)
                 out = self.model(ids, tgt, grad_scale=grad_scale, x_in=x_in, x0_in=x0_in)
                 if self.last:
@@ -228,7 +237,7 @@ class PipelineTrainer(TrainerBase):
                     saved[i] = (x_in, x0_in, scaled, None)
                 else:
                     x_out, x0_out = out
-                    pending += self._send([x_out.detach(), x0_out.detach()], self.stage + 1, self.fwd_group)
+                    out_send = ([x_out.detach(), x0_out.detach()], self.stage + 1)
                     saved[i] = (x_in, x0_in, x_out, x0_out)
             else:
                 x_in, x0_in, y, x0_out = saved.pop(i)
@@ -236,7 +245,7 @@ class PipelineTrainer(TrainerBase):
                     y.backward()
                     d_x0_down = None
                 else:
-                    d_x, d_x0_down = got[0][1], got[1][1]
+                    d_x, d_x0_down = got
                     if self.first:
                         # x0_out is the embedding output itself: both gradients enter the graph
                         torch.autograd.backward([y, x0_out], [d_x, d_x0_down])
@@ -247,9 +256,13 @@ class PipelineTrainer(TrainerBase):
                     g0 = x0_in.grad if x0_in.grad is not None else torch.zeros_like(x0_in)
                     if d_x0_down is not None:
                         g0 = g0 + d_x0_down
-                    pending += self._send([x_in.grad, g0], self.stage - 1, self.bwd_group)
-        for h, _keep in pending:
-            h.wait()
+                    out_send = ([x_in.grad, g0], self.stage - 1)
+        if out_send is not None:
+            _, r0, k0 = self._exchange(out_send, None, act_shape)
+            in_flight.append((r0, k0))
+        for reqs, _keep in in_flight:
+            for r in reqs:
+                r.wait()
         self.timer.mark("bwd_end")
         self.comm.reduce_scatter_grads(self.layout)
         progress = self.wsd.progress(self.step)
@@ -300,15 +313,16 @@ class PipelineTrainer(TrainerBase):
         def forward(ids, tgt):
             x_in = x0_in = None
             if not self.first:
-                got = self._post_recv(("F", 0), act_shape)
-                for h, _b in got:
-                    h.wait()
-                x_in, x0_in = got[0][1], got[1][1]
+                got, reqs, _ = self._exchange(None, self.stage - 1, act_shape)
+                for r in reqs:
+                    r.wait()
+                x_in, x0_in = got
             out = self.model(ids, tgt, x_in=x_in, x0_in=x0_in)
             if self.last:
                 return out[1], tgt
-            for h, _t in self._send([out[0], out[1]], self.stage + 1, self.fwd_group):
-                h.wait()
+            _, reqs, _keep = self._exchange(([out[0], out[1]], self.stage + 1), None, act_shape)
+            for r in reqs:
+                r.wait()
             return torch.zeros(0, device=self.device), tgt.reshape(-1)[:0]
 
         return eval_bpb(self.model, self._make_loader("val"), self.token_bytes, max_batches, self.device,

@@ -72,9 +72,24 @@ class Trainer(TrainerBase):
         groups = self.model.named_matrix_groups()
         expert_groups = [g for g in groups if g[2] == "muon_expert"] if self.ep > 1 else []
         dense_groups = [g for g in groups if g not in expert_groups]
-        self.layout = ParamLayout(dense_groups, self.world, self.rank, allocator=alloc)
+        # gradient buckets by depth (only the peer-memory exchange overlaps with the backward pass)
+        self.n_buckets = 1
+        bucket_of = None
+        if getattr(self.comm, "name", "") == "fused" and tcfg.parallel.dp_buckets > 1 and mcfg.n_layer >= 2:
+            self.n_buckets = min(int(tcfg.parallel.dp_buckets), mcfg.n_layer)
+            bucket_of = self._bucket_of
+        self.layout = ParamLayout(dense_groups, self.world, self.rank, allocator=alloc, bucket_of=bucket_of,
+                                  n_buckets=self.n_buckets)
         if hasattr(self.comm, "attach"):
             self.comm.attach(self.layout)
+        if self.n_buckets > 1:
+            L_, nb = mcfg.n_layer, self.n_buckets
+            lowest = {}
+            for l in range(L_):
+                lowest[self._layer_bucket(l)] = min(l, lowest.get(self._layer_bucket(l), l))
+            # the last bucket ends with the embeddings: it is exchanged after the backward pass, not from a hook
+            self.model.grad_bucket_boundaries = {l: b for b, l in lowest.items() if b < nb - 1}
+            self._side = torch.cuda.Stream(device=self.device)
         kernels = getattr(self.backend, "optim_kernels", None)
         self.opt = MuonAdamW(self.layout, tcfg.schedule_cfg, mcfg.d_model,
                              kernels=kernels() if callable(kernels) else None)
@@ -98,6 +113,16 @@ class Trainer(TrainerBase):
             self._resume()
 
     # ------------------------------------------------------------------
+    def _layer_bucket(self, layer: int) -> int:
+        """Upper layers finish their backward first: bucket 0 = the top third, ..., the last bucket = the bottom."""
+        return (self.mcfg.n_layer - 1 - layer) * self.n_buckets // self.mcfg.n_layer
+
+    def _bucket_of(self, name: str) -> int:
+        parts = name.split(".")
+        if parts[0] == "h" and len(parts) > 1 and parts[1].isdigit():
+            return self._layer_bucket(int(parts[1]))
+        return self.n_buckets - 1            # embeddings, head, per-layer scalar vectors
+
     def _make_comm(self):
         if self.world == 1:
             return LocalComm()
@@ -155,8 +180,20 @@ class Trainer(TrainerBase):
         self._loss_acc.zero_()
         tokens_micro = self.micro_batch * m.seq_len
         grad_scale = 1.0 / (tokens_micro * self.accum * self.world)
+        overlap = self.n_buckets > 1 and t.diagnostic_steps is None
+        progress = self.wsd.progress(self.step)
+        wm = warmup_multiplier(self.step + 1, self.wsd.warmup_steps)
+
+        def run_optimizer(bucket, src):
+            self.opt.step(self.step + 1, progress, wm, grad_source=src, bucket=bucket)
+
+        def bucket_ready(bucket):             # fires inside the last micro-step's backward pass
+            with nvtx_range(f"gradient exchange, bucket {bucket}"):
+                self.comm.exchange_bucket(self.layout, bucket, run_optimizer, self._side)
+
         for micro in range(self.accum):
             ids, tgt = self._stage_batch(micro)
+            self.model.grad_bucket_cb = bucket_ready if (overlap and micro == self.accum - 1) else None
             with nvtx_range(f"forward micro {micro}"):
                 scaled, per_tok = self.model(ids, tgt, grad_scale=grad_scale)
             with nvtx_range(f"backward micro {micro}"):
@@ -172,17 +209,23 @@ class Trainer(TrainerBase):
             self.timer.mark("end")
             self.step += 1
             return self._loss_acc
-        with nvtx_range("gradient exchange"):
-            self.comm.reduce_scatter_grads(self.layout)
-        progress = self.wsd.progress(self.step)
-        wm = warmup_multiplier(self.step + 1, self.wsd.warmup_steps)
-        gs = self.comm.grad_source(self.layout) if hasattr(self.comm, "grad_source") else None
-        with nvtx_range("optimizer"):
-            self.opt.step(self.step + 1, progress, wm, grad_source=gs)
+        if overlap:
+            self.model.grad_bucket_cb = None
+            bucket_ready(self.n_buckets - 1)                 # the bottom layers, embeddings and scalars
             if self.expert_opt is not None:
                 self.expert_opt.step(self.step + 1, progress, wm)
-        with nvtx_range("parameter exchange"):
-            self.comm.all_gather_params(self.layout)
+            torch.cuda.current_stream(self.device).wait_stream(self._side)
+            self.comm.activate_staged()
+        else:
+            with nvtx_range("gradient exchange"):
+                self.comm.reduce_scatter_grads(self.layout)
+            gs = self.comm.grad_source(self.layout) if hasattr(self.comm, "grad_source") else None
+            with nvtx_range("optimizer"):
+                self.opt.step(self.step + 1, progress, wm, grad_source=gs)
+                if self.expert_opt is not None:
+                    self.expert_opt.step(self.step + 1, progress, wm)
+            with nvtx_range("parameter exchange"):
+                self.comm.all_gather_params(self.layout)
         self.timer.mark("opt_end")
         self.timer.mark("end")
         self.step += 1

@@ -26,7 +26,10 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="sm100", choices=["sm100", "baseline", "reference"])
+    ap.add_argument("--impl", default="sm100", choices=["sm100", "baseline", "reference"],
+                    help="sm100: this package's kernels; baseline: the library arm on the same box (cuBLAS GEMMs, cuDNN / "
+                         "flash-attn attention, torch elementwise kernels, NCCL with --comm nccl); reference: the reference "
+                         "engine itself (unavailable here, prints why)")
     ap.add_argument("--model", default="phase2")
     ap.add_argument("--attn", default=None, choices=[None, "own", "library"])
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
@@ -156,7 +159,8 @@ def main() -> int:
                    "parallelism": (f"tp{args.tp}xdp{world // args.tp}" if args.tp > 1 else
                                    (f"pp{args.pp}xdp{world // args.pp}" if args.pp > 1 else
                                     (f"dp{world} ep{args.ep}" if args.ep > 1 else f"dp{world}"))), "comm": comm_name,
-                   "attention": getattr(tr.backend, "attn", "library"),
+                   "attention": (getattr(tr.backend, "attn", None) or
+                                 "library: " + json.dumps(getattr(tr.backend, "attention_used", {}))),
                    "l2": "inputs larger than L2 (per-step working set of tens of GB)",
                    "valid_headline_config": valid},
         "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},

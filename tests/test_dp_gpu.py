@@ -20,7 +20,7 @@ from autoresearch_b200.ops import kernels as K
 world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
 torch.cuda.set_device(local)
 if world > 1:
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=90))
 cfg = model_preset("small")
 t = TrainConfig(device_batch_size=4, total_batch_size=8 * cfg.seq_len, max_steps=20, cooldown_steps=5,
                 synthetic_data=True, synthetic_kind="zipf", impl="sm100", cooldown_trigger_file="",
@@ -50,7 +50,7 @@ def _run(nproc, comm, port):
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
                "--master-addr", "127.0.0.1", "--master-port", str(port), path]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     os.remove(path)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
@@ -67,6 +67,6 @@ def test_dp2_matches_single_gpu():
     assert fused["pending_pulls"] > 0 and lib["pending_pulls"] == 0
     for a, b, c in zip(one["losses"], fused["losses"], lib["losses"]):
         # every decomposition sees the identical global batch: only the bf16 summation order differs
-        assert abs(a - b) < 1e-2, (one, fused)
-        assert abs(a - c) < 1e-2, (one, lib)
+        assert abs(a - b) < 1e-2 * abs(a), (one, fused)
+        assert abs(a - c) < 1e-2 * abs(a), (one, lib)
     assert fused["losses"][-1] < fused["losses"][0]

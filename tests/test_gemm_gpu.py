@@ -185,3 +185,51 @@ def test_gemm_copies_the_next_operand_while_it_computes(shape):
     K.flush_pending_pulls()
     torch.cuda.synchronize()
     assert torch.equal(stale[1], new[1])
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_ragged_batches_skip_rows_beyond_the_valid_count(mode):
+    """Grouped expert GEMM: per-item row counts (device array), several row slabs per weight matrix; tiles beyond the
+    count are left untouched and the K range of the transposed product is cut to the valid rows."""
+    from autoresearch_b200.ops import kernels as K
+    torch.manual_seed(7)
+    E, W, cap, D, M = 2, 3, 640, 256, 512          # E weights, W slabs each, cap rows per slab
+    G = E * W
+    counts = torch.tensor([640, 0, 130, 257, 512, 5], dtype=torch.int32, device="cuda")
+    x = (torch.randn(G, cap, D, device="cuda") * 0.5).to(torch.bfloat16)
+    for g in range(G):                               # rows between the count and the next tile boundary are zero
+        x[g, int(counts[g]):] = 0
+    w = (torch.randn(E, M, D, device="cuda") * 0.1).to(torch.bfloat16)
+    K.gemm_set_mode(mode)
+    try:
+        out = torch.full((G, cap, M), 7.0, dtype=torch.bfloat16, device="cuda")
+        K.gemm(x, w, out=out, epi=K.EPI_RELU2, m_valid=counts, b_div=W)
+        tile = 256 if mode == 2 else 128
+        for g in range(G):
+            c = int(counts[g])
+            ref = torch.relu(x[g, :c].float() @ w[g // W].float().t()) ** 2
+            if c:
+                assert ((out[g, :c].float() - ref).norm() / ref.norm()).item() < 1e-2
+            done = (c + tile - 1) // tile * tile
+            assert (out[g, min(done, cap):] == 7.0).all()           # untouched
+            assert (out[g, c:min(done, cap)] == 0).all()            # computed from zero rows
+        # dW[e] += sum over the slabs of e of dy^T x, K cut to the valid rows; poison what lies beyond the padding
+        dy = (torch.randn(G, cap, M, device="cuda") * 0.1).to(torch.bfloat16)
+        for g in range(G):
+            c = int(counts[g])
+            dy[g, c:] = 0
+            pad = (c + 63) // 64 * 64
+            dy[g, pad:] = float("nan")
+            x[g, pad:] = float("nan")
+        dw = torch.zeros(E, M, D, dtype=torch.float32, device="cuda")
+        K.gemm(dy.view(E, W * cap, M), x.view(E, W * cap, D), trans_a=True, trans_b=False, out=dw, epi=K.EPI_ATOMIC_F32,
+               k_valid=counts.view(E, W).contiguous(), k_seg=cap)
+        torch.cuda.synchronize()
+        K.check_err_flag()
+        for e in range(E):
+            ref = sum(dy[e * W + j, :int(counts[e * W + j])].float().t() @ x[e * W + j, :int(counts[e * W + j])].float()
+                      for j in range(W))
+            assert torch.isfinite(dw[e]).all()
+            assert ((dw[e] - ref).norm() / ref.norm()).item() < 1e-2
+    finally:
+        K.gemm_set_mode(0)

@@ -24,7 +24,7 @@ def test_moe_block_matches_reference(cf):
     mk = lambda *s, sc=1.0: (torch.randn(*s, device="cuda") * sc).to(torch.bfloat16).requires_grad_(True)
     xn, resid = mk(N, D), mk(N, D)
     wr, wfc, wpr = mk(E, D, sc=0.2), mk(E, M, D, sc=0.05), mk(E, D, M, sc=0.05)
-    out, aux = MoEFn.apply(xn, resid, wr, wfc, wpr, k, 0.01, cf, None)
+    out, aux = MoEFn.apply(xn, resid, wr, wfc, wpr, k, 0.01, cf, None, 0)
     g = torch.randn(N, D, device="cuda").to(torch.bfloat16)
     (out.float() * g.float()).sum().add(aux * 3.0).backward()
     K.check_err_flag()
@@ -62,7 +62,7 @@ from autoresearch_b200.ops import kernels as K
 world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
 torch.cuda.set_device(local)
 if world > 1:
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=90))
 cfg = model_preset("small_moe")
 cfg = dataclasses.replace(cfg, moe=dataclasses.replace(cfg.moe, capacity_factor=4.0, aux_coeff=0.0))
 t = TrainConfig(device_batch_size=4, total_batch_size=8 * cfg.seq_len, max_steps=20, cooldown_steps=5,
@@ -112,7 +112,7 @@ def test_expert_parallel_two_gpus_matches_single_gpu():
         cmd = ([sys.executable, path] if n == 1 else
                [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
                 "--master-addr", "127.0.0.1", "--master-port", str(port), path])
-        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
         assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
         return json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
 
@@ -123,7 +123,7 @@ def test_expert_parallel_two_gpus_matches_single_gpu():
     assert one["ep"] == 1 and two["ep"] == 2 and two["experts_local"] == 2
     assert two["ckpt"] == {"experts_in_file": 4, "every_rank_found_its_experts": True, "reload_matches": True}, two["ckpt"]
     for a, b in zip(one["losses"], two["losses"]):
-        assert abs(a - b) < 0.05 * abs(a) + 0.02, (one, two)
+        assert abs(a - b) < 1e-2 * abs(a), (one, two)
 
 
 def test_slot_positions_match_token_order_prefix_sum():

@@ -37,11 +37,11 @@ sys.path.insert(0, os.environ["ARB_ROOT"])
 from autoresearch_b200.config import TrainConfig, model_preset
 from autoresearch_b200.parallel.pipeline import PipelineTrainer
 dist.init_process_group("gloo")
-cfg = model_preset("tiny")
+cfg = model_preset("tiny", n_layer=3)
 t = TrainConfig(device_batch_size=2, total_batch_size=8 * 128, max_steps=10, cooldown_steps=3, synthetic_data=True,
                 synthetic_kind="zipf", impl="oracle", cooldown_trigger_file="")
 t.init_scheme = "normal"
-tr = PipelineTrainer(cfg, t, pp=2, device="cpu", quiet=True)
+tr = PipelineTrainer(cfg, t, pp=dist.get_world_size(), device="cpu", quiet=True)
 ls = [tr.loss_on_all_ranks(tr.train_step()) for _ in range(4)]
 if dist.get_rank() == 0:
     print("RESULT " + json.dumps({"losses": ls, "accum": tr.accum, "bytes": tr.comm_bytes}))
@@ -49,12 +49,17 @@ dist.destroy_process_group()
 """
 
 
-def test_two_stage_pipeline_matches_single_process(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("stages", [2, 3])
+def test_pipeline_matches_single_process(tmp_path, stages):
+    """Two stages (every exchange between the same pair) and three (a middle stage talks to both neighbours)."""
     import torch
     from autoresearch_b200.config import TrainConfig, model_preset
     from autoresearch_b200.models.init import init_weights
     from autoresearch_b200.trainer import Trainer
-    cfg = model_preset("tiny")
+    cfg = model_preset("tiny", n_layer=3)
     t = TrainConfig(device_batch_size=2, total_batch_size=8 * 128, max_steps=10, cooldown_steps=3, synthetic_data=True,
                     synthetic_kind="zipf", impl="oracle", cooldown_trigger_file="")
     one = Trainer(cfg, t, device="cpu", quiet=True)
@@ -65,8 +70,8 @@ def test_two_stage_pipeline_matches_single_process(tmp_path):
     script = tmp_path / "w.py"
     script.write_text(WORKER)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29656", str(script)],
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={stages}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29654 + stages), str(script)],
                        env=dict(os.environ, ARB_ROOT=root), capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])

@@ -38,7 +38,7 @@ elif mode == "inproc":
         torch.cuda.synchronize(d); K.check_err_flag(torch.device("cuda", d))
     extra["bytes"] = tr.comm_bytes
 else:
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=90))
     from autoresearch_b200.parallel.pipeline import PipelineTrainer
     tr = PipelineTrainer(cfg, t, pp=2, device=f"cuda:{local}", quiet=True)
     losses = [tr.global_loss(tr.train_step()) for _ in range(6)]
@@ -62,7 +62,7 @@ def _run(mode, nproc, port):
     cmd = ([sys.executable, path] if nproc == 1 else
            [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
             "--master-addr", "127.0.0.1", "--master-port", str(port), path])
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     os.remove(path)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
@@ -75,7 +75,7 @@ def test_two_stage_pipelines_follow_the_single_gpu_run():
     inproc = _run("inproc", 1, 0)
     assert procs["bytes"] > 0 and inproc["bytes"] > 0 and procs["accum"] == 4
     for a, b, c in zip(one["losses"], procs["losses"], inproc["losses"]):
-        assert abs(a - b) < 1e-2 and abs(a - c) < 1e-2, (one, procs, inproc)
+        assert abs(a - b) < 1e-2 * abs(a) and abs(a - c) < 1e-2 * abs(a), (one, procs, inproc)
     assert one["losses"][-1] < one["losses"][0]
 
 
@@ -85,4 +85,4 @@ def test_pipeline_with_fused_data_parallel_exchange():
     pd = _run("procs", 4, 29672)
     assert pd["comm"] == "fused" and pd["accum"] == 2
     for a, b in zip(one["losses"], pd["losses"]):
-        assert abs(a - b) < 1e-2, (one, pd)
+        assert abs(a - b) < 1e-2 * abs(a), (one, pd)

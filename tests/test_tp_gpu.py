@@ -23,7 +23,7 @@ t = TrainConfig(device_batch_size=4, total_batch_size=4 * cfg.seq_len, max_steps
                 synthetic_data=True, synthetic_kind="zipf", impl="sm100", cooldown_trigger_file="",
                 parallel=ParallelConfig(tp=world, comm=os.environ["ARB_COMM"]))
 if world > 1:
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=90))
     from autoresearch_b200.parallel.tp import TPTrainer
     tr = TPTrainer(cfg, t, tp=world, device=f"cuda:{local}", quiet=True)
     losses = [tr.global_loss(tr.train_step()) for _ in range(6)]
@@ -54,7 +54,7 @@ def test_tp2_fused_and_library_follow_single_gpu():
         cmd = ([sys.executable, path] if n == 1 else
                [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
                 "--master-addr", "127.0.0.1", "--master-port", str(port), path])
-        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
         assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
         return json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
 
@@ -64,4 +64,4 @@ def test_tp2_fused_and_library_follow_single_gpu():
     os.remove(path)
     assert fused["mode"] == "fused" and lib["mode"] == "library"
     for a, b, c in zip(one["losses"], fused["losses"], lib["losses"]):
-        assert abs(a - b) < 1e-2 and abs(b - c) < 1e-2, (one, fused, lib)
+        assert abs(a - b) < 1e-2 * abs(a) and abs(b - c) < 1e-2 * abs(b), (one, fused, lib)
