@@ -25,11 +25,12 @@ from ..ops import build as B
 def fwd2(a):
     """Cycles per key tile (both query tiles) of the MMA-issuing thread and of one warp of each softmax group."""
     T, H = a.T, a.H
+    which = a.kernel          # "fwd2" or "fwd3": same roles, same entry-point signature
     W = a.window if a.window is not None else T
     with tempfile.TemporaryDirectory(prefix="arb_prof_") as td:
         so = Path(td) / "attn_prof.so"
         flags = [f for f in B.NVCC_FLAGS if f not in ("-Xptxas", "-v")]
-        subprocess.run([B.nvcc_path()] + flags + ["-DARB_ATTN_PROF", "-shared", str(B.CSRC / "attn_fwd2_sm100.cu"), "-o", str(so),
+        subprocess.run([B.nvcc_path()] + flags + ["-DARB_ATTN_PROF", "-shared", str(B.CSRC / f"attn_{which}_sm100.cu"), "-o", str(so),
                         "-lcuda"], check=True)
         lib = C.CDLL(str(so))
         Dl = H * 128
@@ -40,7 +41,7 @@ def fwd2(a):
         err = torch.zeros(1, dtype=torch.int32, device="cuda")
         prof = torch.zeros(64, dtype=torch.int64, device="cuda")
         vp, ll, ci = C.c_void_p, C.c_longlong, C.c_int
-        f = lib.arb_attn_prof_fwd2
+        f = getattr(lib, f"arb_attn_prof_{which}")
         f.restype = ci
         f.argtypes = [vp] * 5 + [ci, ci, ci, ll, ll, ci, C.c_float, vp, vp]
         b = qkv.data_ptr()
@@ -71,10 +72,11 @@ def main():
     ap.add_argument("--T", type=int, default=32768)
     ap.add_argument("--H", type=int, default=8)
     ap.add_argument("--window", type=int, default=None)
-    ap.add_argument("--kernel", choices=("bwd", "fwd2"), default="bwd",
-                    help="bwd: the wide backward kernels; fwd2: the forward with two query tiles per CTA")
+    ap.add_argument("--kernel", choices=("bwd", "fwd2", "fwd3"), default="bwd",
+                    help="bwd: the wide backward kernels; fwd2: the forward with two query tiles per CTA; fwd3: the same "
+                         "with the register file split between the roles and packed softmax arithmetic")
     a = ap.parse_args()
-    if a.kernel == "fwd2":
+    if a.kernel in ("fwd2", "fwd3"):
         return fwd2(a)
     T, H, Bsz = a.T, a.H, 1
     W = a.window if a.window is not None else T

@@ -89,15 +89,19 @@ class MoEFn(torch.autograd.Function):
         f = counts.float() / float(N * top_k)
         aux = aux_coeff * E * (f * probs.mean(0)).sum()
         T_ = MoEFn.TILE
-        if ep is None:
-            W = 1
+        lib_ep = ep is not None and ep.mode == "library"
+        if ep is None or lib_ep:
+            W = 1 if ep is None else ep.world
             xg = torch.empty(E, cap, D, dtype=torch.bfloat16, device=dev)
             y = torch.empty(E, cap, D, dtype=torch.bfloat16, device=dev)
             mv = torch.empty(E, dtype=torch.int32, device=dev)
-            x_tab, y_tab = _ptr_table(xg), _ptr_table(y)
+            x_tab = _ptr_table(xg)
             cnt_tab = (C.c_void_p * E)(*[mv.data_ptr() + 4 * e for e in range(E)])
             K._check(L.arb_moe_dispatch(xn.data_ptr(), x_tab, idx.data_ptr(), row.data_ptr(), N, top_k, D, E, s), "moe_dispatch")
             _finish(L, s, x_tab, cnt_tab, counts, keep, cap, D, E, T_)
+            if lib_ep:                                        # library all-to-all of the padded slabs and their counts
+                xg, mv = ep.to_owners(xg), ep.to_owners(mv)
+                y = torch.empty_like(xg)
         else:
             W = ep.world
             x_tab, y_tab = ep.table("x", layer), ep.table("y", layer)
@@ -108,7 +112,13 @@ class MoEFn(torch.autograd.Function):
         act = torch.empty(xg.shape[0], cap, M, dtype=torch.bfloat16, device=dev)
         K.gemm(xg, w_fc, out=act, epi=K.EPI_RELU2, m_valid=mv, b_div=W)
         K.gemm(act, w_proj, out=y, m_valid=mv, b_div=W)
-        if ep is not None:
+        if lib_ep:
+            y_src = ep.to_sources(y)                          # expert outputs of this rank's tokens, by expert
+            y_tab = _ptr_table(y_src)
+            y = y_src                                         # what the backward reads for the gate gradient
+        elif ep is None:
+            y_tab = _ptr_table(y)
+        else:
             ep.barrier()                                      # every expert's outputs are complete
         out = _gather_rows(y_tab, idx, row, N, top_k, D, E, resid, gates)
         ctx.save_for_backward(xn, router_w, w_fc, w_proj, probs, idx, gates, row, xg, act, y, f, counts, mv)
@@ -127,8 +137,9 @@ class MoEFn(torch.autograd.Function):
         T_ = MoEFn.TILE
         d_out = d_out.contiguous()
         d_gates = torch.empty(N, top_k, dtype=torch.float32, device=dev)
-        if ep is None:
-            W = 1
+        lib_ep = ep is not None and ep.mode == "library"
+        if ep is None or lib_ep:
+            W = 1 if ep is None else ep.world
             dy = torch.empty_like(y)
             d_xg = torch.empty_like(xg)
             y_tab, dy_tab, dx_tab = _ptr_table(y), _ptr_table(dy), _ptr_table(d_xg)
@@ -140,7 +151,9 @@ class MoEFn(torch.autograd.Function):
         K._check(L.arb_moe_combine_bwd(d_out.data_ptr(), y_tab, 0, dy_tab, idx.data_ptr(), row.data_ptr(), gates.data_ptr(),
                                        d_gates.data_ptr(), N, top_k, D, E, s), "moe_combine_bwd")
         _finish(L, s, dy_tab, None, counts, keep, cap, D, E, T_)
-        if ep is not None:
+        if lib_ep:
+            dy = ep.to_owners(dy)
+        elif ep is not None:
             ep.barrier()                                      # every source has pushed gate * d_out
         d_act = torch.empty_like(act)
         K.gemm(dy, w_proj, trans_b=False, out=d_act, epi=K.EPI_RELU2_BWD, aux=act, m_valid=mv, b_div=W)
@@ -156,7 +169,9 @@ class MoEFn(torch.autograd.Function):
         g_proj = acc_grad(w_proj, dy, act)
         g_fc = acc_grad(w_fc, d_act, xg)
         K.gemm(d_act, w_fc, trans_b=False, out=d_xg, m_valid=mv, b_div=W)
-        if ep is not None:
+        if lib_ep:
+            dx_tab = _ptr_table(ep.to_sources(d_xg))
+        elif ep is not None:
             ep.barrier()                                      # the input gradients of my tokens are complete
         d_xn = _gather_rows(dx_tab, idx, row, N, top_k, D, E)
         aux_dp = None

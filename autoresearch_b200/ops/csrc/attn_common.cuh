@@ -144,4 +144,9 @@ int attn_wide_bwd_launch(const void* q, const void* k, const void* v, const void
 int attn_fwd2_launch(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv, AttnArgs a,
                      cudaStream_t stream);
 
+
+// attn_fwd3_sm100.cu
+int attn_fwd3_launch(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv, AttnArgs a,
+                     cudaStream_t stream);
+
 }  // namespace arb

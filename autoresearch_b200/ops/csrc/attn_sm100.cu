@@ -815,11 +815,12 @@ __global__ void __launch_bounds__(256) attn_delta_k(const __nv_bfloat16* __restr
 
 using namespace arb;
 
-// 3: as 2 with the two-query-tile forward for every shape; 2 (default): wide backward, two-query-tile forward on
-// large grids only; 1: 64-wide sub-tiles with TMEM operands; 0: with shared-memory operands
+// 4: as 2 with the register-split forward (attn_fwd3_sm100.cu) for every shape; 3: as 2 with the two-query-tile forward
+// for every shape; 2 (default): wide backward, forward chosen by shape (see arb_attn_fwd); 1: 64-wide sub-tiles with TMEM
+// operands; 0: with shared-memory operands
 static int g_attn_mode = 2;
 static int g_attn_ts = 1;
-extern "C" void arb_attn_set_mode(int mode) { g_attn_mode = mode < 0 ? 0 : (mode > 3 ? 3 : mode); g_attn_ts = g_attn_mode ? 1 : 0; }
+extern "C" void arb_attn_set_mode(int mode) { g_attn_mode = mode < 0 ? 0 : (mode > 4 ? 4 : mode); g_attn_ts = g_attn_mode ? 1 : 0; }
 
 template <bool TS>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a, dim3 grid,
@@ -863,13 +864,15 @@ extern "C" int arb_attn_fwd(const void* q, const void* k, const void* v, void* o
   AttnArgs a{};
   a.B = B; a.T = T; a.H = H; a.window = window > T ? T : window; a.scale = scale;
   a.o = o; a.ldo = ldo; a.lse = lse; a.err = err_flag;
-  // Two query tiles per CTA: 3-5 % faster than one tile on grids of several waves (B=4, H=8, T=32768: full causal
-  // 9.79 -> 9.42 ms, window 4096 2.61 -> 2.50 ms, window 1024 0.96 -> 0.92 ms, window 256 0.51 -> 0.47 ms), slower on small
-  // grids, where halving the CTA count costs more than the shared K / V loads save, and no gain on short sequences
-  // (B=64, H=4, T=2048: full equal, window 1024 0.369 -> 0.392 ms; B=8, H=16, T=8192: full 2.49 -> 2.39 ms).
+  // Two query tiles per CTA pay on grids of several waves (B=4, H=8, T=32768, ms one tile / two tiles: full causal
+  // 9.79 / 9.42, window 4096 2.61 / 2.50, window 256 0.51 / 0.47) and lose on small grids, where halving the CTA count
+  // costs more than the shared K / V loads save, and on short sequences.  Of the two-tile kernels the register-split
+  // one (attn_fwd3) is the default: 4-5 % faster than attn_fwd2 on the same shapes (full causal 8.95 -> 8.54 ms,
+  // window 4096 2.13 -> 2.04, window 256 0.471 -> 0.458; B=8, H=16, T=8192 full 2.38 -> 2.27).
   const long long pair_ctas = (long long)((T + 255) / 256) * H * B;
-  if (g_attn_mode == 3 || (g_attn_mode == 2 && pair_ctas >= 2048 && T >= 4096))
-    return attn_fwd2_launch(q, k, v, ldq, ldk, ldv, a, stream);
+  if (g_attn_mode == 4 || (g_attn_mode == 2 && pair_ctas >= 2048 && T >= 4096))
+    return attn_fwd3_launch(q, k, v, ldq, ldk, ldv, a, stream);
+  if (g_attn_mode == 3) return attn_fwd2_launch(q, k, v, ldq, ldk, ldv, a, stream);
   dim3 grid((T + 127) / 128, H, B);
   return g_attn_ts ? launch_fwd<true>(tq, tk, tv, a, grid, stream) : launch_fwd<false>(tq, tk, tv, a, grid, stream);
 }

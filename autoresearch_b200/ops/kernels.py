@@ -263,7 +263,8 @@ def flush_pending_pulls() -> None:
 
 
 def attn_set_mode(mode: int) -> None:
-    """3 = as 2, with the forward on two query tiles per CTA in ping-pong; 2 = backward on 128 x 128 tiles with
+    """4 = as 2, with the register-split two-query-tile forward (attn_fwd3) for every shape;
+    3 = as 2, with the forward on two query tiles per CTA in ping-pong; 2 = backward on 128 x 128 tiles with
     the two-phase softmax; 1 = 64-wide sub-tiles with P / dS operands in TMEM; 0 = 64-wide sub-tiles with P / dS
     in shared memory (forward too)."""
     f = lib().arb_attn_set_mode

@@ -30,6 +30,7 @@ from .symm import SymmBuffer
 
 class EPContext:
     TILE = 256            # rows per GEMM tile: the dispatch zero-pads every slab to this boundary
+    mode = "fused"
 
     def __init__(self, group, device, n_experts: int, d_model: int, max_tokens: int, top_k: int,
                  capacity_factor: float):
@@ -101,3 +102,45 @@ class EPContext:
 
     def symmetric_bytes(self) -> int:
         return sum(b.tensor.numel() * b.tensor.element_size() for b in self._bufs.values())
+
+
+class LibraryEPContext:
+    """The comparison arm: the same capacity rule and slab layout, but the token exchange is the library's
+    all-to-all (``ncclSend/Recv`` grouped by ``all_to_all_single``) on padded fixed-size slabs, between local
+    dispatch / combine kernels.  Used to measure what the peer-memory path buys."""
+
+    mode = "library"
+
+    def __init__(self, group, device, n_experts: int, d_model: int, max_tokens: int, top_k: int, capacity_factor: float):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if n_experts % self.world:
+            raise ValueError(f"{n_experts} experts do not divide over {self.world} ranks")
+        if capacity_factor <= 0:
+            raise ValueError("expert parallelism needs a capacity factor (fixed-size exchange buffers)")
+        self.E, self.E_local, self.D, self.K = n_experts, n_experts // self.world, d_model, top_k
+        self.keep = (int(math.ceil(capacity_factor * max_tokens * top_k / n_experts)) + 7) // 8 * 8
+        self.cap_src = (self.keep + 63) // 64 * 64
+        self.G = self.E_local * self.world
+        self.device = torch.device(device)
+        self.bytes = 0
+
+    def to_owners(self, t: torch.Tensor) -> torch.Tensor:
+        """[E, ...] by expert (owner-major) on every source -> [E_local * world, ...] by (local expert, source) on the
+        owner: the all-to-all plus, with several experts per rank, the re-ordering of the received blocks."""
+        out = torch.empty_like(t)
+        dist.all_to_all_single(out, t.contiguous(), group=self.group)
+        self.bytes += t.numel() * t.element_size() * (self.world - 1) // self.world
+        if self.E_local > 1:
+            out = out.view(self.world, self.E_local, *t.shape[1:]).transpose(0, 1).contiguous().view_as(t)
+        return out
+
+    def to_sources(self, t: torch.Tensor) -> torch.Tensor:
+        """The inverse of to_owners."""
+        if self.E_local > 1:
+            t = t.view(self.E_local, self.world, *t.shape[1:]).transpose(0, 1).contiguous().view_as(t)
+        out = torch.empty_like(t)
+        dist.all_to_all_single(out, t.contiguous(), group=self.group)
+        self.bytes += t.numel() * t.element_size() * (self.world - 1) // self.world
+        return out

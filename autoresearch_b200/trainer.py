@@ -99,10 +99,11 @@ class Trainer(TrainerBase):
             self.expert_layout = ParamLayout(expert_groups, 1, 0)
             self.expert_opt = MuonAdamW(self.expert_layout, tcfg.schedule_cfg, mcfg.d_model,
                                         kernels=kernels() if callable(kernels) else None)
-            from .parallel.ep import EPContext
-            self.backend.ep = EPContext(self.group if self.group is not None else dist.group.WORLD, self.device,
-                                        mcfg.moe.n_experts, mcfg.d_model, self.micro_batch * mcfg.seq_len,
-                                        mcfg.moe.top_k, mcfg.moe.capacity_factor)
+            from .parallel.ep import EPContext, LibraryEPContext
+            ctx_cls = EPContext if tcfg.parallel.comm == "fused" else LibraryEPContext
+            self.backend.ep = ctx_cls(self.group if self.group is not None else dist.group.WORLD, self.device,
+                                      mcfg.moe.n_experts, mcfg.d_model, self.micro_batch * mcfg.seq_len,
+                                      mcfg.moe.top_k, mcfg.moe.capacity_factor)
         self.wsd = WSDState(tcfg.max_steps, tcfg.cooldown_steps, tcfg.schedule_cfg.warmdown_ratio,
                             warmup_steps=int(round(tcfg.schedule_cfg.warmup_ratio * (tcfg.max_steps or 0))))
         self._init_common()

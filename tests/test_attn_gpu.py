@@ -65,6 +65,15 @@ def test_attention_two_query_tiles_forward(B, T, H, window):
     _run(B, T, H, window, mode=3)
 
 
+@pytest.mark.parametrize("B,T,H,window", [(1, 128, 1, 128), (2, 256, 2, 256), (1, 384, 1, 384), (1, 512, 2, 256), (1, 1024, 1, 256),
+                                         (1, 640, 1, 64), (2, 320, 1, 100), (1, 1536, 2, 1536), (1, 2000, 1, 700),
+                                         (1, 4096, 1, 4096)])
+def test_attention_register_split_forward(B, T, H, window):
+    """Forward with the register file split between the roles (score rows held in registers, packed fp32 arithmetic,
+    one exponential in four as a polynomial): same cases as the two-query-tile kernel it is derived from."""
+    _run(B, T, H, window, mode=4)
+
+
 def test_attention_long_sequence():
     """Enough tiles for every ring slot and barrier phase to wrap several times."""
     _run(1, 4096, 1, 4096)

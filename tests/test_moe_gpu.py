@@ -67,7 +67,7 @@ cfg = model_preset("small_moe")
 cfg = dataclasses.replace(cfg, moe=dataclasses.replace(cfg.moe, capacity_factor=4.0, aux_coeff=0.0))
 t = TrainConfig(device_batch_size=4, total_batch_size=8 * cfg.seq_len, max_steps=20, cooldown_steps=5,
                 synthetic_data=True, synthetic_kind="zipf", impl="sm100", cooldown_trigger_file="",
-                parallel=ParallelConfig(dp=world, ep=world, comm="fused"))
+                parallel=ParallelConfig(dp=world, ep=world, comm=os.environ.get("ARB_COMM", "fused")))
 tr = Trainer(cfg, t, device=f"cuda:{local}", quiet=True)
 losses = [tr.mean_loss_across_ranks(tr.train_step()) for _ in range(6)]
 torch.cuda.synchronize(); K.check_err_flag()
@@ -92,7 +92,8 @@ if world > 1:
     ok2 = torch.tensor([int(same)], device="cuda"); dist.all_reduce(ok2, op=dist.ReduceOp.MIN)
     ck["reload_matches"] = bool(ok2.item())
 if int(os.environ.get("RANK", "0")) == 0:
-    print("RESULT " + json.dumps({"losses": losses, "ep": tr.ep, "experts_local": tr.model.blocks[0].expert_fc.shape[0], "ckpt": ck}))
+    print("RESULT " + json.dumps({"losses": losses, "ep": tr.ep, "experts_local": tr.model.blocks[0].expert_fc.shape[0], "ckpt": ck,
+                                  "exchange": getattr(tr.backend.ep, "mode", None) if world > 1 else None}))
 if world > 1:
     dist.destroy_process_group()
 """
@@ -108,15 +109,18 @@ def test_expert_parallel_two_gpus_matches_single_gpu():
     ckdir = tempfile.mkdtemp(prefix="arb_ep_ckpt_")
     env = dict(os.environ, ARB_ROOT=root, NCCL_NVLS_ENABLE="0", ARB_DISABLE_MULTIMEM="1", ARB_CKPT=ckdir)
 
-    def run(n, port):
+    def run(n, port, comm="fused"):
         cmd = ([sys.executable, path] if n == 1 else
                [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
                 "--master-addr", "127.0.0.1", "--master-port", str(port), path])
-        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+        r = subprocess.run(cmd, env=dict(env, ARB_COMM=comm), capture_output=True, text=True, timeout=240)
         assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
         return json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
 
-    one, two = run(1, 0), run(2, 29631)
+    one, two, lib = run(1, 0), run(2, 29631), run(2, 29632, "nccl")
+    assert two["exchange"] == "fused" and lib["exchange"] == "library"      # the library all-to-all arm
+    for a, b in zip(one["losses"], lib["losses"]):
+        assert abs(a - b) < 1e-2 * abs(a), (one, lib)
     os.remove(path)
     import shutil
     shutil.rmtree(ckdir, ignore_errors=True)
