@@ -107,11 +107,11 @@ int arb_rmsnorm_bwd(const void* x, const void* g, const void* add_to, void* gx, 
                     cudaStream_t s);
 int arb_resid_scale_norm_fwd(const void* x, const void* x0, const void* lam_r, const void* lam_0, int idx,
                              void* x_out, void* xn_out, long long rows, int D, float eps, cudaStream_t s);
-// t = g_xs + rmsnorm_bwd(x', g_xn);  d_x = lam_r*t;  d_x0 = lam_0*t;  dlam_r[idx] += sum(x*t);
-// dlam_0[idx] += sum(x0*t)   (fp32 atomics, one per CTA)
+// t = g_xs + rmsnorm_bwd(x', g_xn);  d_x = lam_r*t;  d_x0 = lam_0*t (+ d_x0_acc when given; it may be d_x0 itself);
+// dlam_r[idx] += sum(x*t);  dlam_0[idx] += sum(x0*t)   (fp32 atomics, one per CTA)
 int arb_resid_scale_norm_bwd(const void* x, const void* x0, const void* lam_r, const void* lam_0, int idx,
-                             const void* g_xs, const void* g_xn, void* d_x, void* d_x0, float* dlam_r,
-                             float* dlam_0, long long rows, int D, float eps, cudaStream_t s);
+                             const void* g_xs, const void* g_xn, void* d_x, void* d_x0, const void* d_x0_acc,
+                             float* dlam_r, float* dlam_0, long long rows, int D, float eps, cudaStream_t s);
 int arb_add_norm_fwd(const void* x, const void* proj, void* x_out, void* xn_out, long long rows, int D, float eps,
                      cudaStream_t s);
 int arb_residual_add(const void* a, const void* b, void* out, long long n, cudaStream_t s);

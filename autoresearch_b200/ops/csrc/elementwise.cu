@@ -155,9 +155,11 @@ template <int NV>
 __global__ void __launch_bounds__(256) resid_norm_bwd_k(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x0,
                                                         const __nv_bfloat16* __restrict__ lam_r, const __nv_bfloat16* __restrict__ lam_0,
                                                         int idx, const __nv_bfloat16* __restrict__ g_xs, const __nv_bfloat16* __restrict__ g_xn,
-                                                        __nv_bfloat16* __restrict__ d_x, __nv_bfloat16* __restrict__ d_x0,
+                                                        __nv_bfloat16* __restrict__ d_x, __nv_bfloat16* d_x0,
+                                                        const __nv_bfloat16* d_x0_acc,
                                                         float* __restrict__ dlam_r, float* __restrict__ dlam_0,
                                                         long long rows, int D, float eps) {
+  // d_x0_acc (may equal d_x0): the x0 gradient of the layers above, added here instead of by a separate pass
   __shared__ float red[2][ROWS_PER_CTA];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long row = (long long)blockIdx.x * ROWS_PER_CTA + warp;
@@ -195,15 +197,16 @@ __global__ void __launch_bounds__(256) resid_norm_bwd_k(const __nv_bfloat16* __r
     for (int i = 0; i < NV; ++i) {
       const int c = lane + 32 * i;
       if (c < nch) {
-        float gs[8], o1[8], o2[8], xv[8], bv[8], gv[8];
+        float gs[8], o1[8], o2[8], xv[8], bv[8], gv[8], av[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         ld8(g_xs + row * D + c * 8, gs);
+        if (d_x0_acc) ld8(d_x0_acc + row * D + c * 8, av);
         unpack8(xq[i], xv); unpack8(bq[i], bv); unpack8(gq[i], gv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float xs = bf16_round(lr * xv[j] + l0 * bv[j]);
           const float t = gs[j] + r * (gv[j] - xs * coef);
           o1[j] = lr * t;
-          o2[j] = l0 * t;
+          o2[j] = l0 * t + av[j];
           sr += xv[j] * t;
           s0 += bv[j] * t;
         }
@@ -596,11 +599,13 @@ int arb_add_norm_fwd(const void* x, const void* proj, void* x_out, void* xn_out,
   return int(cudaGetLastError());
 }
 int arb_resid_scale_norm_bwd(const void* x, const void* x0, const void* lam_r, const void* lam_0, int idx, const void* g_xs,
-                             const void* g_xn, void* d_x, void* d_x0, float* dlam_r, float* dlam_0, long long rows, int D,
-                             float eps, cudaStream_t s) {
-  if (check_row_args(rows, D) || misaligned(x) || misaligned(x0) || misaligned(g_xs) || misaligned(g_xn) || misaligned(d_x) || misaligned(d_x0)) return -3;
+                             const void* g_xn, void* d_x, void* d_x0, const void* d_x0_acc, float* dlam_r, float* dlam_0,
+                             long long rows, int D, float eps, cudaStream_t s) {
+  if (check_row_args(rows, D) || misaligned(x) || misaligned(x0) || misaligned(g_xs) || misaligned(g_xn) || misaligned(d_x) ||
+      misaligned(d_x0) || (d_x0_acc && misaligned(d_x0_acc)))
+    return -3;
   ROW_DISPATCH(resid_norm_bwd_k, (const bf16*)x, (const bf16*)x0, (const bf16*)lam_r, (const bf16*)lam_0, idx, (const bf16*)g_xs,
-               (const bf16*)g_xn, (bf16*)d_x, (bf16*)d_x0, dlam_r, dlam_0, rows, D, eps);
+               (const bf16*)g_xn, (bf16*)d_x, (bf16*)d_x0, (const bf16*)d_x0_acc, dlam_r, dlam_0, rows, D, eps);
   return int(cudaGetLastError());
 }
 int arb_residual_add(const void* a, const void* b, void* out, long long n, cudaStream_t s) {

@@ -57,7 +57,7 @@ def lib() -> C.CDLL:
         "arb_rmsnorm_fwd": [vp, vp, i64, i32, f32, vp],
         "arb_rmsnorm_bwd": [vp, vp, vp, vp, i64, i32, f32, vp],
         "arb_resid_scale_norm_fwd": [vp, vp, vp, vp, i32, vp, vp, i64, i32, f32, vp],
-        "arb_resid_scale_norm_bwd": [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
+        "arb_resid_scale_norm_bwd": [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp],
         "arb_add_norm_fwd": [vp, vp, vp, vp, i64, i32, f32, vp],
         "arb_residual_add": [vp, vp, vp, i64, vp],
         "arb_relu_sq_fwd": [vp, vp, i64, vp],
@@ -294,10 +294,14 @@ def resid_scale_norm_fwd(x, x0, lam_r, lam_0, idx, eps):
     return xo, xn
 
 
-def resid_scale_norm_bwd(x, x0, lam_r, lam_0, idx, g_xs, g_xn, dlam_r, dlam_0, eps):
-    dx, dx0 = torch.empty_like(x), torch.empty_like(x)
+def resid_scale_norm_bwd(x, x0, lam_r, lam_0, idx, g_xs, g_xn, dlam_r, dlam_0, eps, dx0_acc=None):
+    """dx0_acc: the x0 gradient summed over the layers above; this layer's share is added to it in place and the
+    same tensor is returned, which saves one pass over [N, D] per layer."""
+    dx = torch.empty_like(x)
+    dx0 = dx0_acc if dx0_acc is not None else torch.empty_like(x)
     _check(lib().arb_resid_scale_norm_bwd(x.data_ptr(), x0.data_ptr(), lam_r.data_ptr(), lam_0.data_ptr(), idx,
                                           g_xs.data_ptr(), g_xn.data_ptr(), dx.data_ptr(), dx0.data_ptr(),
+                                          dx0_acc.data_ptr() if dx0_acc is not None else None,
                                           dlam_r.data_ptr(), dlam_0.data_ptr(), x.shape[0], x.shape[1], eps, _stream()),
            "resid_scale_norm_bwd")
     return dx, dx0

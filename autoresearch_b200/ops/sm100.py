@@ -222,11 +222,20 @@ class LinearRelu2Fn(torch.autograd.Function):
         return dx, dw
 
 
+class _X0GradChain:
+    """The x0 gradient of one forward pass: every layer of a stage adds its share to one buffer inside its
+    backward kernel, and only the stage's first layer (the last to run backward) hands the sum to autograd."""
+    __slots__ = ("buf",)
+
+    def __init__(self):
+        self.buf = None
+
+
 class ResidScaleNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, x0, lam_r, lam_0, idx, eps):
+    def forward(ctx, x, x0, lam_r, lam_0, idx, eps, chain=None):
         ctx.save_for_backward(x, x0, lam_r, lam_0)
-        ctx.idx, ctx.eps = idx, eps
+        ctx.idx, ctx.eps, ctx.chain = idx, eps, chain
         xs, xn = K.resid_scale_norm_fwd(x, x0, lam_r, lam_0, idx, eps)
         return xs, xn
 
@@ -240,10 +249,17 @@ class ResidScaleNormFn(torch.autograd.Function):
         mr, m0 = _main_grad(lam_r), _main_grad(lam_0)
         dr = mr if mr is not None else torch.zeros(lam_r.shape, dtype=torch.float32, device=x.device)
         d0 = m0 if m0 is not None else torch.zeros(lam_0.shape, dtype=torch.float32, device=x.device)
+        chain = ctx.chain
         dx, dx0 = K.resid_scale_norm_bwd(x, x0, lam_r, lam_0, ctx.idx, g_xs.contiguous(), g_xn.contiguous(),
-                                         dr, d0, ctx.eps)
+                                         dr, d0, ctx.eps, dx0_acc=chain.buf if chain is not None else None)
+        if chain is not None:
+            chain.buf = dx0
+            if ctx.idx != 0:
+                dx0 = None          # still being summed; layer 0 of the stage returns it
+            else:
+                chain.buf = None
         return (dx, dx0, None if mr is not None else dr.to(lam_r.dtype),
-                None if m0 is not None else d0.to(lam_0.dtype), None, None)
+                None if m0 is not None else d0.to(lam_0.dtype), None, None, None)
 
 
 class EmbeddingFn(torch.autograd.Function):
@@ -565,6 +581,7 @@ class Sm100Backend(OracleBackend):
         K.lib()  # fail loudly when the native library is missing
         self.attn = attn
         self.big_ce_chunk = 16384
+        self._x0_chain = None
 
     def optim_kernels(self):
         if getattr(self, "_optim_kernels", None) is None:
@@ -578,7 +595,10 @@ class Sm100Backend(OracleBackend):
         return RMSNormFn.apply(x.contiguous(), self.eps)
 
     def resid_scale_norm(self, x, x0, lam_r, lam_0, i):
-        return ResidScaleNormFn.apply(x.contiguous(), x0.contiguous(), lam_r, lam_0, i, self.eps)
+        # layers are visited in order within one forward pass: index 0 opens a new x0-gradient chain
+        if i == 0 or self._x0_chain is None:
+            self._x0_chain = _X0GradChain()
+        return ResidScaleNormFn.apply(x.contiguous(), x0.contiguous(), lam_r, lam_0, i, self.eps, self._x0_chain)
 
     def linear_col(self, x, w):
         return LinearFn.apply(x, w)

@@ -40,6 +40,8 @@ def main() -> int:
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (world = tp x dp); dense models")
     ap.add_argument("--ep", type=int, default=1, help="expert-parallel group size (MoE models; 1 or the world size)")
     ap.add_argument("--pp", type=int, default=1, help="pipeline stages (world = pp x dp); one process per stage, 1F1B")
+    ap.add_argument("--dp-buckets", type=int, default=3,
+                    help="gradient buckets of the fused data-parallel exchange (1 = exchange after the backward pass)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: marks the result invalid")
     args = ap.parse_args()
 
@@ -92,7 +94,8 @@ def main() -> int:
     tcfg = TrainConfig(device_batch_size=args.micro_batch, total_batch_size=args.total_batch,
                        max_steps=1000, cooldown_steps=300, synthetic_data=True, synthetic_kind="zipf",
                        impl=args.impl, schedule_cfg=sched, cooldown_trigger_file="", peak_flops=peak,
-                       parallel=ParallelConfig(dp=world // model_par, tp=args.tp, ep=args.ep, pp=args.pp, comm=args.comm))
+                       parallel=ParallelConfig(dp=world // model_par, tp=args.tp, ep=args.ep, pp=args.pp, comm=args.comm,
+                                               dp_buckets=args.dp_buckets))
     if args.tp > 1:
         from autoresearch_b200.parallel.tp import TPTrainer
         tr = TPTrainer(mcfg, tcfg, tp=args.tp, device=f"cuda:{local}", quiet=True)
@@ -161,6 +164,7 @@ def main() -> int:
                                     (f"dp{world} ep{args.ep}" if args.ep > 1 else f"dp{world}"))), "comm": comm_name,
                    "attention": (getattr(tr.backend, "attn", None) or
                                  "library: " + json.dumps(getattr(tr.backend, "attention_used", {}))),
+                   "dp_buckets": getattr(tr, "n_buckets", 1),
                    "l2": "inputs larger than L2 (per-step working set of tens of GB)",
                    "valid_headline_config": valid},
         "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},

@@ -52,6 +52,13 @@ def test_resid_scale_norm_fwd_bwd():
     dx, dx0 = K.resid_scale_norm_bwd(x, x0, lr, l0, idx, g1, g2, dr, d0, EPS)
     _close(dx, xf.grad, what="dx"); _close(dx0, x0f.grad, what="dx0")
     _close(dr, lrf.grad, 3e-2, "dlam_r"); _close(d0, l0f.grad, 3e-2, "dlam_0")
+    # accumulate form: the x0 gradient of the layers above is added in place
+    acc = _bf(rows, D)
+    want = acc.float() + x0f.grad
+    dr2 = torch.zeros(L, device="cuda"); d02 = torch.zeros(L, device="cuda")
+    dx2, out = K.resid_scale_norm_bwd(x, x0, lr, l0, idx, g1, g2, dr2, d02, EPS, dx0_acc=acc)
+    assert out.data_ptr() == acc.data_ptr() and torch.equal(dx2, dx)
+    _close(out, want, what="dx0 accumulated")
 
 
 def test_add_norm_relu_residual_embedding():
