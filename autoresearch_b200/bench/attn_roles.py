@@ -58,9 +58,12 @@ def fwd2(a):
         p = prof.cpu()
         nt = (T + 127) // 128 if W >= T else (W // 128 + 2)
         print(f"cycles per key tile, heaviest CTA ({nt} key tiles, two query tiles each)")
+        # fwd3: marks inside the issuing thread cost it registers (it runs on 56) and the spills showed up as slow MMAs,
+        # so that kernel reports the thread's total only
+        issuer = ["total"] + [""] * 7 if which == "fwd3" else ["total", "wait V(t)", "wait P0(t)", "issue PV0(t)", "wait K(t+1)",
+                                                               "issue S0(t+1)", "wait P1(t)", "issue PV1(t), S1(t+1)"]
         for role, label, names in (
-                (0, "issuer", ["total", "wait V(t)", "wait P0(t)", "issue PV0(t)", "wait K(t+1)", "issue S0(t+1)", "wait P1(t)",
-                               "issue PV1(t), S1(t+1)"]),
+                (0, "issuer", issuer),
                 (2, "softmax g0", ["total", "wait S", "row max", "rescale", "exp + store P", "store wait, arrive", "", ""]),
                 (3, "softmax g1", ["total", "wait S", "row max", "rescale", "exp + store P", "store wait, arrive", "", ""])):
             row = p[role * 8: role * 8 + 8].tolist()

@@ -123,12 +123,16 @@ attn_fwd2_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const uint32_t sq = smem_u32(smem + Fwd2Smem::Q);
       const uint32_t sk0 = smem_u32(smem + Fwd2Smem::K0), sv0 = smem_u32(smem + Fwd2Smem::V0);
       int cnt[2] = {0, 0};                           // key tiles of each query tile whose PV has been issued
+      // descriptor words computed once; a K slice or a ring slot is an add on the low word (start address >> 4)
+      const uint32_t hi_k = uint32_t(make_smem_desc(0, 0, 1024) >> 32), hi_v = uint32_t(make_smem_desc(0, 16384, 1024) >> 32);
+      const uint32_t q_lo = uint32_t(make_smem_desc(sq, 0, 1024)), k_lo = uint32_t(make_smem_desc(sk0, 0, 1024));
+      const uint32_t v_lo = uint32_t(make_smem_desc(sv0, 16384, 1024));
       auto issue_s = [&](int i, int t) {             // S_i = Q_i K(t)^T ; K(t) has been waited for by the caller
-        const uint32_t sk = sk0 + uint32_t((t - lo) % 3) * 32768u, sa = sq + uint32_t(i) * 32768u;
+        const uint32_t kb = k_lo + uint32_t((t - lo) % 3) * 2048u, qa = q_lo + uint32_t(i) * 2048u;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t off = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
-          tc_mma_ss(tmem + uint32_t(i) * 128u, make_smem_desc(sa + off, 0, 1024), make_smem_desc(sk + off, 0, 1024), idesc_s, k > 0);
+          const uint32_t off = uint32_t(k >> 2) * 1024u + uint32_t(k & 3) * 2u;
+          tc_mma_ss_lh(tmem + uint32_t(i) * 128u, qa + off, hi_k, kb + off, hi_k, idesc_s, k > 0);
         }
         tc_commit(&s_full[i]);
       };
@@ -138,11 +142,11 @@ attn_fwd2_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         return true;
       };
       auto issue_pv = [&](int i, int t) {            // O_i += P_i V(t)
-        const uint32_t sv = sv0 + uint32_t((t - lo) & 1) * 32768u;
+        const uint32_t vb = v_lo + uint32_t((t - lo) & 1) * 2048u;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          tc_mma_ts(tmem + 256u + uint32_t(i) * 128u, tmem + uint32_t(i) * 128u + uint32_t(k) * 8u,
-                    make_smem_desc(sv + k * 2048, 16384, 1024), idesc_o, (cnt[i] > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ts_lh(tmem + 256u + uint32_t(i) * 128u, tmem + uint32_t(i) * 128u + uint32_t(k) * 8u, vb + uint32_t(k) * 128u, hi_v,
+                       idesc_o, (cnt[i] > 0 || k > 0) ? 1u : 0u);
         ++cnt[i];
         if (t == hi_i[i]) tc_commit(&o_done[i]);
       };

@@ -206,12 +206,18 @@ attn_fwd3_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const uint32_t sq = smem_u32(smem + Fwd3Smem::Q);
       const uint32_t sk0 = smem_u32(smem + Fwd3Smem::K0), sv0 = smem_u32(smem + Fwd3Smem::V0);
       int cnt[2] = {0, 0};                           // key tiles of each query tile whose PV has been issued
+      // descriptor words computed once: low word = start address >> 4 (+ the leading-dimension offset for V), high word
+      // constant; a K slice or a ring slot is a 32-bit add on the low word.  The thread issues from a warp whose scheduler
+      // also serves two softmax warps, so every instruction between two MMAs counts.
+      const uint32_t hi_k = uint32_t(make_smem_desc(0, 0, 1024) >> 32), hi_v = uint32_t(make_smem_desc(0, 16384, 1024) >> 32);
+      const uint32_t q_lo = uint32_t(make_smem_desc(sq, 0, 1024)), k_lo = uint32_t(make_smem_desc(sk0, 0, 1024));
+      const uint32_t v_lo = uint32_t(make_smem_desc(sv0, 16384, 1024));
       auto issue_s = [&](int i, int t) {             // S_i = Q_i K(t)^T ; K(t) has been waited for by the caller
-        const uint32_t sk = sk0 + uint32_t((t - lo) % 3) * 32768u, sa = sq + uint32_t(i) * 32768u;
+        const uint32_t kb = k_lo + uint32_t((t - lo) % 3) * 2048u, qa = q_lo + uint32_t(i) * 2048u;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t off = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
-          tc_mma_ss(tmem + uint32_t(i) * 128u, make_smem_desc(sa + off, 0, 1024), make_smem_desc(sk + off, 0, 1024), idesc_s, k > 0);
+          const uint32_t off = uint32_t(k >> 2) * 1024u + uint32_t(k & 3) * 2u;     // (16 KB half, 32 B slice) >> 4
+          tc_mma_ss_lh(tmem + uint32_t(i) * 128u, qa + off, hi_k, kb + off, hi_k, idesc_s, k > 0);
         }
         tc_commit(&s_full[i]);
       };
@@ -221,16 +227,15 @@ attn_fwd3_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         return true;
       };
       auto issue_pv = [&](int i, int t) {            // O_i += P_i V(t)
-        const uint32_t sv = sv0 + uint32_t((t - lo) & 1) * 32768u;
+        const uint32_t vb = v_lo + uint32_t((t - lo) & 1) * 2048u;
+        const uint32_t to = tmem + 256u + uint32_t(i) * 128u, tp = tmem + uint32_t(i) * 128u;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          tc_mma_ts(tmem + 256u + uint32_t(i) * 128u, tmem + uint32_t(i) * 128u + uint32_t(k) * 8u,
-                    make_smem_desc(sv + k * 2048, 16384, 1024), idesc_o, (cnt[i] > 0 || k > 0) ? 1u : 0u);
-        }
+        for (int k = 0; k < 8; ++k)
+          tc_mma_ts_lh(to, tp + uint32_t(k) * 8u, vb + uint32_t(k) * 128u, hi_v, idesc_o, (cnt[i] > 0 || k > 0) ? 1u : 0u);
         ++cnt[i];
         if (t == hi_i[i]) tc_commit(&o_done[i]);
       };
-      PROF_DECL();
+      PROF_DECL();                                   // total only: marks inside the loop cost this thread registers it does not have
       bool ok = mbar_wait(q_full, 0, abort_flag);
       if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
       if (ok) {
@@ -242,25 +247,18 @@ attn_fwd3_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       for (int t = lo; t <= hi && ok; ++t) {
         const int kt = t - lo;
         const bool nxt = t + 1 <= hi;
-        PROF_TIC();
         if (!mbar_wait(&v_full[kt & 1], uint32_t(kt >> 1) & 1u, abort_flag)) { ok = false; break; }
-        PROF_TOC(1);
         if (uses(0, t)) {
           if (!wait_p(0)) { ok = false; break; }
-          PROF_TOC(2);
           issue_pv(0, t);
         }
-        PROF_TOC(3);
         if (nxt) {
           if (!mbar_wait(&k_full[(kt + 1) % 3], uint32_t((kt + 1) / 3) & 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          PROF_TOC(4);
           if (uses(0, t + 1)) issue_s(0, t + 1);     // after PV0(t): it overwrites the tile P0(t) lives in
         }
-        PROF_TOC(5);
         if (uses(1, t)) {
           if (!wait_p(1)) { ok = false; break; }
-          PROF_TOC(6);
           issue_pv(1, t);
         }
         tc_commit(&v_empty[kt & 1]);
@@ -268,7 +266,6 @@ attn_fwd3_k(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           if (uses(1, t + 1)) issue_s(1, t + 1);
           tc_commit(&k_empty[(kt + 1) % 3]);
         }
-        PROF_TOC(7);
       }
       PROF_DUMP(0);
     }

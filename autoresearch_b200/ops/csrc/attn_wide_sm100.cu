@@ -51,19 +51,23 @@ static_assert(WideSmem::TOTAL <= 232448, "exceeds the 227 KB shared memory of on
 
 // One 128 x 128 x 128 product as eight K=16 MMAs.  A, B K-major tiles (two 16 KB halves).
 __device__ __forceinline__ void mma_tile_kk(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t idesc) {
+  // one descriptor per operand; a K slice is an add on its low word (start address >> 4)
+  const uint32_t hi = uint32_t(make_smem_desc(0, 0, 1024) >> 32);
+  const uint32_t al = uint32_t(make_smem_desc(sa, 0, 1024)), bl = uint32_t(make_smem_desc(sb, 0, 1024));
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
-    const uint32_t off = uint32_t(k >> 2) * 16384u + uint32_t(k & 3) * 32u;
-    tc_mma_ss(d_tmem, make_smem_desc(sa + off, 0, 1024), make_smem_desc(sb + off, 0, 1024), idesc, k > 0);
+    const uint32_t off = uint32_t(k >> 2) * 1024u + uint32_t(k & 3) * 2u;       // (16 KB half, 32 B slice) >> 4
+    tc_mma_ss_lh(d_tmem, al + off, hi, bl + off, hi, idesc, k > 0);
   }
 }
 // D (+)= A[tmem, 128 x 128 bf16 as two groups of 32 columns] * B[smem tile used MN-major: rows are K]
 __device__ __forceinline__ void mma_tile_ts(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t sb, uint32_t idesc,
                                             bool accumulate) {
+  const uint32_t hi = uint32_t(make_smem_desc(0, 16384, 1024) >> 32), bl = uint32_t(make_smem_desc(sb, 16384, 1024));
 #pragma unroll
   for (int k = 0; k < 8; ++k)
-    tc_mma_ts(d_tmem, (k < 4 ? a_lo : a_hi) + uint32_t(k & 3) * 8u, make_smem_desc(sb + k * 2048, 16384, 1024), idesc,
-              (accumulate || k > 0) ? 1u : 0u);
+    tc_mma_ts_lh(d_tmem, (k < 4 ? a_lo : a_hi) + uint32_t(k & 3) * 8u, bl + uint32_t(k) * 128u, hi, idesc,
+                 (accumulate || k > 0) ? 1u : 0u);
 }
 
 // exp2 of 64 scores of one row/lane; the offsets are one per-row value or 64 per-column values

@@ -518,8 +518,8 @@ __global__ void __launch_bounds__(256) ve_gate_bwd_k(const float* __restrict__ d
   const long long t0 = (long long)blockIdx.x * tok_per_cta;
   const long long t1 = min(N, t0 + tok_per_cta);
   const int tid = threadIdx.x;
-  if (tid < H * ch) {
-    const int h = tid / ch, j = tid - h * ch;
+  for (int p = tid; p < H * ch; p += blockDim.x) {
+    const int h = p / ch, j = p - h * ch;
     float acc = 0.f;
     for (long long t = t0; t < t1; ++t) acc += dgl[t * H + h] * __bfloat162float(xn[t * D_model + j]);
     atomicAdd(d_gate_w + h * ch + j, acc);
@@ -636,7 +636,7 @@ int arb_qkv_post_bwd(void* d_qkv, const void* qkv, const void* cos_t, const void
                      const int* ids, const void* ve_w, const void* gate_w, const float* gate, void* d_ve, float* d_gate_w,
                      void* d_xn_gate, float* dgl, long long N, int T, int H, int D_model, int gate_ch, cudaStream_t s) {
   if (N <= 0 || T <= 0 || H <= 0 || misaligned(d_qkv) || misaligned(qkv)) return -3;
-  if (ve_w && (!gate_w || !gate || !xn || !ids || !d_ve || !d_gate_w || !d_xn_gate || !dgl || H * gate_ch > 256)) return -3;
+  if (ve_w && (!gate_w || !gate || !xn || !ids || !d_ve || !d_gate_w || !d_xn_gate || !dgl)) return -3;
   qkv_post_bwd_k<<<int((N + 7) / 8), 256, 0, s>>>((bf16*)d_qkv, (const bf16*)qkv, (const bf16*)cos_t, (const bf16*)sin_t, rstd_qk,
                                                       (const bf16*)xn, ids, (const bf16*)ve_w, (const bf16*)gate_w, gate, (bf16*)d_ve,
                                                       dgl, N, T, H);

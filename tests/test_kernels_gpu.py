@@ -101,10 +101,11 @@ def test_softcap_ce(V):
     _close(loss2, ref, 1e-3)
 
 
-def test_qkv_post_matches_reference():
+@pytest.mark.parametrize("H", [2, 16])     # 16 heads x 32 gate channels = more (head, channel) pairs than threads in a CTA
+def test_qkv_post_matches_reference(H):
     from autoresearch_b200.ops import kernels as K, reference as R, sm100
     torch.manual_seed(4)
-    B, T, H, D, V, ch = 2, 64, 2, 256, 50, 32
+    B, T, D, V, ch = 2, 64, 128 * H, 50, 32
     N = B * T
     xn = _bf(N, D).requires_grad_(True)
     w = _bf(3 * D, D, scale=0.05).requires_grad_(True)
