@@ -11,64 +11,54 @@ namespace arb {
 
 constexpr int CE_THREADS = 256;
 
+// The soft-capped logits lie in [-cap, cap], so exp(s - cap) can neither overflow nor vanish in fp32 (cap = 15 gives
+// e^-30 at worst): the row maximum and its block-wide reduction are not needed.  One barrier per row.
 template <int VPT>  // 8-element vectors per thread
 __global__ void __launch_bounds__(CE_THREADS) softcap_ce_k(__nv_bfloat16* __restrict__ logits, long long ld,
                                                            const int* __restrict__ targets, float* __restrict__ loss,
                                                            int V, float cap, float gscale) {
   __shared__ float red[CE_THREADS / 32];
-  __shared__ float bcast;
   const long long row = blockIdx.x;
   __nv_bfloat16* p = logits + row * ld;
   const int nch = V >> 3;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float inv_cap = 1.f / cap;
-  float s[VPT][8];
-  float mx = -INFINITY;
+  const float k2 = cap * 1.4426950408889634f;      // exp(cap * (t - 1)) = exp2(k2 * t - k2)
+  const int tgt = targets[row];
+  const bool tgt_ok = tgt >= 0 && tgt < V;
+  float t[VPT][8];                                  // tanh(x / cap)
+  float sum = 0.f, t_tgt = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int c = tid + CE_THREADS * i;
     if (c < nch) {
-      uint4 u = *reinterpret_cast<const uint4*>(p + c * 8);
-      float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
-      float x[8] = {a.x, a.y, b.x, b.y, cc.x, cc.y, d.x, d.y};
+      const uint4 u = *reinterpret_cast<const uint4*>(p + c * 8);
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      const float x[8] = {a.x, a.y, b.x, b.y, cc.x, cc.y, d.x, d.y};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { s[i][j] = cap * tanhf(x[j] * inv_cap); mx = fmaxf(mx, s[i][j]); }
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if (lane == 0) red[warp] = mx;
-  __syncthreads();
-  if (tid == 0) { float m = red[0]; for (int w = 1; w < CE_THREADS / 32; ++w) m = fmaxf(m, red[w]); bcast = m; }
-  __syncthreads();
-  mx = bcast;
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int c = tid + CE_THREADS * i;
-    if (c < nch) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) sum += __expf(s[i][j] - mx);
+      for (int j = 0; j < 8; ++j) {
+        t[i][j] = tanhf(x[j] * inv_cap);
+        sum += exp2f(fmaf(t[i][j], k2, -k2));
+        if (c * 8 + j == tgt) t_tgt = t[i][j];
+      }
     }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  __syncthreads();
   if (lane == 0) red[warp] = sum;
   __syncthreads();
-  if (tid == 0) { float t = 0.f; for (int w = 0; w < CE_THREADS / 32; ++w) t += red[w]; bcast = t; }
-  __syncthreads();
-  sum = bcast;
-  const float lse = mx + __logf(sum);
-  int tgt = targets[row];
-  const bool tgt_ok = tgt >= 0 && tgt < V;
-  if (tid == 0) {
-    float st = 0.f;
-    if (tgt_ok) st = cap * tanhf(__bfloat162float(p[tgt]) * inv_cap);
-    loss[row] = tgt_ok ? (lse - st) : 0.f;
+  sum = 0.f;
+#pragma unroll
+  for (int w = 0; w < CE_THREADS / 32; ++w) sum += red[w];     // same order in every thread
+  const float lse = cap + __logf(sum);
+  // the thread that holds the target column writes the loss; thread 0 writes 0 for an out-of-range target
+  if (tgt_ok) {
+    const int ct = tgt >> 3;
+    if ((ct % CE_THREADS) == tid) loss[row] = lse - cap * t_tgt;
+  } else if (tid == 0) {
+    loss[row] = 0.f;
   }
   if (gscale != 0.f) {
-    __syncthreads();  // p[tgt] has been read before anyone overwrites it
     const float inv_sum = 1.f / sum;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -77,10 +67,10 @@ __global__ void __launch_bounds__(CE_THREADS) softcap_ce_k(__nv_bfloat16* __rest
         float g[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float pr = __expf(s[i][j] - mx) * inv_sum;
-          const float t = s[i][j] * inv_cap;
-          const float ind = (tgt_ok && (c * 8 + j == tgt)) ? 1.f : 0.f;
-          g[j] = tgt_ok ? (pr - ind) * gscale * (1.f - t * t) : 0.f;
+          const float tt = t[i][j];
+          const float pr = exp2f(fmaf(tt, k2, -k2)) * inv_sum;
+          const float ind = (c * 8 + j == tgt) ? 1.f : 0.f;
+          g[j] = tgt_ok ? (pr - ind) * gscale * (1.f - tt * tt) : 0.f;
         }
         uint4 u;
         u.x = pack_bf16(g[0], g[1]); u.y = pack_bf16(g[2], g[3]); u.z = pack_bf16(g[4], g[5]); u.w = pack_bf16(g[6], g[7]);
