@@ -34,12 +34,21 @@ HEADLINE_SHAPES = [  # (name, M, N, K, layout) at the 428 M config, 131072 token
 ]
 
 
-def table(iters=10, warmup=3):
+PHASE1_SHAPES = [  # the 119.5 M config (D=512): 64 sequences of 2048 tokens per micro-batch
+    ("qkv fwd", 131072, 1536, 512, "nt"), ("o-proj fwd", 131072, 512, 512, "nt"),
+    ("fc1 fwd", 131072, 2048, 512, "nt"), ("fc2 fwd", 131072, 512, 2048, "nt"),
+    ("fc2 dX", 131072, 2048, 512, "nn"), ("qkv dX", 131072, 512, 1536, "nn"),
+    ("fc1 dW", 2048, 512, 131072, "tn"), ("o-proj dW", 512, 512, 131072, "tn"),
+    ("lm head chunk", 16384, 8192, 512, "nt"),
+]
+
+
+def table(iters=10, warmup=3, shapes=None):
     """Markdown table of the headline shapes: own kernel vs torch.matmul, CUDA events."""
     rows = ["| GEMM | M | N | K | layout | own ms | own TFLOP/s | cuBLAS ms | cuBLAS TFLOP/s | ratio |", "|---|---|---|---|---|---|---|---|---|---|"]
     g = torch.Generator(device="cuda").manual_seed(0)
     r = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
-    for name, M, N, Kd, lay in HEADLINE_SHAPES:
+    for name, M, N, Kd, lay in (shapes or HEADLINE_SHAPES):
         if lay == "nt":
             x, w = r(M, Kd), r(N, Kd)
             f, ref = (lambda: K.gemm(x, w)), (lambda: x @ w.t())
@@ -60,7 +69,8 @@ def table(iters=10, warmup=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--table", action="store_true", help="print the headline-shape table and exit")
+    ap.add_argument("--table", action="store_true", help="print the table of one model's GEMM shapes and exit")
+    ap.add_argument("--shapes", default="headline", choices=["headline", "phase1"], help="which model's shapes --table times")
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=1024)
@@ -71,7 +81,7 @@ def main():
     ap.add_argument("--no-ref", action="store_true")
     a = ap.parse_args()
     if a.table:
-        print(table(a.iters, a.warmup))
+        print(table(a.iters, a.warmup, PHASE1_SHAPES if a.shapes == "phase1" else HEADLINE_SHAPES))
         return
     K.gemm_set_mode(a.mode)
     M, N, Kd = a.M, a.N, a.K

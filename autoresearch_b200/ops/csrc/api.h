@@ -15,6 +15,8 @@ enum ArbEpilogue {
   EPI_RELU2_BWD = 4,    // C = acc * 2*sqrt(max(aux, 0)): aux = relu(h)^2 saved by the forward (bf16)
   EPI_STORE_F32 = 5,    // C = acc                      (fp32)
   EPI_ADD_AUX = 6,      // C = aux + acc                (bf16)
+  EPI_QKV_POST = 7,     // packed q|k|v projection: RoPE + RMS norm on q and k heads, value embedding on v heads (bf16);
+                        // 2-CTA tiles, NT layout; parameters from arb_gemm_qkv_post_args
 };
 
 enum ArbError {
@@ -65,6 +67,14 @@ int arb_gemm_bf16_ragged(const void* A, const void* B, void* C, const void* aux,
                          float gamma, int* err_flag, cudaStream_t stream, const void* pull_src, long long pull_bytes,
                          const void* ahead_src, void* ahead_dst, long long ahead_bytes, const int* m_valid, int b_div,
                          const int* k_valid, int k_seg_rows);
+// Parameters of the next EPI_QKV_POST product on this host thread (consumed by it).  The product is
+// [rows, D] x [3 * H * 128, D]^T; column blocks of 128 are heads: H query heads, H key heads, H value heads.
+// Query and key heads are rotated (cos / sin: bf16 [T, 64], position = row % T; lo' = lo c + hi s, hi' = hi c - lo s)
+// and divided by their RMS over 128 (its inverse goes to rstd_qk[row, 2H]).  With ve_w given, value head h gets
+// 2 sigmoid(xn[row, :gate_ch] . gate_w[h]) * ve_w[ids[row], h] added; the gate logit goes to gate_out[row, H].
+int arb_gemm_qkv_post_args(const void* cos_t, const void* sin_t, float* rstd_qk, int T, int H, const void* xn,
+                           long long ld_xn, const int* ids, const void* ve_w, const void* gate_w, float* gate_out,
+                           int gate_ch, float eps);
 
 // Tile selection: 0 = automatic (2-CTA 256x256 tiles when M >= 512 and N >= 256, else 1-CTA
 // 128x256/128x128), 1 = always 1-CTA, 2 = always 2-CTA.  Process-wide; meant for tests / benchmarks.

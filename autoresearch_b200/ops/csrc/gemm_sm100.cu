@@ -27,6 +27,22 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 224;
 
+// EPI_QKV_POST: what the epilogue does to the heads of the packed q|k|v projection (see api.h)
+struct QkvPostArgs {
+  const __nv_bfloat16* cos_t;
+  const __nv_bfloat16* sin_t;
+  float* rstd;
+  int T, H;
+  const __nv_bfloat16* xn;
+  long long ld_xn;
+  const int* ids;
+  const __nv_bfloat16* ve;
+  const __nv_bfloat16* gate_w;
+  float* gate;
+  int gate_ch;
+  float eps;
+};
+
 struct GemmArgs {
   int M, N, K, batch;
   int m_tiles, n_tiles, kb_total, kb_per_split, splitk;
@@ -60,6 +76,7 @@ struct GemmArgs {
   int b_div;
   const int* k_valid;
   int k_seg_kb, k_nseg;
+  QkvPostArgs qp;
 };
 
 // K blocks of [kb0, kb1) of batch item b that are multiplied
@@ -379,6 +396,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
 }
 
+// One head (128 accumulator columns of one row) of the packed q|k|v projection, in place.
+__device__ __forceinline__ void qkv_post_head(float (&f)[128], const QkvPostArgs& q, int row, int col_h) {
+  const int Dl = q.H * 128;
+  const int sec = col_h / Dl;                       // 0 query, 1 key, 2 value
+  const int head = (col_h - sec * Dl) >> 7;
+  if (sec < 2) {
+    const int t = row % q.T;
+    const uint4* cp = reinterpret_cast<const uint4*>(q.cos_t + (long long)t * 64);
+    const uint4* sp = reinterpret_cast<const uint4*>(q.sin_t + (long long)t * 64);
+    float ss = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const uint4 cu = __ldg(cp + g), su = __ldg(sp + g);
+      const uint32_t cw[4] = {cu.x, cu.y, cu.z, cu.w}, sw[4] = {su.x, su.y, su.z, su.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 c2 = unpack_bf16(cw[e]), s2 = unpack_bf16(sw[e]);
+        const int j = g * 8 + 2 * e;
+        const float lo0 = f[j], hi0 = f[j + 64], lo1 = f[j + 1], hi1 = f[j + 65];
+        const float a0 = lo0 * c2.x + hi0 * s2.x, b0 = hi0 * c2.x - lo0 * s2.x;
+        const float a1 = lo1 * c2.y + hi1 * s2.y, b1 = hi1 * c2.y - lo1 * s2.y;
+        f[j] = a0; f[j + 64] = b0; f[j + 1] = a1; f[j + 65] = b1;
+        ss += a0 * a0 + b0 * b0 + a1 * a1 + b1 * b1;
+      }
+    }
+    const float r = rsqrtf(ss * (1.f / 128.f) + q.eps);
+#pragma unroll
+    for (int j = 0; j < 128; ++j) f[j] *= r;
+    q.rstd[(long long)row * (2 * q.H) + sec * q.H + head] = r;
+  } else if (q.ve) {
+    const __nv_bfloat16* xr = q.xn + (long long)row * q.ld_xn;
+    const __nv_bfloat16* gw = q.gate_w + head * q.gate_ch;
+    float gl = 0.f;
+    for (int j = 0; j < q.gate_ch; j += 8) {
+      const uint4 xu = __ldg(reinterpret_cast<const uint4*>(xr + j)), gu = __ldg(reinterpret_cast<const uint4*>(gw + j));
+      const uint32_t xw[4] = {xu.x, xu.y, xu.z, xu.w}, gg[4] = {gu.x, gu.y, gu.z, gu.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = unpack_bf16(xw[e]), b = unpack_bf16(gg[e]);
+        gl += a.x * b.x + a.y * b.y;
+      }
+    }
+    q.gate[(long long)row * q.H + head] = gl;
+    const float gs = 2.f / (1.f + __expf(-gl));
+    const uint4* vp = reinterpret_cast<const uint4*>(q.ve + (long long)q.ids[row] * Dl + head * 128);
+#pragma unroll
+    for (int g = 0; g < 16; ++g) {
+      const uint4 eu = __ldg(vp + g);
+      const uint32_t ew[4] = {eu.x, eu.y, eu.z, eu.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 v = unpack_bf16(ew[e]);
+        f[g * 8 + 2 * e] += gs * v.x;
+        f[g * 8 + 2 * e + 1] += gs * v.y;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // 2-CTA variant: a cluster of two CTAs (one SM pair) owns a 256 x 256 tile.  Each CTA loads its
 // own 128 rows of A and 128 of the 256 rows of B (half the B traffic per SM of the 1-CTA kernel,
@@ -605,6 +681,49 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(&xfull_bar[0], 16384);
           tma_load_3d(smem + L::X_STAGE, &tmX, &xfull_bar[0], nt * BN2, row0, b);
         }
+        if constexpr (EPI == EPI_QKV_POST) {
+          // a head (128 columns) at a time: both halves of a rotation pair and the whole RMS sit in one thread's registers;
+          // the two 64-column staging slabs are written together and leave as two TMA stores
+#pragma unroll 1
+          for (int hh = 0; hh < 2; ++hh) {
+            const int col_h = nt * BN2 + hh * 128;
+            float f[128];
+            {
+              uint32_t v0[32], v1[32], v2[32], v3[32];
+              const uint32_t ta = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN2 + hh * 128);
+              tmem_ld32(ta, v0); tmem_ld32(ta + 32u, v1); tmem_ld32(ta + 64u, v2); tmem_ld32(ta + 96u, v3);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                f[j] = __uint_as_float(v0[j]); f[32 + j] = __uint_as_float(v1[j]);
+                f[64 + j] = __uint_as_float(v2[j]); f[96 + j] = __uint_as_float(v3[j]);
+              }
+            }
+            if (row_ok && col_h < p.N) qkv_post_head(f, p.qp, row, col_h);
+            if (t0) tma_store_wait_read();                // both stores of the previous head have read their slabs
+            named_barrier(2, 128);                        // (they drained while this head was computed)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const uint32_t cbase = smem_u32(smem + L::C_STAGE + half * 16384);
+#pragma unroll
+              for (int j = 0; j < 64; j += 8) {
+                const float* g = f + half * 64 + j;
+                uint4 u;
+                u.x = pack_bf16(g[0], g[1]); u.y = pack_bf16(g[2], g[3]); u.z = pack_bf16(g[4], g[5]); u.w = pack_bf16(g[6], g[7]);
+                st_sw128(cbase, 128, r_local, j, u);
+              }
+            }
+            fence_proxy_async_smem();
+            named_barrier(3, 128);
+            if (t0) {
+              if (col_h < p.N && row0 < p.M) {
+                tma_store_3d(&tmC, smem + L::C_STAGE, col_h, row0, b);
+                tma_store_3d(&tmC, smem + L::C_STAGE + 16384, col_h + 64, row0, b);
+              }
+              tma_store_commit();
+            }
+          }
+        } else {
 #pragma unroll 1
         for (int sl = 0; sl < (epi_is_bf16(EPI) ? 4 : 0); ++sl, ++slab_it) {
           const int buf = slab_it & 1;
@@ -681,6 +800,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else if (t0) {
             tma_store_commit();                           // keep the group count in step with the slab count
           }
+        }
         }
       }
       tc_fence_before();
@@ -798,6 +918,9 @@ static int dispatch_pair(int epi, const CUtensorMap& ta, const CUtensorMap& tb, 
     case EPI_RELU2_BWD: return launch_pair<A_MN, B_MN, EPI_RELU2_BWD>(ta, tb, a, st);
     case EPI_STORE_F32: return launch_pair<A_MN, B_MN, EPI_STORE_F32>(ta, tb, a, st);
     case EPI_ADD_AUX: return launch_pair<A_MN, B_MN, EPI_ADD_AUX>(ta, tb, a, st);
+    case EPI_QKV_POST:
+      if constexpr (!A_MN && !B_MN) return launch_pair<false, false, EPI_QKV_POST>(ta, tb, a, st);
+      else return -3;
   }
   return -2;
 }
@@ -819,6 +942,27 @@ static int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, c
 }  // namespace arb
 
 using namespace arb;
+
+static thread_local QkvPostArgs g_qkv_post;
+static thread_local bool g_qkv_post_set = false;
+
+extern "C" int arb_gemm_qkv_post_args(const void* cos_t, const void* sin_t, float* rstd_qk, int T, int H, const void* xn,
+                                      long long ld_xn, const int* ids, const void* ve_w, const void* gate_w, float* gate_out,
+                                      int gate_ch, float eps) {
+  g_qkv_post_set = false;
+  if (!cos_t || !sin_t || !rstd_qk || T <= 0 || H <= 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t)) & 15) return -4;
+  if (ve_w) {
+    if (!xn || !ids || !gate_w || !gate_out || gate_ch <= 0 || (gate_ch & 7) || (ld_xn & 7)) return -3;
+    if ((reinterpret_cast<uintptr_t>(xn) | reinterpret_cast<uintptr_t>(ve_w) | reinterpret_cast<uintptr_t>(gate_w)) & 15) return -4;
+  }
+  QkvPostArgs& q = g_qkv_post;
+  q.cos_t = (const __nv_bfloat16*)cos_t; q.sin_t = (const __nv_bfloat16*)sin_t; q.rstd = rstd_qk; q.T = T; q.H = H;
+  q.xn = (const __nv_bfloat16*)xn; q.ld_xn = ld_xn; q.ids = ids; q.ve = (const __nv_bfloat16*)ve_w;
+  q.gate_w = (const __nv_bfloat16*)gate_w; q.gate = gate_out; q.gate_ch = gate_ch; q.eps = eps;
+  g_qkv_post_set = true;
+  return 0;
+}
 
 extern "C" int arb_gemm_set_mode(int mode) {
   if (mode < 0 || mode > 2) return -3;
@@ -910,6 +1054,13 @@ extern "C" int arb_gemm_bf16_ragged(const void* A, const void* B, void* C, const
   a.m_valid = m_valid; a.b_div = b_div; a.k_valid = k_valid;
   a.k_seg_kb = k_valid ? k_seg_rows / BK : 1;
   a.k_nseg = k_valid ? K / k_seg_rows : 1;
+  std::memset(&a.qp, 0, sizeof a.qp);
+  if (epi == EPI_QKV_POST) {
+    const bool have = g_qkv_post_set;
+    g_qkv_post_set = false;
+    if (!have || !pair || a_mn_major || b_mn_major || batch != 1 || N != 3 * g_qkv_post.H * 128) return -6;
+    a.qp = g_qkv_post;
+  }
 
   CUtensorMap ta, tb;
   {

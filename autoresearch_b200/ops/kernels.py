@@ -6,6 +6,7 @@ so a missing or failing native kernel is never silently replaced by a PyTorch fa
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -15,7 +16,7 @@ from . import build as _build
 _lib = None
 _err_flag = {}
 
-EPI_STORE_BF16, EPI_RELU2, EPI_ATOMIC_F32, EPI_NS_COMBINE, EPI_RELU2_BWD, EPI_STORE_F32, EPI_ADD_AUX = range(7)
+EPI_STORE_BF16, EPI_RELU2, EPI_ATOMIC_F32, EPI_NS_COMBINE, EPI_RELU2_BWD, EPI_STORE_F32, EPI_ADD_AUX, EPI_QKV_POST = range(8)
 ERR_NAMES = {1: "GEMM barrier wait timed out", 2: "attention barrier wait timed out",
              3: "peer barrier wait timed out", 4: "MoE dispatch wait timed out",
              5: "dynamic shared memory base is not 1 KB aligned"}
@@ -63,6 +64,7 @@ def lib() -> C.CDLL:
         "arb_relu_sq_fwd": [vp, vp, i64, vp],
         "arb_relu_sq_bwd": [vp, vp, vp, i64, vp],
         "arb_qkv_post_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, vp],
+        "arb_gemm_qkv_post_args": [vp, vp, vp, i32, i32, vp, i64, vp, vp, vp, vp, i32, f32],
         "arb_qkv_post_bwd": [vp] * 14 + [i64, i32, i32, i32, i32, vp],
         "arb_embedding_fwd": [vp, vp, vp, i64, i32, i32, vp],
         "arb_embedding_bwd": [vp, vp, vp, i64, i32, i32, vp],
@@ -157,7 +159,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
          out: Optional[torch.Tensor] = None, epi: int = EPI_STORE_BF16, aux: Optional[torch.Tensor] = None,
          splitk: int = 0, alpha: float = 0.0, beta: float = 0.0, gamma: float = 1.0,
          m_valid: Optional[torch.Tensor] = None, b_div: int = 1, k_valid: Optional[torch.Tensor] = None,
-         k_seg: int = 0) -> torch.Tensor:
+         k_seg: int = 0, post: Optional[dict] = None) -> torch.Tensor:
     """C = op(A) @ op(B) on the tcgen05 kernel.
 
     2-D or batched 3-D bf16 operands with unit inner stride.  ``trans_a=False``: ``a`` is
@@ -168,6 +170,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     tiles beyond are neither computed nor written); ``b_div``: ``b`` holds G / b_div matrices, item g uses matrix
     g // b_div; ``k_valid`` int32 [G, K // k_seg] with ``k_seg`` rows per segment: for EPI_ATOMIC_F32 products over
     rows, only the 64-row blocks below ``k_valid`` of each segment are multiplied.
+
+    ``epi=EPI_QKV_POST`` with ``post`` = the arguments of :func:`qkv_post_args`: the packed q|k|v projection with
+    RoPE + RMS norm of the q / k heads and the value embedding of the v heads done in the epilogue.
     """
     _bf16(a, "a"); _bf16(b, "b")
     batched = a.dim() == 3
@@ -222,6 +227,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         if t is not None and (t.dtype != torch.int32 or not t.is_cuda or not t.is_contiguous() or t.numel() != n_want):
             raise ValueError(f"{nm} must be a contiguous CUDA int32 tensor of {n_want} elements")
     try:
+        if (epi == EPI_QKV_POST) != (post is not None):
+            raise ValueError("EPI_QKV_POST and post= go together")
+        if post is not None:
+            qkv_post_args(**post)
         rc = lib().arb_gemm_bf16_ragged(a.data_ptr(), b.data_ptr(), out.data_ptr(), auxp, M, N, K, G,
                                         a2.stride(0), b2.stride(0), o2.stride(0), sa, sb, so,
                                         int(trans_a), int(not trans_b), epi, splitk, alpha, beta, gamma,
@@ -239,6 +248,22 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
             pending_pulls[b.data_ptr()] = pull
         raise
     return out
+
+
+def qkv_post_args(cos, sin, rstd, T, H, xn=None, ids=None, ve_w=None, gate_w=None, gate=None, gate_ch=0, eps=1e-6) -> None:
+    """Parameters of the next EPI_QKV_POST product on this thread (rstd [rows, 2H] fp32 and, with a value embedding,
+    gate [rows, H] fp32 are outputs)."""
+    has_ve = ve_w is not None
+    _check(lib().arb_gemm_qkv_post_args(cos.data_ptr(), sin.data_ptr(), rstd.data_ptr(), T, H,
+                                        xn.data_ptr() if has_ve else None, xn.stride(0) if has_ve else 0,
+                                        ids.data_ptr() if has_ve else None, ve_w.data_ptr() if has_ve else None,
+                                        gate_w.data_ptr() if has_ve else None, gate.data_ptr() if has_ve else None,
+                                        gate_ch if has_ve else 0, eps), "gemm_qkv_post_args")
+
+
+def qkv_post_fusable(rows: int, cols: int) -> bool:
+    """The fused epilogue exists in the 2-CTA kernel only (products of at least 512 rows and 256 columns)."""
+    return rows >= 512 and cols >= 256 and os.environ.get("ARB_QKV_EPILOGUE", "1") != "0"
 
 
 def gemm_set_mode(mode: int) -> None:

@@ -287,6 +287,17 @@ class AttnPreFn(torch.autograd.Function):
     def forward(ctx, xn, wqkv, ids, ve_w, gate_w, cos, sin, T, H, gate_ch, eps, tp=None):
         # tp (a FusedTPContext): xn is this rank's sequence shard; the gather is overlapped with the GEMM
         ctx.tp = tp
+        if tp is None and K.qkv_post_fusable(xn.shape[0], wqkv.shape[0]):
+            # RoPE, QK-norm and the value embedding run in the epilogue of the projection: qkv is written once
+            N, D = xn.shape
+            rstd = torch.empty(N, 2 * H, dtype=torch.float32, device=xn.device)
+            gate = torch.empty(N, H, dtype=torch.float32, device=xn.device) if ve_w is not None else None
+            qkv = K.gemm(xn, wqkv, epi=K.EPI_QKV_POST,
+                         post=dict(cos=cos, sin=sin, rstd=rstd, T=T, H=H, xn=xn, ids=ids, ve_w=ve_w, gate_w=gate_w, gate=gate,
+                                   gate_ch=gate_ch, eps=eps))
+            ctx.save_for_backward(xn, wqkv, ids, ve_w, gate_w, cos, sin, qkv, rstd, gate)
+            ctx.dims = (T, H, gate_ch)
+            return qkv
         if tp is not None:
             qkv, xn = tp.ag_gemm(xn, wqkv)
         else:

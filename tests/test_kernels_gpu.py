@@ -101,11 +101,14 @@ def test_softcap_ce(V):
     _close(loss2, ref, 1e-3)
 
 
-@pytest.mark.parametrize("H", [2, 16])     # 16 heads x 32 gate channels = more (head, channel) pairs than threads in a CTA
-def test_qkv_post_matches_reference(H):
+# 16 heads x 32 gate channels = more (head, channel) pairs than threads in a CTA; 1024 rows take the projection whose
+# epilogue does RoPE / QK-norm / value embedding itself, 128 rows the separate kernel
+@pytest.mark.parametrize("H,B,T", [(2, 2, 64), (16, 2, 64), (2, 4, 256), (3, 3, 256)])
+def test_qkv_post_matches_reference(H, B, T):
     from autoresearch_b200.ops import kernels as K, reference as R, sm100
     torch.manual_seed(4)
-    B, T, D, V, ch = 2, 64, 128 * H, 50, 32
+    D, V, ch = 128 * H, 50, 32
+    assert K.qkv_post_fusable(B * T, 3 * D) == (B * T >= 512)
     N = B * T
     xn = _bf(N, D).requires_grad_(True)
     w = _bf(3 * D, D, scale=0.05).requires_grad_(True)
