@@ -380,7 +380,8 @@ def _embedding_plan(ids, vocab: int):
     N = ids.numel()
     flat = ids.reshape(-1).long().clamp(0, vocab - 1)
     perm = torch.sort(flat, stable=True).indices.contiguous()                     # int64 [N]
-    counts = torch.bincount(flat, minlength=vocab)[:vocab]
+    # (torch.bincount reads the largest id back to the host to size its result: a sync per micro-batch)
+    counts = torch.zeros(vocab, dtype=torch.int64, device=ids.device).scatter_add_(0, flat, torch.ones_like(flat))
     seg_start = (torch.cumsum(counts, 0) - counts).to(torch.int32)
     n_it = (counts + R - 1) // R
     it_end = torch.cumsum(n_it, 0)
