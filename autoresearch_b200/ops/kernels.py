@@ -14,6 +14,7 @@ import torch
 from . import build as _build
 
 _lib = None
+_gemm_mode = 0       # as set by gemm_set_mode: 0 automatic, 1 always 1-CTA tiles, 2 always 2-CTA tiles
 _err_flag = {}
 
 EPI_STORE_BF16, EPI_RELU2, EPI_ATOMIC_F32, EPI_NS_COMBINE, EPI_RELU2_BWD, EPI_STORE_F32, EPI_ADD_AUX, EPI_QKV_POST = range(8)
@@ -263,15 +264,19 @@ def qkv_post_args(cos, sin, rstd, T, H, xn=None, ids=None, ve_w=None, gate_w=Non
 
 def qkv_post_fusable(rows: int, cols: int) -> bool:
     """The fused epilogue exists in the 2-CTA kernel only (products of at least 512 rows and 256 columns)."""
-    return rows >= 512 and cols >= 256 and os.environ.get("ARB_QKV_EPILOGUE", "1") != "0"
+    if os.environ.get("ARB_QKV_EPILOGUE", "1") == "0" or _gemm_mode == 1:
+        return False
+    return _gemm_mode == 2 or (rows >= 512 and cols >= 256)
 
 
 def gemm_set_mode(mode: int) -> None:
     """0 = automatic tile choice, 1 = always 1-CTA tiles, 2 = always 2-CTA (cta_group::2) tiles."""
+    global _gemm_mode
     f = lib().arb_gemm_set_mode
     f.restype, f.argtypes = C.c_int, [C.c_int]
     if f(mode) != 0:
         raise ValueError(f"bad GEMM mode {mode}")
+    _gemm_mode = mode
 
 
 def flush_pending_pulls() -> None:
