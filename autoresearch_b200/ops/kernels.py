@@ -46,8 +46,19 @@ def lib() -> C.CDLL:
     if not _build.is_current():
         _build.build()
     L = C.CDLL(str(_build.SO))
+    for name, args in _signatures().items():
+        if hasattr(L, name):
+            f = getattr(L, name)
+            f.restype = C.c_int
+            f.argtypes = args
+    _lib = L
+    return L
+
+
+def _signatures() -> dict:
+    """ctypes argument lists of the entry points declared in csrc/api.h (a CPU test counts them against the header)."""
     vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
-    sigs = {
+    return {
         "arb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32,
                           f32, f32, f32, vp, vp],
         "arb_gemm_bf16_ex": [vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i64, i32, i32, i32, i32,
@@ -97,13 +108,6 @@ def lib() -> C.CDLL:
         "arb_moe_combine_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
         "arb_moe_combine_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
     }
-    for name, args in sigs.items():
-        if hasattr(L, name):
-            f = getattr(L, name)
-            f.restype = C.c_int
-            f.argtypes = args
-    _lib = L
-    return L
 
 
 def available() -> bool:
